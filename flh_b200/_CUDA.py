@@ -1,0 +1,217 @@
+"""Drop-in for the `flh._CUDA` extension module (flh/cuda/flh_cuda_bindings.cpp:301-313).
+
+Same nine function names, argument order, validation (RuntimeError, as TORCH_CHECK raises) and
+return values; every call goes through the C ABI of libflh_b200.so on the tensor's device and the
+current torch stream.  `install()` binds this module to `flh._CUDA`, which every FLH call site
+resolves at call time (flh/nn/quantization.py:127,158,161; flh/nn/linear.py:128).
+
+Extended entry points for the per-token asymmetric mode follow the same conventions.
+PyTorch is used only for device memory, streams and the device guard.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+from .hadamard import get_hadK
+
+F16, BF16 = 0, 1
+GEMM_AUTO, GEMM_TCGEN05, GEMM_MMA_SYNC, GEMM_STREAM = 0, 1, 2, 3
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+# --------------------------------------------------------------------------- the nine pybind names
+def gemm_i4_dequant_o16(A, B, A_scale, B_scale):
+    """flh/cuda/flh_cuda_bindings.cpp:75-113.  u8[M,K/2], u8[N,K/2], f16[M,*], f16[N,*] -> f16[M,N]."""
+    _check(A.is_cuda and B.is_cuda and A_scale.is_cuda and B_scale.is_cuda, "tensors must be CUDA")
+    _check(A.dtype == torch.uint8, "A must be uint8 packed int4")
+    _check(B.dtype == torch.uint8, "B must be uint8 packed int4")
+    _check(A_scale.dtype == torch.float16, "A_scale must be float16")
+    _check(B_scale.dtype == torch.float16, "B_scale must be float16")
+    _check(A.is_contiguous() and B.is_contiguous() and A_scale.is_contiguous() and B_scale.is_contiguous(),
+           "tensors must be contiguous")
+    _check(A.dim() == 2 and B.dim() == 2, "A/B must be 2D")
+    _check(A_scale.dim() == 2 and B_scale.dim() == 2, "scale must be 2D")
+    M, Kp = A.shape
+    N = B.shape[0]
+    _check(B.shape[1] == Kp, "B.shape[1] must equal A.shape[1]")
+    _check(A_scale.shape[0] == M, "A_scale.shape[0] must equal M")
+    _check(B_scale.shape[0] == N, "B_scale.shape[0] must equal N")
+    return gemm_i4_dequant(A, B, A_scale, B_scale)
+
+
+def _fht(x, n):
+    _check(x.is_cuda, "Input tensor must be on CUDA")
+    _check(x.dtype == torch.float16, "Input tensor must be float16 (half)")
+    _check(x.dim() == 2, "Input tensor must be 2D")
+    _check(x.shape[1] == n, f"Last dimension must be {n}")
+    _check(x.is_contiguous(), "Input tensor must be contiguous")
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().flh_b200_hadamard_f16_inplace(_ptr(x), x.shape[0], n, _stream(x)), "hadamard_transform")
+    return x
+
+
+def hadamard_transform_half(x):
+    """In place, un-normalised, rows of 128 (flh/cuda/flh_cuda_bindings.cpp:115-126)."""
+    return _fht(x, 128)
+
+
+def hadamard_transform_64_half(x):
+    return _fht(x, 64)
+
+
+def hadamard_transform_32_half(x):
+    return _fht(x, 32)
+
+
+def _quant_group(x, gs, hadamard):
+    _check(x.is_cuda, "Input tensor must be on CUDA")
+    _check(x.dtype == torch.float16, "Input tensor must be float16 (half)")
+    _check(x.dim() == 2, "Input tensor must be 2D")
+    _check(gs in (32, 64, 128), "group_size must be 32, 64, or 128")
+    _check(x.shape[1] == gs, "Last dimension must equal group_size" if gs != 128 else "Last dimension must be 128")
+    _check(x.is_contiguous(), "Input tensor must be contiguous")
+    rows = x.shape[0]
+    q = torch.empty((rows, gs // 2), dtype=torch.uint8, device=x.device)
+    s = torch.empty((rows,), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().flh_b200_quant_group_sym_i4(_ptr(x), rows, gs, int(hadamard), _ptr(q), _ptr(s), _stream(x)),
+                   "quant_group_sym_i4")
+    return [q, s]
+
+
+def hadamard_and_quantize_i4(x):
+    """f16[R,128] -> [u8[R,64], f16[R]] (raw scale) — flh/cuda/flh_cuda_bindings.cpp:154-175."""
+    return _quant_group(x, 128, True)
+
+
+def quant_and_pack_i4(x):
+    """flh/cuda/flh_cuda_bindings.cpp:177-198."""
+    return _quant_group(x, 128, False)
+
+
+def hadamard_and_quantize_i4_gs(x, group_size):
+    """flh/cuda/flh_cuda_bindings.cpp:202-225."""
+    return _quant_group(x, int(group_size), True)
+
+
+def quant_and_pack_i4_gs(x, group_size):
+    """flh/cuda/flh_cuda_bindings.cpp:227-251."""
+    return _quant_group(x, int(group_size), False)
+
+
+def gemm_i4_dequant_o16_gs(A, B, A_scale, B_scale, group_size):
+    """flh/cuda/flh_cuda_bindings.cpp:253-299.  Only group 128 is served by this build; the
+    reference kernel itself applies one scale per 128-K block whatever group_size says."""
+    _check(group_size in (32, 64, 128), "group_size must be 32, 64, or 128")
+    _check(A.dim() == 2 and B.dim() == 2, "A/B must be 2D")
+    K = A.shape[1] * 2
+    _check(K % group_size == 0, "K must be divisible by group_size")
+    g = K // group_size
+    _check(A_scale.shape[0] == A.shape[0], "A_scale.shape[0] must equal M")
+    _check(A_scale.shape[1] == g, "A_scale.shape[1] must equal K/group_size")
+    _check(B_scale.shape[0] == B.shape[0], "B_scale.shape[0] must equal N")
+    _check(B_scale.shape[1] == g, "B_scale.shape[1] must equal K/group_size")
+    _check(group_size == 128, "flh_b200 serves group_size 128 only")
+    return gemm_i4_dequant_o16(A, B, A_scale, B_scale)
+
+
+# --------------------------------------------------------------------------- extended entry points
+_SIGN_CACHE: dict = {}
+
+
+def _sign_bits(n: int, device):
+    """(kfac, device uint32 bit rows or None) for width n, cached per device."""
+    signs, k = get_hadK(n)
+    if k == 1:
+        return 1, None
+    key = (k, str(device))
+    if key not in _SIGN_CACHE:
+        words = (k + 31) // 32
+        s8 = np.ascontiguousarray(signs, dtype=np.int8)
+        out = np.zeros((k, words), dtype=np.uint32)
+        _lib.check(_lib.load().flh_b200_pack_signs(s8.ctypes.data_as(ctypes.c_void_p), k,
+                                                   out.ctypes.data_as(ctypes.c_void_p)), "pack_signs")
+        _SIGN_CACHE[key] = torch.from_numpy(out.view(np.int32)).to(device)
+    return k, _SIGN_CACHE[key]
+
+
+def quant_token_asym_i4(x, hadamard: bool = True, clip: float = 1.0):
+    """x [M, K] f16/bf16 (row stride allowed) -> (q u8[M,K/2] codes 0..15, scale f16[M], zero f16[M]).
+    hadamard=True applies the full-width transform of matmul_hadU (flh/functional/hadamard.py:92-113)
+    before the per-token asymmetric quantiser of fake_quant/quant_utils.py:94-128."""
+    _check(x.is_cuda, "Input tensor must be on CUDA")
+    _check(x.dtype in (torch.float16, torch.bfloat16), "Input tensor must be float16 or bfloat16")
+    _check(x.dim() == 2 and x.stride(1) == 1, "Input tensor must be 2D with unit inner stride")
+    M, K = x.shape
+    kfac, bits = _sign_bits(K, x.device) if hadamard else (1, None)
+    q = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float16, device=x.device)
+    z = torch.empty((M,), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().flh_b200_quant_token_asym_i4(
+            _ptr(x), BF16 if x.dtype == torch.bfloat16 else F16, M, K, x.stride(0) if M > 1 else K, int(hadamard), kfac,
+            _ptr(bits), float(clip), _ptr(q), _ptr(s), _ptr(z), _stream(x)), "quant_token_asym_i4")
+    return q, s, z
+
+
+def weight_rowsum(B, group: int):
+    """int32 [N, K/group] sums of the signed weight codes (needed with zero-points)."""
+    _check(B.is_cuda and B.dtype == torch.uint8 and B.dim() == 2 and B.is_contiguous(), "B must be a contiguous CUDA uint8 matrix")
+    N, K = B.shape[0], B.shape[1] * 2
+    rs = torch.empty((N, K // group), dtype=torch.int32, device=B.device)
+    with torch.cuda.device(B.device):
+        _lib.check(_lib.load().flh_b200_weight_rowsum(_ptr(B), N, K, group, _ptr(rs), _stream(B)), "weight_rowsum")
+    return rs
+
+
+def gemm_i4_dequant(A, B, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=None,
+                    out_dtype=torch.float16, algo: int = GEMM_AUTO, out=None):
+    """General form of the GEMM (include/flh_b200.h: flh_b200_gemm_i4_dequant).  Scale granularity
+    is read off the scale shapes: a_group = K / A_scale.shape[1], b_group = K / B_scale.shape[1]."""
+    M, Kp = A.shape
+    N = B.shape[0]
+    K = Kp * 2
+    A_scale = A_scale.reshape(M, -1)
+    B_scale = B_scale.reshape(N, -1)
+    _check(A_scale.shape[1] > 0 and K % A_scale.shape[1] == 0, "A_scale columns must divide K")
+    _check(B_scale.shape[1] > 0 and K % B_scale.shape[1] == 0, "B_scale columns must divide K")
+    ag, bg = K // A_scale.shape[1], K // B_scale.shape[1]
+    D = out if out is not None else torch.empty((M, N), dtype=out_dtype, device=A.device)
+    with torch.cuda.device(A.device):
+        _lib.check(_lib.load().flh_b200_gemm_i4_dequant(
+            _ptr(A), _ptr(B), _ptr(A_scale), _ptr(A_zero), _ptr(B_scale), _ptr(B_rowsum), _ptr(bias), _ptr(D),
+            M, N, K, ag, bg, BF16 if D.dtype == torch.bfloat16 else F16, algo, None, 0, _stream(A)),
+            "gemm_i4_dequant")
+    return D
+
+
+def gemm_status():
+    """[code, cta, 0, 0] of the tcgen05 GEMM's bounded waits; synchronises.  0 = clean."""
+    out = (ctypes.c_int * 4)()
+    _lib.check(_lib.load().flh_b200_gemm_status(out), "gemm_status")
+    return list(out)
+
+
+def install():
+    """Bind this module as `flh._CUDA` so unmodified flh.nn / flh.quantized_model code runs on it."""
+    import sys
+    import flh  # the FLH package must be importable
+    flh._CUDA = sys.modules[__name__]
+    return flh

@@ -1,0 +1,191 @@
+// C ABI of libflh_b200.so: argument validation, error strings, algorithm choice.
+// Every entry point only enqueues work on the caller's stream.
+#include "common.cuh"
+#include <string.h>
+
+namespace flh {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int cuda_status(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return 0;
+    set_error("%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+    return -(int)e;
+}
+
+// kernels (other translation units)
+int launch_quant_group_sym(const void *, long, int, int, uint8_t *, void *, cudaStream_t);
+int launch_fht_inplace(void *, long, int, cudaStream_t);
+int launch_quant_token_asym(const void *, int, long, long, long, int, int, const uint32_t *, float,
+                            uint8_t *, void *, void *, cudaStream_t);
+int launch_weight_rowsum(const uint8_t *, long, long, long, int32_t *, cudaStream_t);
+int launch_gemm_mma_tile(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
+                         const int32_t *, const void *, void *, long, long, long, long, long, int,
+                         cudaStream_t);
+int launch_gemm_stream(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
+                       const int32_t *, const void *, void *, long, long, long, long, long, int,
+                       cudaStream_t);
+int launch_gemm_tcgen05(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
+                        const int32_t *, const void *, void *, long, long, long, long, long, int,
+                        cudaStream_t);
+
+int gemm_tcgen05_status(int *);
+int gemm_tcgen05_status_clear();
+
+static bool is_pow2(long v) { return v > 0 && (v & (v - 1)) == 0; }
+
+}  // namespace flh
+
+using namespace flh;
+
+extern "C" {
+
+int flh_b200_version(void) { return 100; }
+
+const char *flh_b200_last_error(void) { return g_err; }
+
+int flh_b200_device_check(void) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_status(e, "cudaGetDevice");
+    int major = 0, minor = 0;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+    FLH_REQUIRE(major == 10, FLH_B200_EUNSUPPORTED,
+                "flh_b200 is built for sm_100a only; device %d is sm_%d%d", dev, major, minor);
+    return 0;
+}
+
+int flh_b200_quant_group_sym_i4(const void *x, long rows, int gs, int hadamard, uint8_t *q,
+                                void *scales, void *stream) {
+    FLH_REQUIRE(rows >= 0, FLH_B200_EINVAL, "rows must be >= 0 (got %ld)", rows);
+    FLH_REQUIRE(gs == 32 || gs == 64 || gs == 128, FLH_B200_EINVAL, "group size must be 32, 64 or 128 (got %d)", gs);
+    if (rows == 0) return 0;
+    FLH_REQUIRE(x && q && scales, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(aligned16(x), FLH_B200_EALIGN, "x must be 16-byte aligned");
+    FLH_REQUIRE((reinterpret_cast<uintptr_t>(q) & 3) == 0, FLH_B200_EALIGN, "q must be 4-byte aligned");
+    return launch_quant_group_sym(x, rows, gs, hadamard != 0, q, scales, static_cast<cudaStream_t>(stream));
+}
+
+int flh_b200_hadamard_f16_inplace(void *x, long rows, int n, void *stream) {
+    FLH_REQUIRE(rows >= 0, FLH_B200_EINVAL, "rows must be >= 0 (got %ld)", rows);
+    FLH_REQUIRE(n == 32 || n == 64 || n == 128, FLH_B200_EINVAL, "row length must be 32, 64 or 128 (got %d)", n);
+    if (rows == 0) return 0;
+    FLH_REQUIRE(x, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(aligned16(x), FLH_B200_EALIGN, "x must be 16-byte aligned");
+    return launch_fht_inplace(x, rows, n, static_cast<cudaStream_t>(stream));
+}
+
+int flh_b200_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, long ld, int hadamard,
+                                 int kfac, const uint32_t *sign_bits, float clip, uint8_t *q,
+                                 void *scale, void *zero, void *stream) {
+    FLH_REQUIRE(M >= 0 && K > 0, FLH_B200_EINVAL, "bad shape M=%ld K=%ld", M, K);
+    FLH_REQUIRE(in_dtype == FLH_B200_F16 || in_dtype == FLH_B200_BF16, FLH_B200_EINVAL, "in_dtype must be F16 or BF16");
+    FLH_REQUIRE(K % 64 == 0 && K <= 32768, FLH_B200_EINVAL, "K must be a multiple of 64 and <= 32768 (got %ld)", K);
+    FLH_REQUIRE(ld >= K && ld % 8 == 0, FLH_B200_EALIGN, "row stride must be >= K and a multiple of 8 elements (got %ld)", ld);
+    FLH_REQUIRE(clip > 0.0f && clip <= 1.0f, FLH_B200_EINVAL, "clip ratio must be in (0, 1]");
+    if (hadamard) {
+        FLH_REQUIRE(kfac >= 1 && K % kfac == 0, FLH_B200_EINVAL, "kfac=%d does not divide K=%ld", kfac, K);
+        const long p = K / kfac;
+        FLH_REQUIRE(is_pow2(p) && p >= 64, FLH_B200_EINVAL, "K / kfac must be a power of two >= 64 (got %ld)", p);
+        FLH_REQUIRE(kfac == 1 || (kfac % 4 == 0 && kfac <= 172 && sign_bits), FLH_B200_EINVAL,
+                    "kfac must be 1 or a Hadamard order <= 172 with its sign bits");
+    } else {
+        kfac = 1;
+    }
+    if (M == 0) return 0;
+    FLH_REQUIRE(x && q && scale && zero, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(aligned16(x), FLH_B200_EALIGN, "x must be 16-byte aligned");
+    FLH_REQUIRE((reinterpret_cast<uintptr_t>(q) & 7) == 0, FLH_B200_EALIGN, "q must be 8-byte aligned");
+    return launch_quant_token_asym(x, in_dtype, M, K, ld, hadamard != 0, kfac, sign_bits, clip, q, scale,
+                                   zero, static_cast<cudaStream_t>(stream));
+}
+
+int flh_b200_pack_signs(const int8_t *signs, int kfac, uint32_t *out) {
+    FLH_REQUIRE(signs && out && kfac > 0, FLH_B200_EINVAL, "bad arguments");
+    const int words = (kfac + 31) / 32;
+    memset(out, 0, sizeof(uint32_t) * (size_t)kfac * words);
+    for (int k = 0; k < kfac; ++k)
+        for (int j = 0; j < kfac; ++j)
+            if (signs[k * kfac + j] < 0) out[k * words + (j >> 5)] |= 1u << (j & 31);
+    return 0;
+}
+
+int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t *rowsum, void *stream) {
+    FLH_REQUIRE(N >= 0 && K > 0 && group > 0, FLH_B200_EINVAL, "bad shape");
+    FLH_REQUIRE(K % group == 0 && group % 32 == 0, FLH_B200_EINVAL, "group must divide K and be a multiple of 32");
+    if (N == 0) return 0;
+    FLH_REQUIRE(B && rowsum, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE((reinterpret_cast<uintptr_t>(B) & 3) == 0, FLH_B200_EALIGN, "B must be 4-byte aligned");
+    return launch_weight_rowsum(B, N, K, group, rowsum, static_cast<cudaStream_t>(stream));
+}
+
+int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group) {
+    (void)N; (void)K; (void)a_group; (void)b_group;
+    if (M <= 32) return FLH_B200_GEMM_STREAM;
+    return FLH_B200_GEMM_TCGEN05;
+}
+
+size_t flh_b200_gemm_workspace_bytes(long M, long N, long K, long a_group, long b_group, int algo) {
+    (void)M; (void)N; (void)K; (void)a_group; (void)b_group; (void)algo;
+    return 0;
+}
+
+int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_scale, const void *a_zero,
+                             const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D,
+                             long M, long N, long K, long a_group, long b_group, int out_dtype, int algo,
+                             void *workspace, size_t workspace_bytes, void *stream) {
+    (void)workspace; (void)workspace_bytes;
+    FLH_REQUIRE(M >= 0 && N >= 0 && K > 0, FLH_B200_EINVAL, "bad shape M=%ld N=%ld K=%ld", M, N, K);
+    FLH_REQUIRE(K % 128 == 0 && K <= 65536, FLH_B200_EINVAL, "K must be a multiple of 128 and <= 65536 (got %ld)", K);
+    FLH_REQUIRE(N % 128 == 0, FLH_B200_EINVAL, "N must be a multiple of 128 (got %ld)", N);
+    FLH_REQUIRE(a_group == 128 || a_group == K, FLH_B200_EINVAL, "a_group must be 128 or K (got %ld)", a_group);
+    FLH_REQUIRE(b_group == 128 || b_group == K, FLH_B200_EINVAL, "b_group must be 128 or K (got %ld)", b_group);
+    FLH_REQUIRE(out_dtype == FLH_B200_F16 || out_dtype == FLH_B200_BF16, FLH_B200_EINVAL, "out_dtype must be F16 or BF16");
+    if (M == 0 || N == 0) return 0;
+    FLH_REQUIRE(A && B && a_scale && b_scale && D, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(!a_zero || b_rowsum, FLH_B200_EINVAL, "a_zero needs b_rowsum");
+    FLH_REQUIRE(aligned16(A) && aligned16(B), FLH_B200_EALIGN, "A and B must be 16-byte aligned");
+    FLH_REQUIRE((reinterpret_cast<uintptr_t>(D) & 15) == 0, FLH_B200_EALIGN, "D must be 16-byte aligned");
+    if (algo == FLH_B200_GEMM_AUTO) algo = flh_b200_gemm_pick_algo(M, N, K, a_group, b_group);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (algo) {
+        case FLH_B200_GEMM_STREAM:
+            FLH_REQUIRE(M <= 32, FLH_B200_EINVAL, "the streaming kernel serves M <= 32 (got %ld)", M);
+            return launch_gemm_stream(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, s);
+        case FLH_B200_GEMM_MMA_SYNC:
+            return launch_gemm_mma_tile(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, s);
+        case FLH_B200_GEMM_TCGEN05:
+            return launch_gemm_tcgen05(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, s);
+        default:
+            return fail(FLH_B200_EINVAL, "unknown algo %d", algo);
+    }
+}
+
+int flh_b200_gemm_status(int *out) {
+    FLH_REQUIRE(out, FLH_B200_EINVAL, "null pointer");
+    int rc = gemm_tcgen05_status(out);
+    if (rc) return rc;
+    return out[0] ? gemm_tcgen05_status_clear() : 0;
+}
+
+void flhDenseLayerGEMM_i4_o16(const uint8_t *A, const uint8_t *B, const void *A_scale, const void *B_scale,
+                              void *D, size_t M, size_t N, size_t K) {
+    (void)flh_b200_gemm_i4_dequant(A, B, A_scale, nullptr, B_scale, nullptr, nullptr, D, (long)M, (long)N,
+                                   (long)K, 128, 128, FLH_B200_F16, FLH_B200_GEMM_AUTO, nullptr, 0, nullptr);
+}
+
+}  // extern "C"

@@ -1,0 +1,459 @@
+// int4 x int4 GEMM with fused dequantisation on the 5th-generation tensor cores.
+//
+//   TMA (cp.async.bulk.tensor.2d)  packed int4 tiles of A [128 x 64 B] and B [BN x 64 B] -> smem ring
+//   4 converter warps              nibbles -> int8 (x16, see below) written in the K-major
+//                                  128-byte-swizzled layout tcgen05 reads, fence.proxy.async
+//   1 elected thread               tcgen05.mma.cta_group::1.kind::i8, int32 accumulators in TMEM
+//   4 epilogue warps               tcgen05.ld, dequantise (per 128-K group or once), f16/bf16 store
+//
+// There is no int4 MMA kind on sm_100, so the expansion to int8 happens in shared memory.  It is
+// exact and needs no sign extension: (w << 4) & 0xF0F0F0F0 and w & 0xF0F0F0F0 leave each nibble in
+// the high half of a byte, i.e. the int8 value 16 * q.  Both operands are expanded by the same rule
+// (even elements of a packed word first, then the odd ones), so products pair up correctly and the
+// int32 dot product is 256 * sum(qa * qw) — shifted back (or folded into the scale) exactly.
+//
+// Group-128 scales: the accumulator of every 128-K block goes to one of two TMEM buffers; the
+// epilogue warps drain buffer g while the MMA thread fills buffer g+1, and keep one binary32
+// accumulator per output column in registers:  acc = fmaf(float(I_g), sa * sb, acc), g ascending.
+//
+// Every wait on an mbarrier is bounded (two seconds); a wait that runs out records where in a
+// device status word, and the CTA drains its copies, frees its TMEM and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace flh {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 128;                 // int8 elements per stage = one 128-byte swizzle row
+constexpr int kConvWarp0 = 2, kEpiWarp0 = 6, kThreads = 320;
+
+__device__ int g_status[4];             // [0] = first error code, [1] = block, [2] = kb
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t gtimer() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false when two seconds pass or another thread of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const uint64_t t0 = gtimer();
+    for (int it = 0;; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 63) == 63) {
+            if (*abort_flag) return false;
+            if (gtimer() - t0 > 2000000000ull) {
+                *abort_flag = code;
+                if (atomicCAS(&g_status[0], 0, code) == 0) g_status[1] = blockIdx.x + 65536 * blockIdx.y;
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// K-major, 128-byte swizzle: 8-row groups 1024 B apart (SBO), LBO unused (1), descriptor version 1.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+struct TcParams {
+    const __half *a_scale, *a_zero, *b_scale, *bias;
+    const int32_t *b_rowsum;
+    void *D;
+    int M, N, K;
+    int ga_cols, gb_cols;
+    int out_bf16;
+};
+
+template <int BN>
+struct SmemPlan {
+    static constexpr int kStages = BN == 256 ? 3 : 4;
+    static constexpr int kExpStage = (BM + BN) * BK;          // int8 bytes
+    static constexpr int kPkStage = (BM + BN) * (BK / 2);     // packed bytes
+    static constexpr int kExpOff = 0;
+    static constexpr int kPkOff = kStages * kExpStage;
+    static constexpr int kAuxOff = kPkOff + kStages * kPkStage;   // sb/rs/bias staging: 4 x BN x 4 B
+    static constexpr int kBarOff = kAuxOff + 4 * BN * 4;
+    static constexpr int kBytes = kBarOff + 256 + 1024;           // + slack to align the base to 1024
+};
+
+__device__ __forceinline__ void store_row_chunk(void *D, bool bf16, long off, const float (&v)[32]) {
+    if (bf16) {
+        __nv_bfloat16 *d = static_cast<__nv_bfloat16 *>(D) + off;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+            o.x = *reinterpret_cast<uint32_t *>(&h0); o.y = *reinterpret_cast<uint32_t *>(&h1);
+            o.z = *reinterpret_cast<uint32_t *>(&h2); o.w = *reinterpret_cast<uint32_t *>(&h3);
+            *reinterpret_cast<uint4 *>(d + 8 * j) = o;
+        }
+    } else {
+        __half *d = static_cast<__half *>(D) + off;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            __half2 h0 = __floats2half2_rn(v[8 * j], v[8 * j + 1]), h1 = __floats2half2_rn(v[8 * j + 2], v[8 * j + 3]);
+            __half2 h2 = __floats2half2_rn(v[8 * j + 4], v[8 * j + 5]), h3 = __floats2half2_rn(v[8 * j + 6], v[8 * j + 7]);
+            o.x = *reinterpret_cast<uint32_t *>(&h0); o.y = *reinterpret_cast<uint32_t *>(&h1);
+            o.z = *reinterpret_cast<uint32_t *>(&h2); o.w = *reinterpret_cast<uint32_t *>(&h3);
+            *reinterpret_cast<uint4 *>(d + 8 * j) = o;
+        }
+    }
+}
+
+template <int BN, bool GROUPED, bool A_UNSIGNED>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const TcParams p) {
+    using Plan = SmemPlan<BN>;
+    constexpr int S = Plan::kStages;
+    extern __shared__ uint8_t smem_dyn[];
+    const uint32_t raw = smem_u32(smem_dyn);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *sm = smem_dyn + (base - raw);
+
+    const uint32_t bars = base + Plan::kBarOff;
+    auto pk_full = [&](int s) { return bars + 8u * s; };
+    auto pk_empty = [&](int s) { return bars + 8u * (4 + s); };
+    auto ex_full = [&](int s) { return bars + 8u * (8 + s); };
+    auto ex_empty = [&](int s) { return bars + 8u * (12 + s); };
+    auto acc_full = [&](int b) { return bars + 8u * (16 + b); };
+    auto acc_empty = [&](int b) { return bars + 8u * (18 + b); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + Plan::kBarOff + 8 * 20);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(sm + Plan::kBarOff + 8 * 20 + 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int KB = p.K / BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(pk_full(s), 1);
+            mbar_init(pk_empty(s), 128);
+            mbar_init(ex_full(s), 128);
+            mbar_init(ex_empty(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 128); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < KB; ++kb) {
+                const int s = kb % S;
+                if (!mbar_wait(pk_empty(s), ((kb / S) & 1) ^ 1, abort_flag, 1)) break;
+                mbar_expect_tx(pk_full(s), Plan::kPkStage);
+                const uint32_t dst = base + Plan::kPkOff + s * Plan::kPkStage;
+                tma_load_2d(dst, &map_a, kb * (BK / 2), m0, pk_full(s));
+                tma_load_2d(dst + BM * (BK / 2), &map_b, kb * (BK / 2), n0, pk_full(s));
+                issued = kb + 1;
+            }
+            if (*abort_flag) {
+                // let the copies already issued land before the CTA leaves
+                for (int kb = issued > S ? issued - S : 0; kb < issued; ++kb) {
+                    const uint64_t t0 = gtimer();
+                    while (!mbar_try(pk_full(kb % S), (kb / S) & 1) && gtimer() - t0 < 100000000ull) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (2u << 4) | ((A_UNSIGNED ? 0u : 1u) << 7) | (1u << 10) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            for (int kb = 0; kb < KB; ++kb) {
+                const int s = kb % S;
+                const int buf = GROUPED ? (kb & 1) : 0;
+                if (GROUPED && kb >= 2) {
+                    if (!mbar_wait(acc_empty(buf), ((kb >> 1) & 1) ^ 1, abort_flag, 2)) break;
+                }
+                if (!mbar_wait(ex_full(s), (kb / S) & 1, abort_flag, 3)) break;
+                tc_fence_after();
+                const uint32_t a_addr = base + Plan::kExpOff + s * Plan::kExpStage;
+                const uint64_t adesc = make_smem_desc(a_addr), bdesc = make_smem_desc(a_addr + BM * BK);
+#pragma unroll
+                for (int k4 = 0; k4 < BK / 32; ++k4) {
+                    const uint32_t accum = GROUPED ? (k4 > 0) : (kb > 0 || k4 > 0);
+                    tc_mma_i8(tmem + buf * BN, adesc + 2 * k4, bdesc + 2 * k4, idesc, accum);
+                }
+                tc_commit(ex_empty(s));
+                if (GROUPED || kb == KB - 1) tc_commit(acc_full(buf));
+            }
+        }
+    } else if (warp < kEpiWarp0) {
+        // ------------------------------------------------------------ int4 -> int8 converters
+        const int ct = tid - kConvWarp0 * 32;          // 0..127
+        for (int kb = 0; kb < KB; ++kb) {
+            const int s = kb % S;
+            if (!mbar_wait(pk_full(s), (kb / S) & 1, abort_flag, 4)) break;
+            if (!mbar_wait(ex_empty(s), ((kb / S) & 1) ^ 1, abort_flag, 5)) break;
+            const uint8_t *pk = sm + Plan::kPkOff + s * Plan::kPkStage;
+            uint8_t *ex = sm + Plan::kExpOff + s * Plan::kExpStage;
+            constexpr int kChunks = (BM + BN) * 4;
+#pragma unroll 4
+            for (int ch = ct; ch < kChunks; ch += 128) {
+                const int row = ch >> 2, c = ch & 3;     // row over A rows then B rows
+                const uint4 w = *reinterpret_cast<const uint4 *>(pk + row * 64 + c * 16);
+                uint4 e, o;
+                e.x = (w.x << 4) & 0xF0F0F0F0u; e.y = (w.y << 4) & 0xF0F0F0F0u;
+                e.z = (w.z << 4) & 0xF0F0F0F0u; e.w = (w.w << 4) & 0xF0F0F0F0u;
+                o.x = w.x & 0xF0F0F0F0u; o.y = w.y & 0xF0F0F0F0u; o.z = w.z & 0xF0F0F0F0u; o.w = w.w & 0xF0F0F0F0u;
+                uint8_t *dst = ex + row * 128;           // the B tile follows the A tile: (row - BM) * 128 + BM * 128
+                const int sw = row & 7;
+                *reinterpret_cast<uint4 *>(dst + (((2 * c) ^ sw) << 4)) = e;
+                *reinterpret_cast<uint4 *>(dst + (((2 * c + 1) ^ sw) << 4)) = o;
+            }
+            fence_proxy_async();
+            mbar_arrive(ex_full(s));
+            mbar_arrive(pk_empty(s));
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int et = tid - kEpiWarp0 * 32;            // 0..127
+        const int wq = warp & 3;                         // TMEM lane quarter this warp may read
+        const int row = m0 + wq * 32 + lane;
+        const int rowc = row < p.M ? row : p.M - 1;
+        float *sbuf = reinterpret_cast<float *>(sm + Plan::kAuxOff);        // [2][BN] weight scales
+        int *rbuf = reinterpret_cast<int *>(sm + Plan::kAuxOff + 2 * BN * 4); // [2][BN] weight row sums
+        const bool has_zero = p.a_zero != nullptr;
+        const uint32_t tlane = tmem + ((uint32_t)(wq * 32) << 16);
+
+        if (GROUPED) {
+            const int G = KB;
+            float acc[BN];
+#pragma unroll
+            for (int i = 0; i < BN; ++i) acc[i] = 0.0f;
+            const int gbs = p.gb_cols == 1 ? 0 : 1, gas = p.ga_cols == 1 ? 0 : 1;
+            for (int c = et; c < BN; c += 128) {
+                sbuf[c] = __half2float(p.b_scale[(long)(n0 + c) * p.gb_cols]);
+                rbuf[c] = has_zero ? p.b_rowsum[(long)(n0 + c) * G] : 0;
+            }
+            bar_sync_named(1, 128);
+            bool ok = true;
+            for (int kb = 0; kb < KB && ok; ++kb) {
+                const int buf = kb & 1;
+                // prefetch the next group's column data (BN == 128: one column per thread)
+                float nsb = 0.f; int nrs = 0;
+                if (kb + 1 < KB) {
+                    nsb = __half2float(p.b_scale[(long)(n0 + et) * p.gb_cols + gbs * (kb + 1)]);
+                    if (has_zero) nrs = p.b_rowsum[(long)(n0 + et) * G + kb + 1];
+                }
+                const float sa = __half2float(p.a_scale[(long)rowc * p.ga_cols + gas * kb]) * (1.0f / 256.0f);
+                const int za = has_zero ? (int)__half2float(p.a_zero[(long)rowc * p.ga_cols + gas * kb]) : 0;
+                ok = mbar_wait(acc_full(buf), (kb >> 1) & 1, abort_flag, 6);
+                if (!ok) break;
+                tc_fence_after();
+                const float *sb = sbuf + buf * BN;
+                const int *rs = rbuf + buf * BN;
+#pragma unroll
+                for (int cc = 0; cc < BN / 32; ++cc) {
+                    uint32_t v[32];
+                    tc_ld32(tlane + buf * BN + cc * 32, v);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = cc * 32 + j;
+                        // v = 256 * sum; the zero-point term is scaled alike so the difference stays exact
+                        const int I = (int)v[j] - ((za * rs[col]) << 8);
+                        acc[col] = __fmaf_rn((float)I, __fmul_rn(sa, sb[col]), acc[col]);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(acc_empty(buf));
+                if (kb + 1 < KB) { sbuf[(buf ^ 1) * BN + et] = nsb; rbuf[(buf ^ 1) * BN + et] = nrs; }
+                bar_sync_named(1, 128);
+            }
+            if (ok && row < p.M) {
+#pragma unroll
+                for (int cc = 0; cc < BN / 32; ++cc) {
+                    float o[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        o[j] = acc[cc * 32 + j];
+                        if (p.bias) o[j] = __fadd_rn(o[j], __half2float(p.bias[n0 + cc * 32 + j]));
+                    }
+                    store_row_chunk(p.D, p.out_bf16, (long)row * p.N + n0 + cc * 32, o);
+                }
+            }
+        } else {
+            float *bbuf = reinterpret_cast<float *>(sm + Plan::kAuxOff + 3 * BN * 4);
+            for (int c = et; c < BN; c += 128) {
+                sbuf[c] = __half2float(p.b_scale[n0 + c]);
+                rbuf[c] = has_zero ? p.b_rowsum[n0 + c] : 0;
+                bbuf[c] = p.bias ? __half2float(p.bias[n0 + c]) : 0.0f;
+            }
+            bar_sync_named(1, 128);
+            const float sa = __half2float(p.a_scale[rowc]) * (1.0f / 256.0f);
+            const int za = has_zero ? (int)__half2float(p.a_zero[rowc]) : 0;
+            if (mbar_wait(acc_full(0), 0, abort_flag, 7)) {
+                tc_fence_after();
+#pragma unroll 1
+                for (int cc = 0; cc < BN / 32; ++cc) {
+                    uint32_t v[32];
+                    tc_ld32(tlane + cc * 32, v);
+                    tc_wait_ld();
+                    float o[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = cc * 32 + j;
+                        const int I = (int)v[j] - ((za * rbuf[col]) << 8);
+                        float r = __fmaf_rn((float)I, __fmul_rn(sa, sbuf[col]), 0.0f);
+                        if (p.bias) r = __fadd_rn(r, bbuf[col]);
+                        o[j] = r;
+                    }
+                    if (row < p.M) store_row_chunk(p.D, p.out_bf16, (long)row * p.N + n0 + cc * 32, o);
+                }
+                tc_fence_before();
+            }
+        }
+    }
+
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// rows x (K/2) bytes, row-major; box = box_rows x 64 bytes, no swizzle, out-of-range rows read as 0.
+int make_map(CUtensorMap *map, const uint8_t *ptr, long rows, long K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(FLH_B200_EUNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(K / 2)};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FLH_B200_EINVAL, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return 0;
+}
+
+template <int BN, bool GROUPED, bool U>
+int launch_t(const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &p, cudaStream_t stream) {
+    auto kern = gemm_tcgen05_kernel<BN, GROUPED, U>;
+    const int smem = SmemPlan<BN>::kBytes;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_status(e, "gemm_tcgen05 attribute");
+    dim3 grid((unsigned)(p.N / BN), (unsigned)((p.M + BM - 1) / BM));
+    kern<<<grid, kThreads, smem, stream>>>(ma, mb, p);
+    return cuda_status(cudaGetLastError(), "gemm_tcgen05 launch");
+}
+
+}  // namespace
+
+int launch_gemm_tcgen05(const uint8_t *A, const uint8_t *B, const void *a_scale, const void *a_zero,
+                        const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D, long M,
+                        long N, long K, long a_group, long b_group, int out_dtype, cudaStream_t stream) {
+    TcParams p;
+    p.a_scale = static_cast<const __half *>(a_scale);
+    p.a_zero = static_cast<const __half *>(a_zero);
+    p.b_scale = static_cast<const __half *>(b_scale);
+    p.bias = static_cast<const __half *>(bias);
+    p.b_rowsum = b_rowsum; p.D = D;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.ga_cols = (int)(K / a_group); p.gb_cols = (int)(K / b_group);
+    p.out_bf16 = out_dtype == FLH_B200_BF16;
+    const bool grouped = a_group < K || b_group < K;
+    const int bn = (!grouped && N % 256 == 0) ? 256 : 128;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, M, K, BM);
+    if (rc) return rc;
+    rc = make_map(&mb, B, N, K, bn);
+    if (rc) return rc;
+    const bool u = a_zero != nullptr;
+    if (grouped) return u ? launch_t<128, true, true>(ma, mb, p, stream) : launch_t<128, true, false>(ma, mb, p, stream);
+    if (bn == 256) return u ? launch_t<256, false, true>(ma, mb, p, stream) : launch_t<256, false, false>(ma, mb, p, stream);
+    return u ? launch_t<128, false, true>(ma, mb, p, stream) : launch_t<128, false, false>(ma, mb, p, stream);
+}
+
+// Host-side read of the device status word the bounded waits write (synchronises the device).
+int gemm_tcgen05_status(int *out4) {
+    cudaError_t e = cudaMemcpyFromSymbol(out4, g_status, sizeof(int) * 4);
+    return cuda_status(e, "status read");
+}
+int gemm_tcgen05_status_clear() {
+    int z[4] = {0, 0, 0, 0};
+    return cuda_status(cudaMemcpyToSymbol(g_status, z, sizeof(z)), "status clear");
+}
+
+}  // namespace flh

@@ -1,0 +1,189 @@
+// Group-wise (32/64/128) binary16 Walsh-Hadamard transform, fused symmetric int4 quantiser and
+// nibble packing — the flh._CUDA activation path (hadamard_and_quantize_i4, quant_and_pack_i4,
+// hadamard_transform_half and their group-size variants).
+//
+// Memory-bound: 2 B in, 0.5 B + 2/gs B out per element.  One thread owns 8 consecutive halves
+// (one 128-bit load), so a group of gs spans gs/8 adjacent lanes: butterfly bits 0-2 are done in
+// registers on half2 pairs, the remaining log2(gs)-3 bits with __shfl_xor, always in ascending bit
+// order so that every binary16 rounding happens where the reference kernel has it
+// (flh/kernels/had_and_quant.cu:13-56).  Each thread keeps U independent 16-byte loads in flight.
+#include "common.cuh"
+
+namespace flh {
+
+namespace {
+
+constexpr int kUnroll = 4;
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ __half2 u2h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+__device__ __forceinline__ uint32_t h22u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+
+// (a, b) -> (a + b, a - b), one rounding each (the product with +-1 is exact).
+__device__ __forceinline__ __half2 bfly_inner(__half2 v) {
+    const __half2 sgn = __halves2half2(__float2half(1.0f), __float2half(-1.0f));
+    return __hfma2(__high2half2(v), sgn, __low2half2(v));
+}
+
+template <int LOG_GS>
+__device__ __forceinline__ void fht_regs(__half2 (&h)[4], int lane_in_group) {
+    // bits 0..2: in registers
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = bfly_inner(h[j]);
+    {
+        __half2 a = h[0], b = h[1], c = h[2], d = h[3];
+        h[0] = __hadd2(a, b); h[1] = __hsub2(a, b);
+        h[2] = __hadd2(c, d); h[3] = __hsub2(c, d);
+    }
+    {
+        __half2 a = h[0], b = h[1], c = h[2], d = h[3];
+        h[0] = __hadd2(a, c); h[2] = __hsub2(a, c);
+        h[1] = __hadd2(b, d); h[3] = __hsub2(b, d);
+    }
+    // bits 3..LOG_GS-1: across lanes; the lane whose bit is set holds the upper element and
+    // receives other - mine, the other lane mine + other.
+#pragma unroll
+    for (int s = 0; s < LOG_GS - 3; ++s) {
+        const int mask = 1 << s;
+        const float sg = (lane_in_group & mask) ? -1.0f : 1.0f;
+        const __half2 sgn = __float2half2_rn(sg);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __half2 other = u2h2(__shfl_xor_sync(0xffffffffu, h22u(h[j]), mask));
+            h[j] = __hfma2(h[j], sgn, other);
+        }
+    }
+}
+
+template <int LOG_GS, bool HADAMARD>
+__global__ void __launch_bounds__(kThreads)
+quant_group_sym_kernel(const uint4 *__restrict__ x, uint32_t *__restrict__ q,
+                       __half *__restrict__ scales, long total_chunks) {
+    constexpr int L = (1 << LOG_GS) / 8;          // lanes per group
+    const long nthreads = (long)gridDim.x * kThreads;
+    const long tid = (long)blockIdx.x * kThreads + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int lig = lane & (L - 1);
+
+    for (long c0 = tid; c0 - lane < total_chunks; c0 += nthreads * kUnroll) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const long c = c0 + u * nthreads;
+            v[u] = (c < total_chunks) ? ldg_nc_v4(x + c) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const long c = c0 + u * nthreads;
+            if (c - lane >= total_chunks) break;   // warp-uniform
+            __half2 h[4] = {u2h2(v[u].x), u2h2(v[u].y), u2h2(v[u].z), u2h2(v[u].w)};
+            if (HADAMARD) fht_regs<LOG_GS>(h, lig);
+
+            // max |x| over the group, in binary16
+            __half2 m2 = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])),
+                                 __hmax2(__habs2(h[2]), __habs2(h[3])));
+            __half m = __hmax(__low2half(m2), __high2half(m2));
+#pragma unroll
+            for (int s = 1; s < L; s <<= 1) {
+                const unsigned short o = __shfl_xor_sync(0xffffffffu, __half_as_ushort(m), s);
+                m = __hmax(m, __ushort_as_half(o));
+            }
+            // scale = __hdiv(max, 7) with a correctly rounded reciprocal (cuda_fp16.hpp __hdiv,
+            // device branch: reciprocal, multiply, round, one correction for tiny results)
+            const float fm = __half2float(m);
+            const float rcp7 = 1.0f / 7.0f;
+            float fv = __fmul_rn(rcp7, fm);
+            __half sh = __float2half_rn(fv);
+            {
+                const unsigned short a = __half_as_ushort(sh) & 0x7fffu;
+                if (a != 0 && a < 0x008Fu) {
+                    const float err = __fmaf_rn(-7.0f, fv, fm);
+                    fv = __fmaf_rn(rcp7, err, fv);
+                    sh = __float2half_rn(fv);
+                }
+            }
+            if (__half2float(sh) <= __half2float(__float2half_rn(1e-6f))) sh = __float2half_rn(1.0f);
+            const float rcp = __frcp_rn(__half2float(sh));
+
+            // q = clamp(rint(half(x * rcp)), -8, 7); adding 1032 (= 1024 + 8) in binary16 rounds
+            // to the nearest integer, ties to even, and leaves q + 8 in the low four bits.
+            const __half2 lo = __float2half2_rn(-8.0f), hi = __float2half2_rn(7.0f);
+            const __half2 magic = __float2half2_rn(1032.0f);
+            uint32_t packed = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                __half2 t = __floats2half2_rn(__fmul_rn(f.x, rcp), __fmul_rn(f.y, rcp));
+                t = __hmax2(__hmin2(t, hi), lo);
+                const uint32_t w = (h22u(__hadd2(t, magic)) & 0x000F000Fu) ^ 0x00080008u;
+                packed |= ((w | (w >> 12)) & 0xFFu) << (8 * j);
+            }
+            if (c < total_chunks) {
+                q[c] = packed;
+                if (lig == 0) scales[c / L] = sh;
+            }
+        }
+    }
+}
+
+template <int LOG_GS>
+__global__ void __launch_bounds__(kThreads)
+fht_inplace_kernel(uint4 *__restrict__ x, long total_chunks) {
+    constexpr int L = (1 << LOG_GS) / 8;
+    const long nthreads = (long)gridDim.x * kThreads;
+    const long tid = (long)blockIdx.x * kThreads + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int lig = lane & (L - 1);
+    for (long c0 = tid; c0 - lane < total_chunks; c0 += nthreads * kUnroll) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const long c = c0 + u * nthreads;
+            v[u] = (c < total_chunks) ? x[c] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const long c = c0 + u * nthreads;
+            if (c - lane >= total_chunks) break;
+            __half2 h[4] = {u2h2(v[u].x), u2h2(v[u].y), u2h2(v[u].z), u2h2(v[u].w)};
+            fht_regs<LOG_GS>(h, lig);
+            if (c < total_chunks) x[c] = make_uint4(h22u(h[0]), h22u(h[1]), h22u(h[2]), h22u(h[3]));
+        }
+    }
+}
+
+inline int grid_for(long total_chunks) {
+    long blocks = (total_chunks + kThreads - 1) / kThreads;
+    const long cap = (long)kNumSMs * 8;            // 8 resident CTAs of 256 threads per SM
+    if (blocks > cap) blocks = cap;
+    return (int)(blocks < 1 ? 1 : blocks);
+}
+
+}  // namespace
+
+int launch_quant_group_sym(const void *x, long rows, int gs, int hadamard, uint8_t *q,
+                           void *scales, cudaStream_t stream) {
+    const long chunks = rows * (gs / 8);
+    const int grid = grid_for(chunks);
+    const uint4 *xi = static_cast<const uint4 *>(x);
+    uint32_t *qo = reinterpret_cast<uint32_t *>(q);
+    __half *so = static_cast<__half *>(scales);
+#define FLH_LAUNCH(LG, H) quant_group_sym_kernel<LG, H><<<grid, kThreads, 0, stream>>>(xi, qo, so, chunks)
+    if (gs == 128) { if (hadamard) FLH_LAUNCH(7, true); else FLH_LAUNCH(7, false); }
+    else if (gs == 64) { if (hadamard) FLH_LAUNCH(6, true); else FLH_LAUNCH(6, false); }
+    else { if (hadamard) FLH_LAUNCH(5, true); else FLH_LAUNCH(5, false); }
+#undef FLH_LAUNCH
+    return cuda_status(cudaGetLastError(), "quant_group_sym launch");
+}
+
+int launch_fht_inplace(void *x, long rows, int n, cudaStream_t stream) {
+    const long chunks = rows * (n / 8);
+    const int grid = grid_for(chunks);
+    uint4 *xi = static_cast<uint4 *>(x);
+    if (n == 128) fht_inplace_kernel<7><<<grid, kThreads, 0, stream>>>(xi, chunks);
+    else if (n == 64) fht_inplace_kernel<6><<<grid, kThreads, 0, stream>>>(xi, chunks);
+    else fht_inplace_kernel<5><<<grid, kThreads, 0, stream>>>(xi, chunks);
+    return cuda_status(cudaGetLastError(), "fht_inplace launch");
+}
+
+}  // namespace flh

@@ -1,0 +1,388 @@
+// Full-width online Hadamard (binary32, matmul_hadU's order) fused with the per-token asymmetric
+// int4 quantiser and nibble packing.
+//
+// One CTA per token row, T = K/64 threads, every thread owns 64 values in registers at each step:
+//   pass 1  butterfly bits 0-5 on 64 consecutive inputs (eight 128-bit loads per thread);
+//   pass 2  bits 6..6+B2-1 after one transpose through padded shared memory;
+//   pass 3  bits 12..12+B3-1 (K > 4096 only) after a second transpose;
+//   factor  the kfac x kfac +-1 matrix across the K/kfac-long chunks (K = 11008, 14336, 28672 ...),
+//           accumulated k' ascending in binary32, signs kept as bit rows in shared memory;
+//   quant   row min/max -> scale (f16), zero-point, codes from the registers, staged as bytes in
+//           shared memory only to be packed two per byte and stored with 64-bit writes.
+// All butterflies run on packed binary32 pairs (add.rn.f32x2 / fma.rn.f32x2), so every result is
+// the IEEE sum or difference of its two inputs, in ascending bit order: bit-exact with the oracle.
+// Shared memory is used only for the transposes between register passes.
+#include "common.cuh"
+
+namespace flh {
+namespace {
+
+// ---- 64 registers, butterfly over the low NST bits of the register index --------------------
+template <int NST>
+__device__ __forceinline__ void bfly_regs(float (&x)[64]) {
+    if (NST >= 1) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            const float a = x[2 * k], b = x[2 * k + 1];
+            x[2 * k] = __fadd_rn(a, b);
+            x[2 * k + 1] = __fsub_rn(a, b);
+        }
+    }
+    if (NST >= 2) {
+        uint64_t p[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) p[k] = pack2(x[2 * k], x[2 * k + 1]);
+#pragma unroll
+        for (int s = 1; s < NST; ++s) {
+            const int h = 1 << (s - 1);
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+                if ((k & h) == 0) {
+                    const uint64_t a = p[k], b = p[k + h];
+                    p[k] = add2(a, b);
+                    p[k + h] = sub2(a, b);
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 32; ++k) unpack2(p[k], x[2 * k], x[2 * k + 1]);
+    }
+}
+
+// Shared-memory position of element e (0..63) of 64-chunk `chunk`: 68 words per chunk keeps the
+// 128-bit stores of pass 1 conflict-free; for B2 < 5 one more word per chunk (two for B2 = 1),
+// granted in blocks of 2^B2 chunks, spreads the 2^B2-strided reads of pass 2 over the banks.
+// A row never needs more than 70 words per chunk.
+template <int B2>
+__device__ __forceinline__ int phys(int chunk, int e) {
+    if (B2 == 1) return 68 * chunk + ((chunk >> 1) << 2) + e;      // keeps 16-byte alignment
+    if (B2 > 1 && B2 < 5) return 68 * chunk + ((chunk >> B2) << B2) + e;
+    return 68 * chunk + e;
+}
+
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, s));
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
+    return v;
+}
+
+struct TokenParams {
+    const void *x;
+    long ld;
+    int bf16;
+    int n;         // K
+    int T;         // n / 64 working threads
+    int kfac;
+    int P;         // n / kfac
+    const uint32_t *sign_bits;
+    float clip;
+    float c;       // sqrtf(n) with the transform, 1 without
+    uint8_t *q;
+    __half *scale;
+    __half *zero;
+};
+
+// B2/B3: bits handled by passes 2/3.  FACTOR: kfac > 1.  HAD: transform at all.
+template <int B2, int B3, bool FACTOR, bool HAD>
+__global__ void __launch_bounds__(512)
+quant_token_asym_kernel(const TokenParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float *buf = reinterpret_cast<float *>(smem_raw);
+    __shared__ float red[2][32];
+    __shared__ float bcast[2];
+
+    const int t = threadIdx.x;
+    const int lane = t & 31, warp = t >> 5;
+    const long row = blockIdx.x;
+    const bool active = t < p.T;
+    float x[64];
+
+    // ---------------- pass 1: load 64 consecutive inputs, bits 0-5 -------------------------
+    if (active) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(
+            static_cast<const uint16_t *>(p.x) + row * p.ld + 64l * t);
+        uint4 v[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) v[c] = ldg_v4(src + c);
+        if (p.bf16) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    x[8 * c + 2 * j] = __uint_as_float(w[j] << 16);
+                    x[8 * c + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
+                    x[8 * c + 2 * j] = f.x;
+                    x[8 * c + 2 * j + 1] = f.y;
+                }
+            }
+        }
+        if (HAD) bfly_regs<6>(x);
+    }
+
+    // element index of register idx once all passes are done: base + stride pattern below
+    // (computed per section); codes are staged at cb[element index].
+    int ebase = 64 * t;      // pass-1 layout: idx -> 64 t + idx
+
+    if (HAD && (B2 > 0 || FACTOR)) {
+        if (active) {
+#pragma unroll
+            for (int e = 0; e < 64; e += 4)
+                *reinterpret_cast<float4 *>(buf + phys<B2>(t, e)) = make_float4(x[e], x[e + 1], x[e + 2], x[e + 3]);
+        }
+        __syncthreads();
+    }
+
+    // ---------------- pass 2: bits 6 .. 6+B2-1 ---------------------------------------------
+    // register idx = r * 2^B2 + m  <->  element hi * 2^(6+B2) + m * 64 + r * 2^B2 + w
+    if (HAD && B2 > 0) {
+        constexpr int NM = 1 << B2;
+        const int w = t & (NM - 1), hi = t >> B2;
+        if (active) {
+#pragma unroll
+            for (int idx = 0; idx < 64; ++idx) {
+                const int m = idx & (NM - 1), r = idx >> B2;
+                x[idx] = buf[phys<B2>(hi * NM + m, r * NM + w)];
+            }
+            bfly_regs<B2>(x);
+        }
+        ebase = (hi << (6 + B2)) + w;
+        if (B3 > 0 || FACTOR) {
+            __syncthreads();   // everyone has read before anyone overwrites
+            if (active) {
+#pragma unroll
+                for (int idx = 0; idx < 64; ++idx) {
+                    const int m = idx & (NM - 1), r = idx >> B2;
+                    buf[phys<B2>(hi * NM + m, r * NM + w)] = x[idx];
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    // ---------------- pass 3: bits 12 .. 12+B3-1 (B2 == 6) ----------------------------------
+    // register idx = r * 2^B3 + m  <->  element hi * 2^(12+B3) + m * 4096 + r * 64 * 2^B3 + w
+    if (HAD && B3 > 0) {
+        constexpr int NM = 1 << B3;
+        const int w = t & (64 * NM - 1), hi = t >> (6 + B3);
+        if (active) {
+#pragma unroll
+            for (int idx = 0; idx < 64; ++idx) {
+                const int m = idx & (NM - 1), r = idx >> B3;
+                const int chunk = (hi << (6 + B3)) + m * 64 + r * NM + (w >> 6);
+                x[idx] = buf[phys<B2>(chunk, w & 63)];
+            }
+            bfly_regs<B3>(x);
+        }
+        ebase = (hi << (12 + B3)) + w;
+        if (FACTOR) {
+            __syncthreads();
+            if (active) {
+#pragma unroll
+                for (int idx = 0; idx < 64; ++idx) {
+                    const int m = idx & (NM - 1), r = idx >> B3;
+                    const int chunk = (hi << (6 + B3)) + m * 64 + r * NM + (w >> 6);
+                    buf[phys<B2>(chunk, w & 63)] = x[idx];
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    // ---------------- factor stage: y[k P + j] = sum_k' S[k][k'] in[k' P + j] ----------------
+    // thread <-> (kb, w): k = 4 kb + v (v < 4); j = 2 w + b + (P/8) u (b < 2, u < 8);
+    // register idx = v * 16 + 2 u + b.
+    int f_kb = 0, f_w = 0;
+    if (HAD && FACTOR) {
+        const int words = (p.kfac + 31) >> 5;
+        uint32_t *sgn = reinterpret_cast<uint32_t *>(buf + (p.T * 70 + 64));   // after the data area
+        for (int i = t; i < p.kfac * words; i += blockDim.x) sgn[i] = p.sign_bits[i];
+        __syncthreads();
+        const int Wd = p.P >> 4;
+        f_w = t % Wd;
+        f_kb = t / Wd;
+        if (active) {
+            uint64_t acc[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0ull;
+            const int jstep = p.P >> 3;
+            for (int kk0 = 0; kk0 < p.kfac; kk0 += 32) {
+                uint32_t sw[4];
+#pragma unroll
+                for (int v = 0; v < 4; ++v) sw[v] = sgn[(4 * f_kb + v) * words + (kk0 >> 5)];
+                const int kend = min(32, p.kfac - kk0);
+                for (int kb = 0; kb < kend; ++kb) {
+                    const int kk = kk0 + kb;
+                    uint64_t in[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int j = 2 * f_w + jstep * u;
+                        const int i = kk * p.P + j;
+                        in[u] = *reinterpret_cast<const uint64_t *>(buf + phys<B2>(i >> 6, i & 63));
+                    }
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const uint32_t s = 0x3f800000u | ((sw[v] >> kb) << 31);
+                        uint64_t s2;
+                        asm("mov.b64 %0, {%1, %1};" : "=l"(s2) : "r"(s));
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[v * 8 + u]) : "l"(s2), "l"(in[u]));
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) unpack2(acc[i], x[2 * i], x[2 * i + 1]);
+        }
+    }
+
+    // ---------------- row min / max ---------------------------------------------------------
+    float vmin = 0.0f, vmax = 0.0f;
+    if (active) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) { vmin = fminf(vmin, x[i]); vmax = fmaxf(vmax, x[i]); }
+    }
+    vmin = warp_min(vmin); vmax = warp_max(vmax);
+    if (lane == 0) { red[0][warp] = vmin; red[1][warp] = vmax; }
+    __syncthreads();            // also: all reads of buf are complete, cb may alias it
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        float a = lane < nw ? red[0][lane] : 0.0f;
+        float b = lane < nw ? red[1][lane] : 0.0f;
+        a = warp_min(a); b = warp_max(b);
+        if (lane == 0) { bcast[0] = a; bcast[1] = b; }
+    }
+    __syncthreads();
+    float zmin = __fmul_rn(bcast[0], p.clip), zmax = __fmul_rn(bcast[1], p.clip);
+    if (zmin == 0.0f && zmax == 0.0f) { zmin = -1.0f; zmax = 1.0f; }
+    float scale32 = __fdiv_rn(__fsub_rn(zmax, zmin), 15.0f);
+    scale32 = __fdiv_rn(scale32, p.c);
+    __half sh = __float2half_rn(scale32);
+    if ((__half_as_ushort(sh) & 0x7fffu) == 0) sh = __ushort_as_half(0x0001u);
+    const float d = __fmul_rn(p.c, __half2float(sh));
+    const float rd = __frcp_rn(d);
+    const float zf = rintf(__fmul_rn(-zmin, rd));
+    if (t == 0) { p.scale[row] = sh; p.zero[row] = __float2half_rn(zf); }
+
+    // codes: clamp(rint(z * rd), -zero, 15 - zero) + zero; adding 1.5 * 2^23 rounds to the
+    // nearest integer (ties to even) and leaves it in the low mantissa bits.
+    uint8_t *cb = smem_raw;
+    if (active) {
+        const float lo = -zf, hi = 15.0f - zf;
+        const float magic = 12582912.0f;
+        const int zi = (int)zf;
+#pragma unroll
+        for (int idx = 0; idx < 64; ++idx) {
+            float v = __fmul_rn(x[idx], rd);
+            v = fminf(fmaxf(v, lo), hi);
+            const int code = (__float_as_int(__fadd_rn(v, magic)) + zi) & 15;
+            int e;
+            if (HAD && FACTOR) {
+                const int v4 = idx >> 4, u = (idx >> 1) & 7, b = idx & 1;
+                e = (4 * f_kb + v4) * p.P + 2 * f_w + b + (p.P >> 3) * u;
+            } else if (HAD && B3 > 0) {
+                const int m = idx & ((1 << B3) - 1), r = idx >> B3;
+                e = ebase + m * 4096 + r * (64 << B3);
+            } else if (HAD && B2 > 0) {
+                const int m = idx & ((1 << B2) - 1), r = idx >> B2;
+                e = ebase + m * 64 + (r << B2);
+            } else {
+                e = ebase + idx;
+            }
+            cb[e] = (uint8_t)code;
+        }
+    }
+    __syncthreads();
+    // pack 16 staged codes into 8 bytes, coalesced 64-bit stores
+    uint2 *qrow = reinterpret_cast<uint2 *>(p.q + row * (long)(p.n >> 1));
+    for (int c = t; c < (p.n >> 4); c += blockDim.x) {
+        const uint4 cv = *reinterpret_cast<const uint4 *>(cb + 16 * c);
+        const uint32_t w[4] = {cv.x, cv.y, cv.z, cv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t tt = w[j] | (w[j] >> 4);
+            o[j] = (tt & 0xFFu) | ((tt >> 8) & 0xFF00u);
+        }
+        qrow[c] = make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16));
+    }
+}
+
+template <int B2, int B3, bool FACTOR, bool HAD>
+int launch_one(const TokenParams &p, long M, cudaStream_t stream) {
+    const int threads = ((p.T + 31) / 32) * 32;
+    size_t smem = (size_t)p.n;                                   // code staging
+    if (HAD && (B2 > 0 || FACTOR)) {
+        smem = ((size_t)p.T * 70 + 64) * 4;
+        if (FACTOR) smem += (size_t)p.kfac * ((p.kfac + 31) / 32) * 4;
+        if (smem < (size_t)p.n) smem = p.n;
+    }
+    auto kern = quant_token_asym_kernel<B2, B3, FACTOR, HAD>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_status(e, "quant_token smem attribute");
+    }
+    kern<<<(unsigned)M, threads, smem, stream>>>(p);
+    return cuda_status(cudaGetLastError(), "quant_token_asym launch");
+}
+
+}  // namespace
+
+int launch_quant_token_asym(const void *x, int in_dtype, long M, long K, long ld, int hadamard,
+                            int kfac, const uint32_t *sign_bits, float clip, uint8_t *q,
+                            void *scale, void *zero, cudaStream_t stream) {
+    TokenParams p;
+    p.x = x; p.ld = ld; p.bf16 = in_dtype == FLH_B200_BF16; p.n = (int)K; p.T = (int)(K / 64);
+    p.kfac = kfac; p.P = (int)(K / kfac); p.sign_bits = sign_bits; p.clip = clip;
+    p.c = hadamard ? sqrtf((float)K) : 1.0f;
+    p.q = q; p.scale = static_cast<__half *>(scale); p.zero = static_cast<__half *>(zero);
+    if (!hadamard) return launch_one<0, 0, false, false>(p, M, stream);
+    int logp = 0;
+    while ((1 << logp) < p.P) ++logp;
+    const int b2 = logp - 6 > 6 ? 6 : logp - 6;
+    const int b3 = logp - 12 > 0 ? logp - 12 : 0;
+    if (kfac > 1) {
+        switch (b2) {
+            case 0: return launch_one<0, 0, true, true>(p, M, stream);
+            case 1: return launch_one<1, 0, true, true>(p, M, stream);
+            case 2: return launch_one<2, 0, true, true>(p, M, stream);
+            case 3: return launch_one<3, 0, true, true>(p, M, stream);
+            case 4: return launch_one<4, 0, true, true>(p, M, stream);
+            case 5: return launch_one<5, 0, true, true>(p, M, stream);
+            default: return launch_one<6, 0, true, true>(p, M, stream);
+        }
+    }
+    if (b3 == 0) {
+        switch (b2) {
+            case 0: return launch_one<0, 0, false, true>(p, M, stream);
+            case 1: return launch_one<1, 0, false, true>(p, M, stream);
+            case 2: return launch_one<2, 0, false, true>(p, M, stream);
+            case 3: return launch_one<3, 0, false, true>(p, M, stream);
+            case 4: return launch_one<4, 0, false, true>(p, M, stream);
+            case 5: return launch_one<5, 0, false, true>(p, M, stream);
+            default: return launch_one<6, 0, false, true>(p, M, stream);
+        }
+    }
+    switch (b3) {
+        case 1: return launch_one<6, 1, false, true>(p, M, stream);
+        case 2: return launch_one<6, 2, false, true>(p, M, stream);
+        default: return launch_one<6, 3, false, true>(p, M, stream);
+    }
+}
+
+}  // namespace flh

@@ -1,0 +1,146 @@
+/*
+ * flh_b200 — C ABI of the B200 (sm_100a) implementation of FLH's W4A4 hot path:
+ * online Hadamard + int4 activation quantiser + int4 x int4 GEMM with fused
+ * dequantisation.
+ *
+ * Conventions (all entry points unless stated otherwise)
+ *   - plain pointers and sizes; every data pointer is a DEVICE pointer on the
+ *     current device; inputs are borrowed, outputs are caller-allocated;
+ *   - no entry point allocates, frees or synchronises; work is enqueued on
+ *     `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream);
+ *   - return value: 0 = ok, > 0 = rejected argument (FLH_B200_EINVAL...),
+ *     < 0 = minus the cudaError_t of a failed runtime call or launch;
+ *     flh_b200_last_error() returns a per-thread message for the last non-zero
+ *     return;
+ *   - "f16" is IEEE binary16, "bf16" bfloat16, both passed as void*;
+ *   - packed int4: byte j of a row holds element 2j in its low nibble and
+ *     element 2j+1 in its high nibble (pack_i4, flh/functional/quantization.py:42-49;
+ *     had_and_quant_kernel, flh/kernels/had_and_quant.cu:141-148).
+ *
+ * File:line citations name the FLH interface each entry point replaces; paths
+ * are relative to the FLH repository root.
+ */
+#ifndef FLH_B200_H
+#define FLH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FLH_B200_OK 0
+#define FLH_B200_EINVAL 1      /* bad size, mode or null pointer            */
+#define FLH_B200_EALIGN 2      /* pointer or stride not aligned as required */
+#define FLH_B200_EUNSUPPORTED 3 /* valid request this build cannot serve    */
+#define FLH_B200_EDEVICE 4     /* kernel reported a device-side error word  */
+
+#define FLH_B200_F16 0
+#define FLH_B200_BF16 1
+
+/* GEMM algorithm selector */
+#define FLH_B200_GEMM_AUTO 0
+#define FLH_B200_GEMM_TCGEN05 1 /* TMA + int4->int8 expand in smem + tcgen05.mma kind::i8, TMEM accumulators */
+#define FLH_B200_GEMM_MMA_SYNC 2 /* legacy mma.sync m16n8k32 s8 path (bring-up cross-check, any M)           */
+#define FLH_B200_GEMM_STREAM 3  /* weight-streaming small-M path (M <= 32)                                    */
+
+int flh_b200_version(void);
+const char *flh_b200_last_error(void);
+
+/* 0 when the current device is an sm_100 part this library was built for. */
+int flh_b200_device_check(void);
+
+/* ---- activation quantisers ------------------------------------------------------------- */
+
+/* Fused (optional) group Hadamard + symmetric int4 quantiser + packing.
+ * x [rows, gs] f16 contiguous, gs in {32, 64, 128}; q [rows, gs/2]; scales [rows] f16 (raw,
+ * un-normalised: the caller folds 1/sqrt(gs), as ActQuantizer.forward does,
+ * flh/nn/quantization.py:156-162).
+ * Replaces had_and_quant_host (flh/kernels/had_and_quant.h:19-24, kernel
+ * flh/kernels/had_and_quant.cu:61-155), quant_and_pack_host (flh/kernels/quant_and_pack.h:19-24)
+ * and their _gs forms (flh/kernels/had_and_quant_gs.h, quant_and_pack_gs.h); bound as
+ * hadamard_and_quantize_i4 / quant_and_pack_i4 (flh/cuda/flh_cuda_bindings.cpp:154-198). */
+int flh_b200_quant_group_sym_i4(const void *x, long rows, int gs, int hadamard,
+                                uint8_t *q, void *scales, void *stream);
+
+/* In-place un-normalised f16 Walsh-Hadamard transform of rows of n in {32, 64, 128}.
+ * Replaces had_trans_half_cuda / had_trans_64_half_cuda / had_trans_32_half_cuda
+ * (flh/kernels/cuda_had_kernel.cu:296-354 and the 64/32 copies), bound as
+ * hadamard_transform_half / _64_half / _32_half (flh/cuda/flh_cuda_bindings.cpp:115-152). */
+int flh_b200_hadamard_f16_inplace(void *x, long rows, int n, void *stream);
+
+/* (Optional full-width Hadamard +) per-token asymmetric int4 quantiser + packing.
+ * x [M, K] f16 or bf16 with row stride ld (elements, multiple of 8; x 16-byte aligned).
+ * hadamard = 0: quantise x itself.  hadamard = 1: quantise (hadK (x) H_p) x / sqrt(K) with
+ * K = kfac * p, p a power of two >= 64; kfac = 1 for a power-of-two K, otherwise one of the
+ * orders get_hadK knows (flh/functional/hadamard.py:39-89) with sign_bits = that matrix packed
+ * by flh_b200_pack_signs (device pointer).  The transform runs in binary32 in the order of
+ * matmul_hadU (flh/functional/hadamard.py:92-113); 1/sqrt(K) is folded into the scale.
+ * Quantiser: ActQuantizer.find_params / asym_quant (fake_quant/quant_utils.py:94-128, 17-21)
+ * with the scale rounded to f16 before use.  q [M, K/2] codes 0..15; scale, zero [M] f16.
+ * clip = the quantiser's clip_ratio in (0, 1]. */
+int flh_b200_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, long ld,
+                                 int hadamard, int kfac, const uint32_t *sign_bits, float clip,
+                                 uint8_t *q, void *scale, void *zero, void *stream);
+
+/* HOST helper: pack a kfac x kfac matrix of +1/-1 (int8, row-major, host memory) into the
+ * bit rows the kernel reads: out[k * words + w] bit b = 1 when signs[k][32 w + b] < 0,
+ * words = (kfac + 31) / 32.  out holds kfac * words uint32 (host memory). */
+int flh_b200_pack_signs(const int8_t *signs, int kfac, uint32_t *out);
+
+/* ---- weights ---------------------------------------------------------------------------- */
+
+/* rowsum[n, g] = sum of the signed int4 codes of weight row n over K-group g (int32,
+ * [N, K/group]); the zero-point term of the asymmetric epilogue needs it.  Offline, once per
+ * weight.  No counterpart in FLH (its GEMM has no zero-point, flh/nn/linear.py:125-133). */
+int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t *rowsum,
+                           void *stream);
+
+/* ---- GEMM ------------------------------------------------------------------------------- */
+
+/* D[M, N] = dequantising int4 x int4 GEMM.
+ *   A [M, K/2], B [N, K/2] packed int4 (B signed; A signed when a_zero == NULL, else unsigned);
+ *   a_scale [M, K/a_group] f16, a_group in {128, K};  a_zero NULL or f16 like a_scale (integer
+ *   values 0..15);  b_scale [N, K/b_group] f16, b_group in {128, K};
+ *   b_rowsum [N, K/min(a_group, b_group)] int32, required when a_zero != NULL;
+ *   bias NULL or [N] f16;  D f16 or bf16 (out_dtype).
+ *   With g running over K-groups of min(a_group, b_group) in ascending order:
+ *     I_g = sum_{k in g} qa[m,k] qw[n,k]  -  zero[m, ga] * rowsum[n, g]
+ *     acc = fmaf((float) I_g, sa[m, ga] * sb[n, gb], acc)        (binary32, acc starts at +0)
+ *     D[m, n] = round(acc + bias[n])
+ *   which with a_zero = NULL, a_group = b_group = 128, f16 output is the arithmetic of
+ *   flh_gemm_i4_dequant_o16_kernel (flh/kernels/gemm_and_dequant_i4.cu:287-313, 315-469).
+ *   N % 128 == 0 and K % 128 == 0 are required (as the reference kernel assumes), K <= 65536.
+ *   algo: FLH_B200_GEMM_*.  workspace: device scratch of at least
+ *   flh_b200_gemm_workspace_bytes(...) bytes (may be NULL when that is 0).
+ * Replaces flhDenseLayerGEMM_i4_o16 (flh/kernels/gemm_and_dequant_i4.cu:471-508) and
+ * flhDenseLayerGEMM_i4_o16_gs (flh/kernels/gemm_and_dequant_i4_gs.h); bound as
+ * gemm_i4_dequant_o16(_gs) (flh/cuda/flh_cuda_bindings.cpp:75-113, 253-299). */
+int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_scale,
+                             const void *a_zero, const void *b_scale, const int32_t *b_rowsum,
+                             const void *bias, void *D, long M, long N, long K, long a_group,
+                             long b_group, int out_dtype, int algo, void *workspace,
+                             size_t workspace_bytes, void *stream);
+
+size_t flh_b200_gemm_workspace_bytes(long M, long N, long K, long a_group, long b_group, int algo);
+
+/* Which algorithm FLH_B200_GEMM_AUTO resolves to for this shape (one of FLH_B200_GEMM_*). */
+int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group);
+
+/* Reads (and clears) the device status words of the tcgen05 GEMM: out[0] = 0, or the code of the
+ * first bounded wait that ran out (1 TMA producer, 2/3 MMA issuer, 4/5 converters, 6/7 epilogue),
+ * out[1] = the CTA that reported it.  SYNCHRONISES the device; for tests and post-mortems only.
+ * out: 4 ints in HOST memory.  No counterpart in FLH. */
+int flh_b200_gemm_status(int *out);
+
+/* The reference's one true C symbol, same signature and meaning
+ * (flh/kernels/gemm_and_dequant_i4.cu:471-480): group-128 symmetric scales, f16 output,
+ * legacy default stream, no status (errors are kept for flh_b200_last_error). */
+void flhDenseLayerGEMM_i4_o16(const uint8_t *A, const uint8_t *B, const void *A_scale,
+                              const void *B_scale, void *D, size_t M, size_t N, size_t K);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLH_B200_H */

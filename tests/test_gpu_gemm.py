@@ -1,0 +1,112 @@
+"""GPU parity of the int4 GEMM + dequant kernels against the CPU oracle (bit-exact), through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import int4_codes, rs, scales
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+STREAM, MMA, TC = 3, 2, 1
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def make_case(seed, m, n, k, a_group, b_group, asym, bias=False, neg_scales=False):
+    a = int4_codes(seed, m, k, unsigned=asym)
+    b = int4_codes(seed + 1, n, k)
+    ga = 1 if a_group == 0 else k // a_group
+    gb = 1 if b_group == 0 else k // b_group
+    sa, sb = scales(seed + 2, m, ga), scales(seed + 3, n, gb)
+    if neg_scales:
+        sa = (rs(seed + 6).standard_normal((m, ga)) * 0.02).astype(np.float16)
+        sb = (rs(seed + 7).standard_normal((n, gb)) * 0.02).astype(np.float16)
+    za = rs(seed + 4).randint(0, 16, size=(m, ga)).astype(np.float16) if asym else None
+    bi = (rs(seed + 5).standard_normal(n) * 0.1).astype(np.float16) if bias else None
+    ap = O.pack_i4(a) if not asym else ((a[:, 0::2] & 15) | ((a[:, 1::2] & 15) << 4)).astype(np.uint8)
+    return ap, O.pack_i4(b), sa, sb, za, bi
+
+
+def run_case(cuda, algo, case, bf16=False):
+    ap, bp, sa, sb, za, bi = case
+    k = ap.shape[1] * 2
+    rsum = None
+    if za is not None:
+        grp = min(k // sa.shape[1], k // sb.shape[1])
+        rsum = cuda.weight_rowsum(_dev(bp), grp)
+        assert np.array_equal(rsum.cpu().numpy(), O.weight_rowsum(bp, grp))
+    d = cuda.gemm_i4_dequant(_dev(ap), _dev(bp), _dev(sa), _dev(sb), A_zero=None if za is None else _dev(za),
+                             B_rowsum=rsum, bias=None if bi is None else _dev(bi),
+                             out_dtype=torch.bfloat16 if bf16 else torch.float16, algo=algo)
+    ref = O.gemm_i4_dequant(ap, bp, sa, sb, a_zero=za, bias=bi, bf16_out=bf16)
+    got = d.view(torch.int16).cpu().numpy().view(np.uint16)
+    want = ref.view(np.uint16)
+    bad = got != want
+    assert not bad.any(), f"{bad.sum()} of {bad.size} outputs differ; first at {np.argwhere(bad)[0]}"
+
+
+MODES = [  # (a_group, b_group, asym): 0 stands for "whole K"
+    (128, 128, False),   # the flh._CUDA contract
+    (0, 0, True),        # per-token asymmetric x per-channel weights
+    (0, 128, True),      # per-token asymmetric x group-128 weights
+    (128, 0, False),
+    (0, 0, False),
+    (128, 128, True),
+]
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 32])
+def test_stream_kernel(cuda, mode, m):
+    run_case(cuda, STREAM, make_case(10 * m, m, 256, 1024, *mode))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1024, 2048), (16, 128, 128), (16, 384, 1152), (32, 4096, 4096), (8, 4096, 11008)])
+def test_stream_kernel_shapes(cuda, m, n, k):
+    run_case(cuda, STREAM, make_case(m + n + k, m, n, k, 128, 128, False))
+    run_case(cuda, STREAM, make_case(m + n + k + 1, m, n, k, 0, 0, True, bias=True), bf16=True)
+
+
+def test_reference_script_case(cuda):
+    # test/test_gemm_dequant.py: M=1, N=1024, K=2048, signed codes, N(0,1)-like scales of both signs
+    run_case(cuda, STREAM, make_case(0, 1, 1024, 2048, 128, 128, False, neg_scales=True))
+    run_case(cuda, MMA, make_case(0, 1, 1024, 2048, 128, 128, False, neg_scales=True))
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("m", [1, 64, 129, 300])
+def test_mma_tile_kernel(cuda, mode, m):
+    run_case(cuda, MMA, make_case(20 * m, m, 256, 1024, *mode))
+
+
+def test_mma_tile_kernel_bias_bf16(cuda):
+    run_case(cuda, MMA, make_case(5, 200, 384, 2048, 0, 0, True, bias=True), bf16=True)
+    run_case(cuda, MMA, make_case(6, 130, 128, 128, 128, 128, False, bias=True))
+
+
+def test_c_symbol_of_the_reference(cuda):
+    # flhDenseLayerGEMM_i4_o16: same signature as flh/kernels/gemm_and_dequant_i4.cu:471-480
+    import ctypes
+    from flh_b200 import _lib
+    ap, bp, sa, sb, _, _ = make_case(3, 16, 256, 512, 128, 128, False)
+    A, B, SA, SB = _dev(ap), _dev(bp), _dev(sa), _dev(sb)
+    D = torch.empty((16, 256), dtype=torch.float16, device="cuda")
+    torch.cuda.synchronize()
+    _lib.load().flhDenseLayerGEMM_i4_o16(A.data_ptr(), B.data_ptr(), SA.data_ptr(), SB.data_ptr(), D.data_ptr(), 16, 256, 512)
+    torch.cuda.synchronize()
+    assert np.array_equal(D.cpu().numpy().view(np.uint16), O.gemm_i4_dequant(ap, bp, sa, sb).view(np.uint16))
+
+
+def test_gemm_argument_errors(cuda):
+    ap, bp, sa, sb, _, _ = make_case(3, 4, 128, 256, 128, 128, False)
+    with pytest.raises(RuntimeError):
+        cuda.gemm_i4_dequant_o16(_dev(ap).cpu(), _dev(bp), _dev(sa), _dev(sb))
+    with pytest.raises(RuntimeError):
+        cuda.gemm_i4_dequant_o16(_dev(ap), _dev(bp)[:, :64].contiguous(), _dev(sa), _dev(sb))
+    with pytest.raises(RuntimeError):
+        cuda.gemm_i4_dequant(_dev(ap), _dev(bp)[:100].contiguous(), _dev(sa), _dev(sb)[:100].contiguous())  # N % 128
+    with pytest.raises(RuntimeError):
+        cuda.gemm_i4_dequant(_dev(ap), _dev(bp), _dev(sa), _dev(sb), A_zero=_dev(sa))    # zero-point without row sums

@@ -1,0 +1,139 @@
+"""GPU parity of the activation quantisers against the CPU oracle (bit-exact), through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import activations, rs
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("gs", [128, 64, 32])
+@pytest.mark.parametrize("had", [True, False])
+@pytest.mark.parametrize("rows", [1, 3, 257, 4099])
+def test_group_sym_bit_exact(cuda, gs, had, rows):
+    x = activations(1000 + rows + gs, rows, gs, outlier_frac=0.02)
+    fn = cuda.hadamard_and_quantize_i4_gs if had else cuda.quant_and_pack_i4_gs
+    q, s = fn(_dev(x), gs)
+    qo, so = O.quant_group_sym(x, had)
+    assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16))
+    assert np.array_equal(q.cpu().numpy(), qo)
+
+
+def test_group_sym_edge_values(cuda):
+    # all-zero groups (scale -> 1), tiny groups (scale in the subnormal correction range),
+    # a saturating group, negative zero
+    x = np.zeros((6, 128), dtype=np.float16)
+    x[1, :] = 3e-6
+    x[1, ::2] *= -1
+    x[2, :] = np.linspace(-6e-5, 6e-5, 128)
+    x[3, :] = 60000.0
+    x[3, 5] = -60000.0
+    x[4, :] = -0.0
+    x[5, :] = rs(5).standard_normal(128) * 1e-3
+    for had, fn in ((False, cuda.quant_and_pack_i4), (True, cuda.hadamard_and_quantize_i4)):
+        q, s = fn(_dev(x))
+        qo, so = O.quant_group_sym(x, had)
+        assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16)), had
+        assert np.array_equal(q.cpu().numpy(), qo), had
+
+
+def test_group_sym_full_size(cuda):
+    # BASELINE sweep size M=4096, K=4096: round trip property + sampled oracle rows
+    x = activations(77, 4096, 4096)
+    q, s = cuda.hadamard_and_quantize_i4(_dev(x).view(-1, 128))
+    q, s = q.cpu().numpy(), s.cpu().numpy()
+    idx = rs(9).choice(q.shape[0], 4096, replace=False)
+    qo, so = O.quant_group_sym(x.reshape(-1, 128)[idx], True)
+    assert np.array_equal(q[idx], qo) and np.array_equal(s[idx].view(np.uint16), so.view(np.uint16))
+    # dequantised codes reproduce the transformed input within half a step (plus f16 rounding)
+    t = O.fht_f16(x.reshape(-1, 128)[idx]).astype(np.float32)
+    deq = O.unpack_i4(q[idx]).astype(np.float32) * s[idx].astype(np.float32)[:, None]
+    assert np.all(np.abs(deq - t) <= 0.51 * s[idx].astype(np.float32)[:, None] + 1e-2 * np.abs(t))
+
+
+@pytest.mark.parametrize("n", [128, 64, 32])
+@pytest.mark.parametrize("rows", [1, 5, 1024, 5000])
+def test_fht_inplace_bit_exact(cuda, n, rows):
+    x = activations(2000 + rows + n, rows, n, outlier_frac=0.02)
+    fn = {128: cuda.hadamard_transform_half, 64: cuda.hadamard_transform_64_half, 32: cuda.hadamard_transform_32_half}[n]
+    xd = _dev(x)
+    y = fn(xd)
+    assert y.data_ptr() == xd.data_ptr()          # in place, returns its argument
+    assert np.array_equal(y.cpu().numpy().view(np.uint16), O.fht_f16(x).view(np.uint16))
+
+
+TOKEN_SHAPES = [(1, 4096), (16, 4096), (5, 8192), (3, 16384), (2, 32768), (3, 64), (3, 128), (4, 256), (3, 512),
+                (3, 1024), (3, 2048), (4, 11008), (3, 14336), (2, 28672), (3, 3584), (3, 7168), (2, 1536), (2, 768)]
+
+
+@pytest.mark.parametrize("m,k", TOKEN_SHAPES)
+def test_token_asym_hadamard_bit_exact(cuda, m, k):
+    x = activations(3000 + k % 977 + m, m, k)
+    q, s, z = cuda.quant_token_asym_i4(_dev(x), hadamard=True)
+    qo, so, zo = O.quant_token_asym(x, True)
+    assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16))
+    assert np.array_equal(z.cpu().numpy().view(np.uint16), zo.view(np.uint16))
+    assert np.array_equal(q.cpu().numpy(), qo)
+
+
+@pytest.mark.parametrize("m,k", [(1, 4096), (7, 11008), (3, 192)])
+def test_token_asym_plain_and_clip(cuda, m, k):
+    x = activations(3500 + k % 977, m, k)
+    for clip in (1.0, 0.9):
+        q, s, z = cuda.quant_token_asym_i4(_dev(x), hadamard=False, clip=clip)
+        qo, so, zo = O.quant_token_asym(x, False, clip=clip)
+        assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16))
+        assert np.array_equal(z.cpu().numpy().view(np.uint16), zo.view(np.uint16))
+        assert np.array_equal(q.cpu().numpy(), qo)
+
+
+def test_token_asym_bf16_strided_and_edges(cuda):
+    k = 4096
+    xf = activations(3600, 6, k).astype(np.float32)
+    xf[1] = 0.0                      # all-zero row -> (-1, +1) range
+    xf[2] = np.abs(xf[2])            # one-sided row: zero-point 0
+    xf[3] = -np.abs(xf[3])           # one-sided negative row: zero-point 15
+    bits = O.f32_to_bf16_bits(xf)
+    wide = torch.zeros((6, k + 64), dtype=torch.bfloat16, device="cuda")
+    wide[:, :k] = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+    q, s, z = cuda.quant_token_asym_i4(wide[:, :k], hadamard=True)      # row stride k + 64
+    qo, so, zo = O.quant_token_asym(bits, True, bf16=True)
+    assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16))
+    assert np.array_equal(z.cpu().numpy().view(np.uint16), zo.view(np.uint16))
+    assert np.array_equal(q.cpu().numpy(), qo)
+
+
+def test_token_asym_full_size_property(cuda):
+    # BASELINE sweep M=4096, K=4096: sampled rows against the oracle + a checksum of all codes
+    x = activations(88, 4096, 4096)
+    q, s, z = cuda.quant_token_asym_i4(_dev(x), hadamard=True)
+    q, s, z = q.cpu().numpy(), s.cpu().numpy(), z.cpu().numpy()
+    idx = rs(10).choice(4096, 64, replace=False)
+    qo, so, zo = O.quant_token_asym(x[idx], True)
+    assert np.array_equal(q[idx], qo) and np.array_equal(s[idx], so) and np.array_equal(z[idx], zo)
+    # dequantised codes stay within half a step of the normalised transform, on the sampled rows
+    y = O.had_full_f32(x[idx].astype(np.float32))
+    deq = (O.unpack_i4(q[idx], False) - z[idx].astype(np.float32)[:, None]) * s[idx].astype(np.float32)[:, None]
+    assert np.all(np.abs(deq - y) <= 0.51 * s[idx].astype(np.float32)[:, None])
+
+
+def test_argument_errors(cuda):
+    x = torch.zeros((4, 128), dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError):
+        cuda.hadamard_and_quantize_i4(x.float())
+    with pytest.raises(RuntimeError):
+        cuda.hadamard_and_quantize_i4(x[:, :64])
+    with pytest.raises(RuntimeError):
+        cuda.hadamard_and_quantize_i4_gs(x, 48)
+    with pytest.raises(RuntimeError):
+        cuda.hadamard_transform_half(x.cpu())
+    with pytest.raises(RuntimeError):
+        cuda.quant_token_asym_i4(torch.zeros((2, 96), dtype=torch.float16, device="cuda"))   # K % 64
+    q, s = cuda.quant_and_pack_i4(x[:0])            # empty input is fine
+    assert q.shape == (0, 64) and s.shape == (0,)
