@@ -1,0 +1,369 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A4 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workloads (synthetic, seeded; shapes from the reference's benchmark configurations):
+  had_quant     (default) fused full-width Hadamard + per-token asymmetric int4 quantiser + packing,
+                f16 X [16384, 4096] ~ N(0,1) with 0.1 % outlier channels x20; metric = algorithmic GB/s
+                (bytes = M * (2K + K/2 + 4)).  One step = one launch over one batch.
+  gemm_prefill  int4 GEMM + dequant, M = 2048, 4096 -> 12288, group-128 scales; metric = TOPS (2MNK).
+  gemm_decode   int4 GEMM + dequant, M = 16, 4096 -> 22016; metric = GB/s on packed-weight bytes.
+The default run also measures the other kernels briefly and reports them under "extra".
+
+One JSON line on stdout (rank 0).  Multi-GPU: token batches are independent, so every rank runs
+the same batch size on its own GPU (weak scaling, no data-path collective); time = max over ranks.
+`--impl reference` times the reference's own CPU implementation of the same path (the PyTorch
+fake_quant code, restated in oracle/fake_quant_port.py) on the host cores, on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
+
+
+def synth_activations(m, k, seed, device, dtype=torch.float16):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randn(m, k, generator=g)
+    n_out = max(1, round(k * 0.001))
+    ch = torch.randperm(k, generator=g)[:n_out]
+    x[:, ch] *= 20.0
+    return x.to(dtype).to(device)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+        self.t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "sw_power_cap": 0x4, "hw_power_brake_slowdown": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.nv:
+            self.t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self.nv:
+            self.t.join(timeout=1)
+
+    def summary(self):
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def dist_setup(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if args.impl == "reference":
+            return world, rank, local, None
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return world, rank, local, dist
+    return world, rank, local, None
+
+
+def timed_loop(fn, steps, warmup, dist, device):
+    """W warm-up steps, then exactly `steps` steps between barrier+synchronize; CUDA events on the
+    current stream; returns seconds (max over ranks)."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1) * 1e-3], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+# ----------------------------------------------------------------------------------------------
+def gemm_inputs(C, m, n, k, grouped, asym, device, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    A = torch.randint(0, 256, (m, k // 2), generator=g, dtype=torch.uint8).to(device)
+    B = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8).to(device)
+    gcols = k // 128 if grouped else 1
+    sa = (torch.rand(m, gcols, generator=g) * 0.015 + 0.005).half().to(device)
+    sb = (torch.rand(n, gcols, generator=g) * 0.015 + 0.005).half().to(device)
+    za = torch.randint(0, 16, (m, gcols), generator=g).half().to(device) if asym else None
+    rs = C.weight_rowsum(B, 128 if grouped else k) if asym else None
+    return A, B, sa, sb, za, rs
+
+
+def run_ours(args, world, rank, local, dist):
+    import flh_b200
+    from flh_b200 import _lib
+    C = flh_b200._CUDA
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    _lib.check(_lib.load().flh_b200_device_check(), "device_check")
+    peaks = measured_peaks()
+    steps, warmup = args.steps, max(args.warmup, 3)
+    out = {"n_gpus": world, "steps": steps, "warmup": warmup, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "data": "synthetic", "impl": "ours"}
+
+    if args.workload == "had_quant":
+        M, K = 16384, 4096
+        xs = [synth_activations(M, K, 100 + i + 10 * rank, device) for i in range(3)]   # 3 x 134 MB > L2
+        step_bytes = M * (2 * K + K // 2 + 4)
+
+        def fn(i):
+            C.quant_token_asym_i4(xs[i % 3], hadamard=True)
+
+        with ClockSampler(local) as cs:
+            t = timed_loop(fn, steps, warmup, dist, device)
+        value = world * step_bytes * steps / t / 1e9
+        out.update(metric="had_quant_GBps", unit="GB/s", value=value, ms_per_step=t / steps * 1e3, dtype="f32",
+                   config={"workload": "fused full-width Hadamard (binary32) + per-token asymmetric int4 quant + pack, "
+                                       "f16 X[16384,4096] per GPU, 0.1% outlier channels x20",
+                           "M_per_gpu": M, "K": K, "bytes_per_step_per_gpu": step_bytes,
+                           "l2": "three rotating 134 MB inputs, each larger than the 126 MB L2",
+                           "parallelism": f"token-sharded x{world}, no collective"},
+                   clocks=cs.summary(), gpu_launches=steps)
+        ach = step_bytes * steps / t / 1e9
+        out["roofline"] = {"kernel": "quant_token_asym_kernel<6,0,false,true>", "bound": "hbm", "achieved": ach,
+                           "peak": peaks["hbm_gbs"], "peak_src": peaks["src"], "unit": "GB/s",
+                           "frac": ach / peaks["hbm_gbs"], "traffic": None}
+        # ---- end to end through the public API with host buffers ----
+        xh = [x.cpu().pin_memory() for x in xs[:2]]
+        qh = torch.empty((M, K // 2), dtype=torch.uint8).pin_memory()
+        sh = torch.empty((M,), dtype=torch.float16).pin_memory()
+        zh = torch.empty((M,), dtype=torch.float16).pin_memory()
+        xd = torch.empty((M, K), dtype=torch.float16, device=device)
+
+        def e2e(i):
+            xd.copy_(xh[i % 2], non_blocking=True)
+            q, s, z = C.quant_token_asym_i4(xd, hadamard=True)
+            qh.copy_(q, non_blocking=True); sh.copy_(s, non_blocking=True); zh.copy_(z, non_blocking=True)
+
+        te = timed_loop(e2e, steps, 3, dist, device)
+        out["e2e"] = {"value": world * step_bytes * steps / te / 1e9, "unit": "GB/s",
+                      "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * K // 2 + 4 * M,
+                      "ms_per_step": te / steps * 1e3}
+        if rank == 0:
+            out["extra"] = extras(C, device, peaks)
+            if world == 1:
+                out["cpu_baseline"] = cpu_had_quant(K, sample_rows=1024, reps=8)
+    elif args.workload in ("gemm_prefill", "gemm_decode"):
+        prefill = args.workload == "gemm_prefill"
+        M, K, N = (2048, 4096, 12288) if prefill else (16, 4096, 22016)
+        sets = [gemm_inputs(C, M, N, K, True, False, device, seed=s + 10 * rank) for s in range(3 if not prefill else 1)]
+        D = torch.empty((M, N), dtype=torch.float16, device=device)
+        flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device) if prefill else None
+
+        def fn(i):
+            A, B, sa, sb, za, rs = sets[i % len(sets)]
+            C.gemm_i4_dequant(A, B, sa, sb, out=D)
+
+        with ClockSampler(local) as cs:
+            t = timed_loop(fn, steps, warmup, dist, device)
+        if prefill:
+            ops = 2.0 * M * N * K
+            value = world * ops * steps / t / 1e12
+            out.update(metric="int4_gemm_TOPS", unit="TOPS", value=value, dtype="s8 x s8 -> s32 (int4 codes)",
+                       roofline={"bound": "tensor", "achieved": ops * steps / t / 1e12,
+                                 "peak": 2 * peaks["bf16_tflops"], "peak_src": peaks["src"] + " bf16 x2 (dense INT8 runs at twice the bf16 rate)",
+                                 "unit": "TOPS", "frac": ops * steps / t / 1e12 / (2 * peaks["bf16_tflops"]), "traffic": None})
+        else:
+            b = N * K // 2 + 2 * N * (K // 128) + M * K // 2 + 2 * M * (K // 128) + 2 * M * N
+            value = world * b * steps / t / 1e9
+            out.update(metric="int4_gemm_decode_GBps", unit="GB/s", value=value, dtype="s8 x s8 -> s32 (int4 codes)",
+                       roofline={"bound": "hbm", "achieved": b * steps / t / 1e9, "peak": peaks["hbm_gbs"],
+                                 "peak_src": peaks["src"], "unit": "GB/s", "frac": b * steps / t / 1e9 / peaks["hbm_gbs"], "traffic": None})
+        out.update(ms_per_step=t / steps * 1e3, clocks=cs.summary(), gpu_launches=steps,
+                   config={"workload": f"int4 GEMM + group-128 dequant, M={M}, {K}->{N}, f16 out", "M": M, "N": N, "K": K,
+                           "l2": "weights of three rotating problems (3 x 45 MB)" if not prefill else "operands re-used across steps (compute-bound)",
+                           "parallelism": f"replicated x{world}, no collective"})
+    else:
+        raise SystemExit(f"unknown workload {args.workload}")
+    st = C.gemm_status()
+    if st[0] != 0:
+        out["device_status"] = st
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+
+
+def _time(fn, iters=10, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / iters
+
+
+def extras(C, device, peaks):
+    """Short measurements of the other kernels of the path (not the headline)."""
+    ex = {}
+    for (m, k) in ((16384, 4096), (4096, 11008), (4096, 14336)):
+        xs = [synth_activations(m, k, 7 + i, device) for i in range(2)]
+        it = [0]
+
+        def f():
+            it[0] += 1
+            C.quant_token_asym_i4(xs[it[0] % 2], hadamard=True)
+
+        def g():
+            it[0] += 1
+            C.hadamard_and_quantize_i4(xs[it[0] % 2].view(-1, 128))
+
+        t = _time(f)
+        ex[f"had_quant_token_asym_M{m}_K{k}_GBps"] = m * (2 * k + k // 2 + 4) / t / 1e9
+        t = _time(g)
+        ex[f"had_quant_group128_sym_M{m}_K{k}_GBps"] = m * (2 * k + k // 2 + 2 * k // 128) / t / 1e9
+        del xs
+    for (m, k, n) in ((2048, 4096, 12288), (8192, 4096, 22016), (2048, 11008, 4096)):
+        for grouped, asym, tag in ((True, False, "g128_sym"), (False, True, "token_asym_channel")):
+            A, B, sa, sb, za, rs = gemm_inputs(C, m, n, k, grouped, asym, device)
+            t = _time(lambda: C.gemm_i4_dequant(A, B, sa, sb, A_zero=za, B_rowsum=rs), iters=5, warm=2)
+            ex[f"gemm_M{m}_{k}to{n}_{tag}_TOPS"] = 2.0 * m * n * k / t / 1e12
+    for (m, k, n) in ((1, 4096, 22016), (16, 4096, 22016), (16, 11008, 4096), (16, 4096, 4096)):
+        sets = [gemm_inputs(C, m, n, k, True, False, device, seed=s) for s in range(3)]
+        it = [0]
+
+        def f():
+            it[0] += 1
+            A, B, sa, sb, za, rs = sets[it[0] % 3]
+            C.gemm_i4_dequant(A, B, sa, sb)
+
+        t = _time(f, iters=12)
+        b = n * k // 2 + 2 * n * (k // 128) + m * k // 2 + 2 * m * n
+        ex[f"gemm_decode_M{m}_{k}to{n}_g128_GBps"] = b / t / 1e9
+    a8 = torch.randint(-8, 8, (8192, 8192), device=device, dtype=torch.int8)
+    b8 = torch.randint(-8, 8, (8192, 8192), device=device, dtype=torch.int8)
+    t = _time(lambda: torch._int_mm(a8, b8), iters=5, warm=2)
+    ex["yardstick_torch_int_mm_8192_TOPS"] = 2.0 * 8192 ** 3 / t / 1e12
+    return ex
+
+
+# ----------------------------------------------------------------------------------------------
+def cpu_had_quant(K, sample_rows, reps):
+    from oracle import fake_quant_port as FQ
+    H = FQ.hadamard_matrix(K)
+    x = synth_activations(sample_rows, K, 5, "cpu")
+    FQ.had_quant_pack(x, H)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        FQ.had_quant_pack(x, H)
+    t = (time.perf_counter() - t0) / reps
+    b = sample_rows * (2 * K + K // 2 + 4)
+    return {"value": b / t / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{sample_rows} rows of K={K} per step, {reps} steps: x @ H (dense, f32) + per-token asymmetric "
+                      f"int4 + pack, torch CPU ({os.cpu_count()} logical CPUs)", "ms_per_step": t * 1e3}
+
+
+def run_reference(args, world, rank):
+    """The reference's own CPU implementation of the path (PyTorch fake_quant code, restated)."""
+    if rank != 0:
+        return
+    if args.workload != "had_quant":
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU arm is implemented for the had_quant workload"}))
+        return
+    from oracle import fake_quant_port as FQ
+    K, rows = 4096, 2048
+    H = FQ.hadamard_matrix(K)
+    xs = [synth_activations(rows, K, 100 + i, "cpu") for i in range(2)]
+    for i in range(max(1, args.warmup)):
+        FQ.had_quant_pack(xs[i % 2], H)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        FQ.had_quant_pack(xs[i % 2], H)
+    t = time.perf_counter() - t0
+    b = rows * (2 * K + K // 2 + 4)
+    v = b * args.steps / t / 1e9
+    sample = f"{rows} rows of K={K} per step (the GPU arm's batch is 16384 rows): x @ H dense f32 + per-token asymmetric int4 + pack"
+    print(json.dumps({
+        "impl": "reference", "metric": "had_quant_GBps", "unit": "GB/s", "value": v, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": t / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "fused full-width Hadamard + per-token asymmetric int4 quant + pack, f16 X[.,4096]", "K": K,
+                   "rows_per_step": rows},
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="had_quant")
+    args = ap.parse_args()
+    world, rank, local, dist = dist_setup(args)
+    if args.impl == "reference":
+        run_reference(args, world, rank)
+        return
+    try:
+        run_ours(args, world, rank, local, dist)
+    finally:
+        if dist is not None:
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
