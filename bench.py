@@ -56,6 +56,7 @@ class ClockSampler:
 
     def __init__(self, index):
         self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.t0 = self.t1 = None        # perf_counter bounds of the timed region, set by timed_loop
         self._stop = threading.Event()
         try:
             import pynvml
@@ -73,7 +74,7 @@ class ClockSampler:
                  "sw_power_cap": 0x4, "hw_power_brake_slowdown": 0x80}
         while not self._stop.is_set():
             try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.samples.append((time.perf_counter(), nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
                 r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
                     else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
                 for k, bit in names.items():
@@ -81,7 +82,7 @@ class ClockSampler:
                         self.reasons.add(k)
             except Exception:
                 pass
-            time.sleep(0.02)
+            time.sleep(0.001)
 
     def __enter__(self):
         if self.nv:
@@ -94,8 +95,13 @@ class ClockSampler:
             self.t.join(timeout=1)
 
     def summary(self):
-        med = float(np.median(self.samples)) if self.samples else None
-        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        inside = [c for (t, c) in self.samples if self.t0 is not None and self.t0 <= t <= self.t1]
+        window = "timed region"
+        if len(inside) < 3:            # a region of a few ms: use every sample taken under load (warm-up included)
+            inside, window = [c for (_, c) in self.samples], "warm-up + timed region"
+        med = float(np.median(inside)) if inside else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(inside),
+                "window": window}
 
 
 def dist_setup(args):
@@ -113,21 +119,37 @@ def dist_setup(args):
     return world, rank, local, None
 
 
-def timed_loop(fn, steps, warmup, dist, device):
+def timed_loop(fn, steps, warmup, dist, device, graph=False, sampler=None):
     """W warm-up steps, then exactly `steps` steps between barrier+synchronize; CUDA events on the
-    current stream; returns seconds (max over ranks)."""
+    current stream; returns seconds (max over ranks).  graph=True: the `steps` steps are recorded into
+    one CUDA graph (after the warm-up) and the timed region is its launch — for steps shorter than the
+    host's per-launch cost."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
+    g = None
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(steps):
+                fn(i)
+        g.replay()          # one untimed replay
+        torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
     e0.record()
-    for i in range(steps):
-        fn(i)
+    if g is not None:
+        g.replay()
+    else:
+        for i in range(steps):
+            fn(i)
     e1.record()
     torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.t0, sampler.t1 = w0, time.perf_counter()
     if dist is not None:
         dist.barrier()
     t = torch.tensor([e0.elapsed_time(e1) * 1e-3], device=device, dtype=torch.float64)
@@ -170,7 +192,7 @@ def run_ours(args, world, rank, local, dist):
             C.quant_token_asym_i4(xs[i % 3], hadamard=True)
 
         with ClockSampler(local) as cs:
-            t = timed_loop(fn, steps, warmup, dist, device)
+            t = timed_loop(fn, steps, warmup, dist, device, sampler=cs)
         value = world * step_bytes * steps / t / 1e9
         out.update(metric="had_quant_GBps", unit="GB/s", value=value, ms_per_step=t / steps * 1e3, dtype="f32",
                    config={"workload": "fused full-width Hadamard (binary32) + per-token asymmetric int4 quant + pack, "
@@ -199,7 +221,7 @@ def run_ours(args, world, rank, local, dist):
         out["e2e"] = {"value": world * step_bytes * steps / te / 1e9, "unit": "GB/s",
                       "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * K // 2 + 4 * M,
                       "ms_per_step": te / steps * 1e3}
-        if rank == 0:
+        if rank == 0 and not args.no_extra:
             out["extra"] = extras(C, device, peaks)
             if world == 1:
                 out["cpu_baseline"] = cpu_had_quant(K, sample_rows=1024, reps=8)
@@ -215,7 +237,7 @@ def run_ours(args, world, rank, local, dist):
             C.gemm_i4_dequant(A, B, sa, sb, out=D)
 
         with ClockSampler(local) as cs:
-            t = timed_loop(fn, steps, warmup, dist, device)
+            t = timed_loop(fn, steps, warmup, dist, device, graph=not prefill, sampler=cs)
         if prefill:
             ops = 2.0 * M * N * K
             value = world * ops * steps / t / 1e12
@@ -231,7 +253,7 @@ def run_ours(args, world, rank, local, dist):
                                  "peak_src": peaks["src"], "unit": "GB/s", "frac": b * steps / t / 1e9 / peaks["hbm_gbs"], "traffic": None})
         out.update(ms_per_step=t / steps * 1e3, clocks=cs.summary(), gpu_launches=steps,
                    config={"workload": f"int4 GEMM + group-128 dequant, M={M}, {K}->{N}, f16 out", "M": M, "N": N, "K": K,
-                           "l2": "weights of three rotating problems (3 x 45 MB)" if not prefill else "operands re-used across steps (compute-bound)",
+                           "l2": "weights of three rotating problems (3 x 45 MB > L2); the K steps run as one CUDA graph" if not prefill else "operands re-used across steps (compute-bound)",
                            "parallelism": f"replicated x{world}, no collective"})
     else:
         raise SystemExit(f"unknown workload {args.workload}")
@@ -242,15 +264,28 @@ def run_ours(args, world, rank, local, dist):
         print(json.dumps(out), flush=True)
 
 
-def _time(fn, iters=10, warm=3):
+def _time(fn, iters=10, warm=3, graph=False):
+    """Seconds per call.  graph=True records `iters` calls into one CUDA graph and times its replay, so
+    that kernels shorter than the host's launch cost are timed back to back."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        fn()
-    e1.record()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        e1.record()
+    else:
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) * 1e-3 / iters
 
@@ -284,12 +319,14 @@ def extras(C, device, peaks):
         sets = [gemm_inputs(C, m, n, k, True, False, device, seed=s) for s in range(3)]
         it = [0]
 
+        D = torch.empty((m, n), dtype=torch.float16, device=device)
+
         def f():
             it[0] += 1
             A, B, sa, sb, za, rs = sets[it[0] % 3]
-            C.gemm_i4_dequant(A, B, sa, sb)
+            C.gemm_i4_dequant(A, B, sa, sb, out=D)
 
-        t = _time(f, iters=12)
+        t = _time(f, iters=12, graph=True)
         b = n * k // 2 + 2 * n * (k // 128) + m * k // 2 + 2 * m * n
         ex[f"gemm_decode_M{m}_{k}to{n}_g128_GBps"] = b / t / 1e9
     a8 = torch.randint(-8, 8, (8192, 8192), device=device, dtype=torch.int8)
@@ -349,10 +386,11 @@ def run_reference(args, world, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="had_quant")
+    ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline (profiling runs)")
     args = ap.parse_args()
     world, rank, local, dist = dist_setup(args)
     if args.impl == "reference":
