@@ -255,6 +255,37 @@ def run_ours(args, world, rank, local, dist):
                    config={"workload": f"int4 GEMM + group-128 dequant, M={M}, {K}->{N}, f16 out", "M": M, "N": N, "K": K,
                            "l2": "weights of three rotating problems (3 x 45 MB > L2); the K steps run as one CUDA graph" if not prefill else "operands re-used across steps (compute-bound)",
                            "parallelism": f"replicated x{world}, no collective"})
+    elif args.workload in ("llama7b_prefill", "llama7b_decode", "llama70b_prefill", "llama70b_decode"):
+        from flh_b200.model import Decoder, DecoderConfig, LLAMA2_7B, LLAMA3_70B
+        big = args.workload.startswith("llama70b")
+        prefill = args.workload.endswith("prefill")
+        shape = dict(LLAMA3_70B if big else LLAMA2_7B)
+        if args.layers:
+            shape["n_layers"] = args.layers
+        cfg = DecoderConfig(**shape, vocab=32000, act_mode=args.act_mode, tp=world)
+        model = Decoder(cfg, device, seed=0, group=None, with_head=True)
+        if prefill:
+            B, S = (4, 2048) if big else (1, 2048)
+            ids = torch.randint(100, 200, (B, S), device=device)
+            fn = lambda i: model(ids)
+            tokens = B * S
+        else:
+            B, ctx = (64, 1024) if big else (16, 1024)
+            cache = model.new_cache(B, ctx + 8)
+            for c in cache:
+                c[0].normal_(); c[1].normal_()
+            ids = torch.randint(100, 200, (B, 1), device=device)
+            fn = lambda i: model(ids, cache=cache, start=ctx)
+            tokens = B
+        steps, warmup = min(steps, 20), min(warmup, 5)
+        with ClockSampler(local) as cs:
+            t = timed_loop(fn, steps, max(warmup, 3), dist, device, sampler=cs)
+        out.update(metric="w4a4_llama_%s_tok_per_s" % ("prefill" if prefill else "decode"), unit="tok/s",
+                   value=tokens * steps / t, ms_per_step=t / steps * 1e3, dtype="int4 codes, s32 accumulate, f16 activations",
+                   steps=steps, warmup=max(warmup, 3), scaling="strong" if world > 1 else "weak", clocks=cs.summary(),
+                   config={"workload": args.workload, **shape, "act_mode": args.act_mode, "batch": B,
+                           "seq_or_ctx": 2048 if prefill else 1024, "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                           "weights": "random int4 codes and scales (no checkpoint)"})
     else:
         raise SystemExit(f"unknown workload {args.workload}")
     st = C.gemm_status()
@@ -390,6 +421,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="had_quant")
+    ap.add_argument("--act-mode", default="group_sym", choices=["group_sym", "token_asym"])
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count of the llama workloads")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline (profiling runs)")
     args = ap.parse_args()
     world, rank, local, dist = dist_setup(args)

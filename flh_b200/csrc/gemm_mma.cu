@@ -2,7 +2,7 @@
 // (mma.sync.m16n8k32 s8), two kernels:
 //   * gemm_tile_kernel    128x128x128 CTA tiles, cp.async ring; any M.  Bring-up cross-check for
 //                         the tcgen05 kernel and the "legacy mma.sync" line of the benchmark.
-//   * gemm_stream_kernel  decode shapes (M <= 32): every CTA streams a 32-row slab of packed
+//   * gemm_stream_kernel  decode shapes (M <= 32): every CTA streams a 32- or 64-row slab of packed
 //                         weights through an 8-deep cp.async ring; HBM-bound on the weight bytes.
 //
 // Both feed the tensor cores without unpacking to natural order.  A packed 32-bit word holds eight
@@ -207,57 +207,141 @@ gemm_tile_kernel(const GemmParams p) {
 }
 
 // --------------------------------------------------------------------------------------------
-// Streaming kernel for decode: CTA = 4 warps, 32 weight rows (8 per warp), K in blocks of 256
-// (128 packed bytes per row per stage), SSTAGES-deep ring.  The MT*16 activation rows ride in
-// the same ring.  16-byte chunk c of row r sits at chunk c ^ ((r & 1) << 2), so the eight lanes of
-// a quarter warp (two rows x four chunks) touch all 32 banks once.
-constexpr int SBN = 32, SSTAGES = 8;
+// Streaming kernel for decode (M <= 32): HBM-bound on the packed weight bytes.
+//
+// The weights are the ROW operand of mma.m16n8k32 (16 output channels per warp), the tokens the
+// column operand (8 per mma), so a warp spends 2 shared-memory loads, 24 logic ops and 4 mma per
+// kilobyte of weights for up to 8 tokens.  CTA = WARPS warps = 16*WARPS weight rows; K advances in
+// stages of 256 (128 packed bytes per row) through a 6-deep cp.async ring that also carries
+// the token tile and, for group-128 scales, the two scale groups of the stage (4-byte copies), so
+// the dequantisation never waits on global memory.  16-byte chunk c of row r sits at chunk
+// c ^ ((r & 1) << 2): the eight lanes of a quarter warp (two rows x four chunks) cover all banks.
+constexpr int SSTAGES = 6;
 
-template <int MT, bool A_UNSIGNED>
-__global__ void __launch_bounds__(128)
+template <int WARPS, int NT>
+struct StreamPlan {
+    static constexpr int BN = 16 * WARPS, TOK = 8 * NT;
+    static constexpr int kB = 0;                              // weights  BN x 128 B
+    static constexpr int kA = kB + BN * 128;                  // tokens   TOK x 128 B
+    static constexpr int kSB = kA + TOK * 128;                // weight scales  [BN][2] half
+    static constexpr int kRS = kSB + BN * 4;                  // weight row sums [BN][2] int32
+    static constexpr int kSA = kRS + BN * 8;                  // token scales   [TOK][2] half
+    static constexpr int kZA = kSA + TOK * 4;                 // token zeros    [TOK][2] half
+    static constexpr int kStage = ((kZA + TOK * 4 + 127) / 128) * 128;
+};
+
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src));
+}
+
+template <bool B_UNSIGNED>
+__device__ __forceinline__ void mma_w_by_tok(int32_t (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    if (B_UNSIGNED)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int WARPS, int NT, bool A_UNSIGNED, bool GROUPED>
+__global__ void __launch_bounds__(WARPS * 32)
 gemm_stream_kernel(const GemmParams p) {
+    using Plan = StreamPlan<WARPS, NT>;
+    constexpr int BN = Plan::BN, TOK = Plan::TOK, NTHREADS = WARPS * 32;
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int STAGE_BYTES = (SBN + MT * 16) * 128;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * SBN;
-    const int KB2 = (p.K + 255) / 256;          // 256-K stages; the last may be half full
+    const int n0 = blockIdx.x * BN;
+    const int KB = p.K / 128, KB2 = (KB + 1) / 2;
     const long ldk = p.K / 2;
+    const bool has_zero = A_UNSIGNED;
+    // 4-byte copies of two adjacent f16 scales need an even number of groups per row
+    const bool pair_ok = (KB & 1) == 0;
 
     auto load_stage = [&](int stage, int kb2) {
-        uint8_t *sB = smem + stage * STAGE_BYTES, *sA = sB + SBN * 128;
-        const int kbytes = (int)ldk - kb2 * 128;     // bytes left in the row from this stage on
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int ch = tid + i * 128, row = ch >> 3, c = ch & 7;
+        uint8_t *st = smem + stage * Plan::kStage;
+        const int kbytes = (int)ldk - kb2 * 128;          // bytes left in a row from this stage on
+        for (int ch = tid; ch < BN * 8; ch += NTHREADS) {
+            const int row = ch >> 3, c = ch & 7;
             const bool ok = c * 16 < kbytes;
-            cp_async16(smem_u32(sB + row * 128 + ((c ^ ((row & 1) << 2)) << 4)),
+            cp_async16(smem_u32(st + Plan::kB + row * 128 + ((c ^ ((row & 1) << 2)) << 4)),
                        p.B + (long)(n0 + row) * ldk + kb2 * 128 + (ok ? c * 16 : 0), ok ? 16 : 0);
         }
-#pragma unroll
-        for (int i = 0; i < MT; ++i) {
-            const int ch = tid + i * 128, row = ch >> 3, c = ch & 7;
+        for (int ch = tid; ch < TOK * 8; ch += NTHREADS) {
+            const int row = ch >> 3, c = ch & 7;
             const bool ok = row < p.M && c * 16 < kbytes;
-            cp_async16(smem_u32(sA + row * 128 + ((c ^ ((row & 1) << 2)) << 4)),
-                       p.A + (long)(row < p.M ? row : p.M - 1) * ldk + kb2 * 128 + (c * 16 < kbytes ? c * 16 : 0),
-                       ok ? 16 : 0);
+            cp_async16(smem_u32(st + Plan::kA + row * 128 + ((c ^ ((row & 1) << 2)) << 4)),
+                       p.A + (long)(row < p.M ? row : p.M - 1) * ldk + kb2 * 128 + (c * 16 < kbytes ? c * 16 : 0), ok ? 16 : 0);
+        }
+        if (GROUPED) {
+            const int g0 = kb2 * 2;
+            const bool two = g0 + 1 < KB;
+            // weight side: BN rows; token side: TOK rows.  One thread per row and array.
+            for (int r = tid; r < BN; r += NTHREADS) {
+                if (p.gb_cols > 1) {
+                    const __half *src = p.b_scale + (long)(n0 + r) * KB + g0;
+                    __half *dst = reinterpret_cast<__half *>(st + Plan::kSB) + 2 * r;
+                    if (pair_ok) cp_async4(smem_u32(dst), src);
+                    else { dst[0] = src[0]; dst[1] = two ? src[1] : src[0]; }
+                }
+                if (has_zero) {
+                    const int32_t *src = p.b_rowsum + (long)(n0 + r) * KB + g0;
+                    int32_t *dst = reinterpret_cast<int32_t *>(st + Plan::kRS) + 2 * r;
+                    if (pair_ok) cp_async8(smem_u32(dst), src);
+                    else { dst[0] = src[0]; dst[1] = two ? src[1] : src[0]; }
+                }
+            }
+            for (int r = tid; r < TOK; r += NTHREADS) {
+                const int rr = r < p.M ? r : p.M - 1;
+                if (p.ga_cols > 1) {
+                    const __half *src = p.a_scale + (long)rr * KB + g0;
+                    __half *dst = reinterpret_cast<__half *>(st + Plan::kSA) + 2 * r;
+                    if (pair_ok) cp_async4(smem_u32(dst), src);
+                    else { dst[0] = src[0]; dst[1] = two ? src[1] : src[0]; }
+                    if (has_zero) {
+                        const __half *zs = p.a_zero + (long)rr * KB + g0;
+                        __half *zd = reinterpret_cast<__half *>(st + Plan::kZA) + 2 * r;
+                        if (pair_ok) cp_async4(smem_u32(zd), zs);
+                        else { zd[0] = zs[0]; zd[1] = two ? zs[1] : zs[0]; }
+                    }
+                }
+            }
         }
     };
 
-    int32_t c[MT][4];
-    float acc[MT][4];
+    int32_t c[NT][4];
+    float acc[NT][4];
 #pragma unroll
-    for (int i = 0; i < MT; ++i)
+    for (int i = 0; i < NT; ++i)
 #pragma unroll
         for (int k = 0; k < 4; ++k) { c[i][k] = 0; acc[i][k] = 0.0f; }
+
+    // quantities that do not depend on the K-group
+    float sb_c[2] = {0.f, 0.f}, sa_c[NT][2];
+    int za_c[NT][2];
+    const int ch0 = n0 + warp * 16 + g;                  // this thread's channels: ch0, ch0 + 8
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int tok = min(i * 8 + 2 * t + j, p.M - 1);
+            sa_c[i][j] = p.ga_cols == 1 ? __half2float(p.a_scale[tok]) : 0.f;
+            za_c[i][j] = (has_zero && p.ga_cols == 1) ? (int)__half2float(p.a_zero[tok]) : 0;
+        }
+    if (p.gb_cols == 1) { sb_c[0] = __half2float(p.b_scale[ch0]); sb_c[1] = __half2float(p.b_scale[ch0 + 8]); }
 
 #pragma unroll
     for (int s = 0; s < SSTAGES - 1; ++s) {
         if (s < KB2) load_stage(s, s);
         cp_async_commit();
     }
-    const bool has_zero = p.a_zero != nullptr;
-    const int KB = p.K / 128;
 
     for (int kb2 = 0; kb2 < KB2; ++kb2) {
         cp_async_wait<SSTAGES - 2>();
@@ -265,52 +349,80 @@ gemm_stream_kernel(const GemmParams p) {
         if (kb2 + SSTAGES - 1 < KB2) load_stage((kb2 + SSTAGES - 1) % SSTAGES, kb2 + SSTAGES - 1);
         cp_async_commit();
 
-        const uint8_t *sB = smem + (kb2 % SSTAGES) * STAGE_BYTES, *sA = sB + SBN * 128;
+        const uint8_t *st = smem + (kb2 % SSTAGES) * Plan::kStage;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int kb = kb2 * 2 + half;
             if (kb >= KB) break;
-            const int brow = warp * 8 + g;
-            const uint4 bv = *reinterpret_cast<const uint4 *>(sB + brow * 128 + (((half * 4 + t) ^ ((brow & 1) << 2)) << 4));
-            const uint32_t b[4] = {bv.x, bv.y, bv.z, bv.w};
+            const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+            const int chunk = half * 4 + t;
+            const uint4 w_lo = *reinterpret_cast<const uint4 *>(st + Plan::kB + r_lo * 128 + ((chunk ^ ((r_lo & 1) << 2)) << 4));
+            const uint4 w_hi = *reinterpret_cast<const uint4 *>(st + Plan::kB + r_hi * 128 + ((chunk ^ ((r_hi & 1) << 2)) << 4));
+            const uint32_t wl[4] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w}, wh[4] = {w_hi.x, w_hi.y, w_hi.z, w_hi.w};
+            uint32_t a0[4], a1[4], a2[4], a3[4];
 #pragma unroll
-            for (int i = 0; i < MT; ++i) {
-                const int r_lo = i * 16 + g, r_hi = r_lo + 8;
-                const uint4 a_lo = *reinterpret_cast<const uint4 *>(sA + r_lo * 128 + (((half * 4 + t) ^ ((r_lo & 1) << 2)) << 4));
-                const uint4 a_hi = *reinterpret_cast<const uint4 *>(sA + r_hi * 128 + (((half * 4 + t) ^ ((r_hi & 1) << 2)) << 4));
-                const uint32_t al[4] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w}, ah[4] = {a_hi.x, a_hi.y, a_hi.z, a_hi.w};
+            for (int q = 0; q < 4; ++q) { a0[q] = even16(wl[q]); a1[q] = even16(wh[q]); a2[q] = odd16(wl[q]); a3[q] = odd16(wh[q]); }
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    mma_i8<A_UNSIGNED>(c[i], even16(al[q]), even16(ah[q]), odd16(al[q]), odd16(ah[q]),
-                                       even16(b[q]), odd16(b[q]));
-                if (p.grouped) {
-                    dequant_frag(c[i], acc[i], load_rowq(p, i * 16 + g, kb, has_zero),
-                                 load_colq(p, n0 + warp * 8 + 2 * t, kb, has_zero));
+            for (int i = 0; i < NT; ++i) {
+                const int tr = i * 8 + g;
+                const uint4 xv = *reinterpret_cast<const uint4 *>(st + Plan::kA + tr * 128 + ((chunk ^ ((tr & 1) << 2)) << 4));
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+                int32_t c2[4] = {0, 0, 0, 0};          // second chain: the four mma no longer depend on each other in a row
+                mma_w_by_tok<A_UNSIGNED>(c[i], a0[0], a1[0], a2[0], a3[0], even16(xw[0]), odd16(xw[0]));
+                mma_w_by_tok<A_UNSIGNED>(c2, a0[1], a1[1], a2[1], a3[1], even16(xw[1]), odd16(xw[1]));
+                mma_w_by_tok<A_UNSIGNED>(c[i], a0[2], a1[2], a2[2], a3[2], even16(xw[2]), odd16(xw[2]));
+                mma_w_by_tok<A_UNSIGNED>(c2, a0[3], a1[3], a2[3], a3[3], even16(xw[3]), odd16(xw[3]));
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) c[i][k] = 0;
+                for (int k = 0; k < 4; ++k) c[i][k] += c2[k];
+                if (GROUPED) {
+                    // c[i][2h + j]: channel ch0 + 8h, token i*8 + 2t + j
+                    const __half *sbS = reinterpret_cast<const __half *>(st + Plan::kSB);
+                    const int32_t *rsS = reinterpret_cast<const int32_t *>(st + Plan::kRS);
+                    const __half *saS = reinterpret_cast<const __half *>(st + Plan::kSA);
+                    const __half *zaS = reinterpret_cast<const __half *>(st + Plan::kZA);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int rr = warp * 16 + g + 8 * h;
+                        const float sb = p.gb_cols == 1 ? sb_c[h] : __half2float(sbS[2 * rr + half]);
+                        const int rs = has_zero ? rsS[2 * rr + half] : 0;
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const int tk = i * 8 + 2 * t + j;
+                            const float sa = p.ga_cols == 1 ? sa_c[i][j] : __half2float(saS[2 * tk + half]);
+                            const int za = !has_zero ? 0 : (p.ga_cols == 1 ? za_c[i][j] : (int)__half2float(zaS[2 * tk + half]));
+                            const int32_t I = (c[i][2 * h + j] >> 8) - za * rs;
+                            acc[i][2 * h + j] = __fmaf_rn((float)I, __fmul_rn(sa, sb), acc[i][2 * h + j]);
+                            c[i][2 * h + j] = 0;
+                        }
+                    }
                 }
             }
         }
     }
     cp_async_wait<0>();
+
 #pragma unroll
-    for (int i = 0; i < MT; ++i) {
-        if (!p.grouped)
-            dequant_frag(c[i], acc[i], load_rowq(p, i * 16 + g, 0, has_zero),
-                         load_colq(p, n0 + warp * 8 + 2 * t, 0, has_zero));
-        const int col = n0 + warp * 8 + 2 * t;
-        float b0 = 0.f, b1 = 0.f;
-        if (p.bias) { b0 = __half2float(p.bias[col]); b1 = __half2float(p.bias[col + 1]); }
+    for (int i = 0; i < NT; ++i)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int r = i * 16 + g + 8 * h;
-            if (r < p.M) {
-                float v0 = acc[i][2 * h], v1 = acc[i][2 * h + 1];
-                if (p.bias) { v0 = __fadd_rn(v0, b0); v1 = __fadd_rn(v1, b1); }
-                store_pair(p.D, p.out_bf16, (long)r * p.N + col, v0, v1);
+            const int ch = ch0 + 8 * h;
+            const float bias = p.bias ? __half2float(p.bias[ch]) : 0.f;
+            const int rs = (!GROUPED && has_zero) ? p.b_rowsum[ch] : 0;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int tok = i * 8 + 2 * t + j;
+                float v = acc[i][2 * h + j];
+                if (!GROUPED) {
+                    const int32_t I = (c[i][2 * h + j] >> 8) - za_c[i][j] * rs;
+                    v = __fmaf_rn((float)I, __fmul_rn(sa_c[i][j], sb_c[h]), 0.0f);
+                }
+                if (p.bias) v = __fadd_rn(v, bias);
+                if (tok < p.M) {
+                    if (p.out_bf16) static_cast<__nv_bfloat16 *>(p.D)[(long)tok * p.N + ch] = __float2bfloat16_rn(v);
+                    else static_cast<__half *>(p.D)[(long)tok * p.N + ch] = __float2half_rn(v);
+                }
             }
         }
-    }
 }
 
 GemmParams make_params(const uint8_t *A, const uint8_t *B, const void *a_scale, const void *a_zero,
@@ -352,13 +464,20 @@ int launch_gemm_mma_tile(const uint8_t *A, const uint8_t *B, const void *a_scale
     return cuda_status(cudaGetLastError(), "gemm_tile launch");
 }
 
-template <int MT, bool U>
+template <int WARPS, int NT, bool U, bool G>
 static int launch_stream_t(const GemmParams &p, cudaStream_t stream) {
-    const int smem = SSTAGES * (SBN + MT * 16) * 128;
-    cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<MT, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    const int smem = SSTAGES * StreamPlan<WARPS, NT>::kStage;
+    auto kern = gemm_stream_kernel<WARPS, NT, U, G>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_status(e, "gemm_stream attribute");
-    gemm_stream_kernel<MT, U><<<(unsigned)(p.N / SBN), 128, smem, stream>>>(p);
+    kern<<<(unsigned)(p.N / (16 * WARPS)), WARPS * 32, smem, stream>>>(p);
     return cuda_status(cudaGetLastError(), "gemm_stream launch");
+}
+
+template <int WARPS, int NT>
+static int launch_stream_w(const GemmParams &p, bool u, cudaStream_t stream) {
+    if (p.grouped) return u ? launch_stream_t<WARPS, NT, true, true>(p, stream) : launch_stream_t<WARPS, NT, false, true>(p, stream);
+    return u ? launch_stream_t<WARPS, NT, true, false>(p, stream) : launch_stream_t<WARPS, NT, false, false>(p, stream);
 }
 
 int launch_gemm_stream(const uint8_t *A, const uint8_t *B, const void *a_scale, const void *a_zero,
@@ -366,8 +485,12 @@ int launch_gemm_stream(const uint8_t *A, const uint8_t *B, const void *a_scale, 
                        long M, long N, long K, long a_group, long b_group, int out_dtype,
                        cudaStream_t stream) {
     const GemmParams p = make_params(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype);
-    if (M <= 16) return a_zero ? launch_stream_t<1, true>(p, stream) : launch_stream_t<1, false>(p, stream);
-    return a_zero ? launch_stream_t<2, true>(p, stream) : launch_stream_t<2, false>(p, stream);
+    const bool u = a_zero != nullptr;
+    // 32-row CTAs unless that would be more than ~8 CTAs per SM; N is a multiple of 128
+    const bool wide = N / 32 > 8 * kNumSMs;
+    if (M <= 8) return wide ? launch_stream_w<4, 1>(p, u, stream) : launch_stream_w<2, 1>(p, u, stream);
+    if (M <= 16) return wide ? launch_stream_w<4, 2>(p, u, stream) : launch_stream_w<2, 2>(p, u, stream);
+    return wide ? launch_stream_w<4, 4>(p, u, stream) : launch_stream_w<2, 4>(p, u, stream);
 }
 
 // rowsum[n, g] = sum of signed nibbles of row n over K-group g.  One warp per (row, group chunk).

@@ -152,9 +152,24 @@ fht_inplace_kernel(uint4 *__restrict__ x, long total_chunks) {
     }
 }
 
-inline int grid_for(long total_chunks) {
-    long blocks = (total_chunks + kThreads - 1) / kThreads;
-    const long cap = (long)kNumSMs * 8;            // 8 resident CTAs of 256 threads per SM
+// One wave of resident CTAs (a multiple of the SM count); the grid-stride loop covers the rest.
+template <typename K>
+int grid_for(K kernel, long total_chunks) {
+    // resident CTAs per SM, remembered per kernel address (a handful of template instances)
+    static const void *known[16];
+    static int occ[16];
+    int per_sm = 0;
+    for (int i = 0; i < 16 && known[i]; ++i)
+        if (known[i] == reinterpret_cast<const void *>(kernel)) per_sm = occ[i];
+    if (per_sm == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0) != cudaSuccess || n < 1) n = 4;
+        per_sm = n;
+        for (int i = 0; i < 16; ++i)
+            if (!known[i]) { occ[i] = n; known[i] = reinterpret_cast<const void *>(kernel); break; }
+    }
+    long blocks = (total_chunks + (long)kThreads * kUnroll - 1) / ((long)kThreads * kUnroll);
+    const long cap = (long)kNumSMs * per_sm;
     if (blocks > cap) blocks = cap;
     return (int)(blocks < 1 ? 1 : blocks);
 }
@@ -164,11 +179,10 @@ inline int grid_for(long total_chunks) {
 int launch_quant_group_sym(const void *x, long rows, int gs, int hadamard, uint8_t *q,
                            void *scales, cudaStream_t stream) {
     const long chunks = rows * (gs / 8);
-    const int grid = grid_for(chunks);
     const uint4 *xi = static_cast<const uint4 *>(x);
     uint32_t *qo = reinterpret_cast<uint32_t *>(q);
     __half *so = static_cast<__half *>(scales);
-#define FLH_LAUNCH(LG, H) quant_group_sym_kernel<LG, H><<<grid, kThreads, 0, stream>>>(xi, qo, so, chunks)
+#define FLH_LAUNCH(LG, H) quant_group_sym_kernel<LG, H><<<grid_for(quant_group_sym_kernel<LG, H>, chunks), kThreads, 0, stream>>>(xi, qo, so, chunks)
     if (gs == 128) { if (hadamard) FLH_LAUNCH(7, true); else FLH_LAUNCH(7, false); }
     else if (gs == 64) { if (hadamard) FLH_LAUNCH(6, true); else FLH_LAUNCH(6, false); }
     else { if (hadamard) FLH_LAUNCH(5, true); else FLH_LAUNCH(5, false); }
@@ -178,11 +192,10 @@ int launch_quant_group_sym(const void *x, long rows, int gs, int hadamard, uint8
 
 int launch_fht_inplace(void *x, long rows, int n, cudaStream_t stream) {
     const long chunks = rows * (n / 8);
-    const int grid = grid_for(chunks);
     uint4 *xi = static_cast<uint4 *>(x);
-    if (n == 128) fht_inplace_kernel<7><<<grid, kThreads, 0, stream>>>(xi, chunks);
-    else if (n == 64) fht_inplace_kernel<6><<<grid, kThreads, 0, stream>>>(xi, chunks);
-    else fht_inplace_kernel<5><<<grid, kThreads, 0, stream>>>(xi, chunks);
+    if (n == 128) fht_inplace_kernel<7><<<grid_for(fht_inplace_kernel<7>, chunks), kThreads, 0, stream>>>(xi, chunks);
+    else if (n == 64) fht_inplace_kernel<6><<<grid_for(fht_inplace_kernel<6>, chunks), kThreads, 0, stream>>>(xi, chunks);
+    else fht_inplace_kernel<5><<<grid_for(fht_inplace_kernel<5>, chunks), kThreads, 0, stream>>>(xi, chunks);
     return cuda_status(cudaGetLastError(), "fht_inplace launch");
 }
 

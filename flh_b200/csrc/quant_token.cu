@@ -2,7 +2,8 @@
 // int4 quantiser and nibble packing.
 //
 // One CTA per token row, T = K/64 threads, every thread owns 64 values in registers at each step:
-//   pass 1  butterfly bits 0-5 on 64 consecutive inputs (eight 128-bit loads per thread);
+//   pass 1  the row arrives in shared memory by coalesced 16-byte cp.async; butterfly bits 0-5 on 64
+//           consecutive inputs per thread (eight 128-bit shared loads);
 //   pass 2  bits 6..6+B2-1 after one transpose through padded shared memory;
 //   pass 3  bits 12..12+B3-1 (K > 4096 only) after a second transpose;
 //   factor  the kfac x kfac +-1 matrix across the K/kfac-long chunks (K = 11008, 14336, 28672 ...),
@@ -60,6 +61,16 @@ __device__ __forceinline__ int phys(int chunk, int e) {
     return 68 * chunk + e;
 }
 
+__device__ __forceinline__ float min3(float a, float b, float c) {
+    float r;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 __device__ __forceinline__ float warp_min(float v) {
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, s));
@@ -88,8 +99,9 @@ struct TokenParams {
 };
 
 // B2/B3: bits handled by passes 2/3.  FACTOR: kfac > 1.  HAD: transform at all.
+// With the transform, K <= 4096 and no factor stage mean at most 64 working threads: ask for ten CTAs per SM.
 template <int B2, int B3, bool FACTOR, bool HAD>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__((HAD && B3 == 0 && !FACTOR) ? 64 : 512, (HAD && B3 == 0 && !FACTOR) ? 10 : 1)
 quant_token_asym_kernel(const TokenParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     float *buf = reinterpret_cast<float *>(smem_raw);
@@ -103,12 +115,25 @@ quant_token_asym_kernel(const TokenParams p) {
     float x[64];
 
     // ---------------- pass 1: load 64 consecutive inputs, bits 0-5 -------------------------
+    // The row is copied into shared memory with coalesced 16-byte cp.async (chunk c of 128-byte line L
+    // lands at chunk c ^ (L & 7), so that a thread reading its own line is conflict-free), then every
+    // thread picks up its 64 consecutive values.
+    {
+        const uint16_t *xrow = static_cast<const uint16_t *>(p.x) + row * p.ld;
+        for (int ch = t; ch < (p.n >> 3); ch += blockDim.x) {
+            const int line = ch >> 3, c = ch & 7;
+            const uint32_t dst = smem_u32(smem_raw + ((line << 3) + (c ^ (line & 7))) * 16);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(xrow + ch * 8));
+        }
+        asm volatile("cp.async.commit_group;" ::);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+    }
     if (active) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(
-            static_cast<const uint16_t *>(p.x) + row * p.ld + 64l * t);
         uint4 v[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) v[c] = ldg_v4(src + c);
+        for (int c = 0; c < 8; ++c)
+            v[c] = *reinterpret_cast<const uint4 *>(smem_raw + ((t << 3) + (c ^ (t & 7))) * 16);
         if (p.bf16) {
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -133,6 +158,7 @@ quant_token_asym_kernel(const TokenParams p) {
         }
         if (HAD) bfly_regs<6>(x);
     }
+    __syncthreads();      // the staged row is consumed; its space is reused below
 
     // element index of register idx once all passes are done: base + stride pattern below
     // (computed per section); codes are staged at cb[element index].
@@ -255,7 +281,7 @@ quant_token_asym_kernel(const TokenParams p) {
     float vmin = 0.0f, vmax = 0.0f;
     if (active) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) { vmin = fminf(vmin, x[i]); vmax = fmaxf(vmax, x[i]); }
+        for (int i = 0; i < 64; i += 2) { vmin = min3(vmin, x[i], x[i + 1]); vmax = max3(vmax, x[i], x[i + 1]); }
     }
     vmin = warp_min(vmin); vmax = warp_max(vmax);
     if (lane == 0) { red[0][warp] = vmin; red[1][warp] = vmax; }
@@ -286,25 +312,38 @@ quant_token_asym_kernel(const TokenParams p) {
         const float lo = -zf, hi = 15.0f - zf;
         const float magic = 12582912.0f;
         const int zi = (int)zf;
+        const uint64_t rd2 = pack2(rd, rd), magic2 = pack2(magic, magic);
+        // Without clipping no element lies below the row minimum, and rint(z * rd) >= -zero follows
+        // from the monotonicity of the product and of rint: only the upper clamp can ever act.
+        const bool need_lo = p.clip != 1.0f;
 #pragma unroll
-        for (int idx = 0; idx < 64; ++idx) {
-            float v = __fmul_rn(x[idx], rd);
-            v = fminf(fmaxf(v, lo), hi);
-            const int code = (__float_as_int(__fadd_rn(v, magic)) + zi) & 15;
-            int e;
-            if (HAD && FACTOR) {
-                const int v4 = idx >> 4, u = (idx >> 1) & 7, b = idx & 1;
-                e = (4 * f_kb + v4) * p.P + 2 * f_w + b + (p.P >> 3) * u;
-            } else if (HAD && B3 > 0) {
-                const int m = idx & ((1 << B3) - 1), r = idx >> B3;
-                e = ebase + m * 4096 + r * (64 << B3);
-            } else if (HAD && B2 > 0) {
-                const int m = idx & ((1 << B2) - 1), r = idx >> B2;
-                e = ebase + m * 64 + (r << B2);
-            } else {
-                e = ebase + idx;
+        for (int idx = 0; idx < 64; idx += 2) {
+            float v0, v1;
+            unpack2(mul2(pack2(x[idx], x[idx + 1]), rd2), v0, v1);
+            v0 = fminf(v0, hi); v1 = fminf(v1, hi);
+            if (need_lo) { v0 = fmaxf(v0, lo); v1 = fmaxf(v1, lo); }
+            float r0, r1;
+            unpack2(add2(pack2(v0, v1), magic2), r0, r1);
+            // low byte of (bits + zero) = rint(v) + zero, already in 0..15
+            const int code[2] = {__float_as_int(r0) + zi, __float_as_int(r1) + zi};
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int id = idx + u;
+                int e;
+                if (HAD && FACTOR) {
+                    const int v4 = id >> 4, uu = (id >> 1) & 7, b = id & 1;
+                    e = (4 * f_kb + v4) * p.P + 2 * f_w + b + (p.P >> 3) * uu;
+                } else if (HAD && B3 > 0) {
+                    const int m = id & ((1 << B3) - 1), r = id >> B3;
+                    e = ebase + m * 4096 + r * (64 << B3);
+                } else if (HAD && B2 > 0) {
+                    const int m = id & ((1 << B2) - 1), r = id >> B2;
+                    e = ebase + m * 64 + (r << B2);
+                } else {
+                    e = ebase + id;
+                }
+                cb[e] = (uint8_t)code[u];
             }
-            cb[e] = (uint8_t)code;
         }
     }
     __syncthreads();
@@ -317,7 +356,7 @@ quant_token_asym_kernel(const TokenParams p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t tt = w[j] | (w[j] >> 4);
-            o[j] = (tt & 0xFFu) | ((tt >> 8) & 0xFF00u);
+            o[j] = __byte_perm(tt, 0, 0x4420);            // bytes 0 and 2 -> a 16-bit pair
         }
         qrow[c] = make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16));
     }
@@ -326,11 +365,11 @@ quant_token_asym_kernel(const TokenParams p) {
 template <int B2, int B3, bool FACTOR, bool HAD>
 int launch_one(const TokenParams &p, long M, cudaStream_t stream) {
     const int threads = ((p.T + 31) / 32) * 32;
-    size_t smem = (size_t)p.n;                                   // code staging
+    size_t smem = (size_t)p.n * 2;                               // staged input row (codes reuse it)
     if (HAD && (B2 > 0 || FACTOR)) {
         smem = ((size_t)p.T * 70 + 64) * 4;
         if (FACTOR) smem += (size_t)p.kfac * ((p.kfac + 31) / 32) * 4;
-        if (smem < (size_t)p.n) smem = p.n;
+        if (smem < (size_t)p.n * 2) smem = (size_t)p.n * 2;
     }
     auto kern = quant_token_asym_kernel<B2, B3, FACTOR, HAD>;
     if (smem > 48 * 1024) {

@@ -1,0 +1,161 @@
+"""Llama-shaped W4A4 decoder on the flh_b200 hot path (the caller either side of the kernels).
+
+Mirrors the wiring of FLH_LlamaAttention / FLH_LlamaMLP (flh/quantized_model/modeling_llama.py:374-470,
+522-526): RMSNorm (weight folded into the next linear) -> activation quantiser -> packed linears; RoPE;
+f16 attention with a KV cache; quantiser -> o_proj; quantiser -> gate/up -> SiLU*up -> quantiser ->
+down_proj.  Differences, all on the host side: q/k/v and gate/up are merged into one GEMM each (one
+quantiser output feeds them), and the linears can be tensor-parallel (flh_b200.tp).
+
+Two activation modes:
+  "group_sym"   FLH's CUDA contract: per-(token, 128) symmetric int4, group-128 weight scales, no online
+                transform (FLH builds every ActQuantizer with use_hadamard=False, :317-319, 478-480);
+  "token_asym"  the fake_quant wiring (fake_quant/main.py:31-35, 63-84): per-token asymmetric int4,
+                per-channel symmetric weights, full-width online Hadamard in front of down_proj.
+Weights are random (no checkpoint in reach): `random_init` draws packed codes and scales directly on the
+device; `from_float_layer` rotates, RTN-quantises and packs real float weights (tests).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import _CUDA
+from .nn import ActQuantizer, LinearFLH
+from .tp import ColumnParallelLinearFLH, RowParallelLinearFLH
+
+
+@dataclass
+class DecoderConfig:
+    hidden: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 32
+    ffn: int = 11008
+    n_layers: int = 32
+    vocab: int = 32000
+    rope_theta: float = 10000.0
+    eps: float = 1e-5
+    act_mode: str = "group_sym"          # or "token_asym"
+    tp: int = 1
+
+    @property
+    def head_dim(self):
+        return self.hidden // self.n_heads
+
+
+LLAMA2_7B = dict(hidden=4096, n_heads=32, n_kv_heads=32, ffn=11008, n_layers=32)
+LLAMA3_70B = dict(hidden=8192, n_heads=64, n_kv_heads=8, ffn=28672, n_layers=80, rope_theta=500000.0)
+
+
+def _random_linear(k, n, cfg, device, gen):
+    """A LinearFLH with uniform random int4 codes and scales ~ U(0.005, 0.02)."""
+    gs = 128 if cfg.act_mode == "group_sym" else -1
+    lin = LinearFLH(k, n, dtype=torch.float16, device=device, group_size=gs, in_group_size=128)
+    lin.w_packed.copy_(torch.randint(0, 256, lin.w_packed.shape, dtype=torch.uint8, device=device, generator=gen))
+    lin.w_scale.copy_((torch.rand(lin.w_scale.shape, device=device, generator=gen) * 0.015 + 0.005).half() / math.sqrt(k / 64))
+    return lin
+
+
+class RMSNorm(torch.nn.Module):
+    """flh/nn/normalization.py: x * rsqrt(mean(x^2) + eps) * weight (weight is 1 once folded)."""
+
+    def __init__(self, dim, eps):
+        super().__init__()
+        self.eps = eps
+        self.weight = torch.nn.Parameter(torch.ones(dim, dtype=torch.float16), requires_grad=False)
+
+    def forward(self, x):
+        v = x.float()
+        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype) * self.weight
+
+
+def rope(x, pos, theta):
+    """Rotary embedding, half-split convention (HF Llama): x [B, S, H, D], pos [S]."""
+    d = x.shape[-1]
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=x.device, dtype=torch.float32) / d))
+    ang = pos.float()[:, None] * inv[None, :]
+    cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+    x1, x2 = x.float()[..., : d // 2], x.float()[..., d // 2:]
+    return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).to(x.dtype)
+
+
+class DecoderLayer(torch.nn.Module):
+    def __init__(self, cfg: DecoderConfig, device, gen=None, group=None):
+        super().__init__()
+        self.cfg, self.group = cfg, group
+        tp = cfg.tp
+        hd = cfg.head_dim
+        self.nh, self.nkv = cfg.n_heads // tp, max(cfg.n_kv_heads // tp, 1)
+        sym = cfg.act_mode == "group_sym"
+        mk = lambda had: ActQuantizer(bits=4, group_size=128 if sym else -1, sym=sym, use_hadamard=had, packed_output=True)
+        self.q_in, self.q_attn, self.q_mlp = mk(False), mk(False), mk(False)
+        self.q_down = mk(not sym)        # token_asym: full-width online transform in front of down_proj
+        self.norm1, self.norm2 = RMSNorm(cfg.hidden, cfg.eps).to(device), RMSNorm(cfg.hidden, cfg.eps).to(device)
+        if gen is not None:              # random weights, already per-rank shards
+            self.qkv = ColumnParallelLinearFLH(_random_linear(cfg.hidden, (self.nh + 2 * self.nkv) * hd, cfg, device, gen), group)
+            self.o = RowParallelLinearFLH(_random_linear(self.nh * hd, cfg.hidden, cfg, device, gen), group)
+            self.gate_up = ColumnParallelLinearFLH(_random_linear(cfg.hidden, 2 * cfg.ffn // tp, cfg, device, gen), group)
+            self.down = RowParallelLinearFLH(_random_linear(cfg.ffn // tp, cfg.hidden, cfg, device, gen), group)
+
+    def forward(self, x, pos, cache=None):
+        """x [B, S, hidden] f16; pos [S] absolute positions; cache = (k, v) [B, nkv, T, D] with a write
+        cursor `cache[2]`, or None for a cache-less prefill."""
+        cfg = self.cfg
+        B, S, _ = x.shape
+        hd = cfg.head_dim
+        s, z, q = self.q_in(self.norm1(x))
+        qkv = self.qkv(q, s, z)
+        qh, kh, vh = qkv.split((self.nh * hd, self.nkv * hd, self.nkv * hd), dim=-1)
+        qh = rope(qh.view(B, S, self.nh, hd), pos, cfg.rope_theta).transpose(1, 2)
+        kh = rope(kh.view(B, S, self.nkv, hd), pos, cfg.rope_theta).transpose(1, 2)
+        vh = vh.view(B, S, self.nkv, hd).transpose(1, 2)
+        if cache is not None:
+            kc, vc, cur = cache
+            kc[:, :, cur:cur + S] = kh
+            vc[:, :, cur:cur + S] = vh
+            kh, vh = kc[:, :, :cur + S], vc[:, :, :cur + S]
+        att = F.scaled_dot_product_attention(qh, kh, vh, is_causal=(S > 1), enable_gqa=self.nh != self.nkv)
+        att = att.transpose(1, 2).reshape(B, S, self.nh * hd)
+        s, z, q = self.q_attn(att)
+        x = x + self.o(q, s, z)
+        s, z, q = self.q_mlp(self.norm2(x))
+        gu = self.gate_up(q, s, z)
+        g, u = gu.chunk(2, dim=-1)
+        a = F.silu(g) * u
+        s, z, q = self.q_down(a)
+        return x + self.down(q, s, z)
+
+
+class Decoder(torch.nn.Module):
+    """Embedding -> layers -> final norm -> f16 lm_head (the head stays f16 in FLH, :1032-1046)."""
+
+    def __init__(self, cfg: DecoderConfig, device, seed=0, group=None, with_head=True):
+        super().__init__()
+        self.cfg, self.device = cfg, device
+        gen = torch.Generator(device=device).manual_seed(seed + (dist.get_rank() if dist.is_initialized() else 0))
+        self.embed = torch.nn.Embedding(cfg.vocab, cfg.hidden, device=device, dtype=torch.float16)
+        self.layers = torch.nn.ModuleList(DecoderLayer(cfg, device, gen, group) for _ in range(cfg.n_layers))
+        self.norm = RMSNorm(cfg.hidden, cfg.eps).to(device)
+        self.head = torch.nn.Linear(cfg.hidden, cfg.vocab, bias=False, device=device, dtype=torch.float16) if with_head else None
+
+    def new_cache(self, batch, max_len):
+        c = self.cfg
+        nkv = max(c.n_kv_heads // c.tp, 1)
+        return [[torch.zeros(batch, nkv, max_len, c.head_dim, dtype=torch.float16, device=self.device),
+                 torch.zeros(batch, nkv, max_len, c.head_dim, dtype=torch.float16, device=self.device), 0]
+                for _ in range(c.n_layers)]
+
+    @torch.no_grad()
+    def forward(self, ids, cache=None, start=0):
+        B, S = ids.shape
+        x = self.embed(ids)
+        pos = torch.arange(start, start + S, device=ids.device)
+        for i, layer in enumerate(self.layers):
+            if cache is not None:
+                cache[i][2] = start
+            x = layer(x, pos, None if cache is None else cache[i])
+        x = self.norm(x)
+        return x if self.head is None else self.head(x[:, -1:])

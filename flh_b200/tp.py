@@ -1,0 +1,87 @@
+"""Megatron-style tensor parallelism for packed W4A4 linears (one process per GPU).
+
+The reference has no multi-GPU code; the sharding follows its checkpoint layout (LinearFLH buffers,
+flh/nn/linear.py:20-30) so that a shard is a slice of the single-GPU tensors:
+
+  column-parallel (q/k/v, gate/up)  rows  [r N/tp, (r+1) N/tp) of w_packed [N, K/2] and w_scale;
+                                    replicated activations, no collective;
+  row-parallel (o_proj, down_proj)  columns [r K/tp, (r+1) K/tp) of every row (K/tp a multiple of 128);
+                                    each rank quantises ITS slice of the activations (per-(token, shard)
+                                    scale / zero-point; a full-width Hadamard becomes block-diagonal per
+                                    shard), runs the GEMM and the f16 partial outputs are summed with one
+                                    all-reduce — the only collective of the path.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .nn import LinearFLH
+
+
+def _clone_meta(lin: LinearFLH, in_features: int, out_features: int) -> LinearFLH:
+    return LinearFLH(in_features, out_features, bias=lin.bias is not None, dtype=lin.w_scale.dtype,
+                     device=lin.w_packed.device, dual_hadamard=lin.dual_hadamard, in_group_size=lin.in_group_size,
+                     out_group_size=lin.out_group_size, no_hadamard=lin.no_hadamard, group_size=lin.weight_group_size)
+
+
+def shard_column(lin: LinearFLH, rank: int, world: int) -> LinearFLH:
+    """Rows [rank*N/world, (rank+1)*N/world) of the weight."""
+    N, K = lin.out_features, lin.in_features
+    assert N % world == 0 and (N // world) % 128 == 0, "N / tp must be a multiple of 128"
+    n = N // world
+    out = _clone_meta(lin, K, n)
+    out.w_packed.copy_(lin.w_packed.view(N, K // 2)[rank * n:(rank + 1) * n].reshape(-1))
+    out.w_scale.copy_(lin.w_scale[rank * n:(rank + 1) * n])
+    out.w_zero.copy_(lin.w_zero[rank * n:(rank + 1) * n])
+    if lin.bias is not None:
+        out.bias.copy_(lin.bias[rank * n:(rank + 1) * n])
+    return out
+
+
+def shard_row(lin: LinearFLH, rank: int, world: int) -> LinearFLH:
+    """Columns [rank*K/world, (rank+1)*K/world) of every weight row.  The bias stays on rank 0 only, so
+    that the all-reduced sum carries it once."""
+    N, K = lin.out_features, lin.in_features
+    assert K % world == 0 and (K // world) % 128 == 0, "K / tp must be a multiple of 128"
+    k = K // world
+    out = _clone_meta(lin, k, N)
+    out.w_packed.copy_(lin.w_packed.view(N, K // 2)[:, rank * k // 2:(rank + 1) * k // 2].reshape(-1))
+    g = lin.w_scale.shape[1]
+    if g > 1:
+        gs = g // world
+        out.w_scale.copy_(lin.w_scale[:, rank * gs:(rank + 1) * gs])
+        out.w_zero.copy_(lin.w_zero[:, rank * gs:(rank + 1) * gs])
+    else:
+        out.w_scale.copy_(lin.w_scale)
+        out.w_zero.copy_(lin.w_zero)
+    if lin.bias is not None:
+        out.bias.copy_(lin.bias if rank == 0 else torch.zeros_like(lin.bias))
+    return out
+
+
+class ColumnParallelLinearFLH(torch.nn.Module):
+    def __init__(self, shard: LinearFLH, group=None, gather_output: bool = False):
+        super().__init__()
+        self.shard, self.group, self.gather_output = shard, group, gather_output
+
+    def forward(self, x, a_scale=None, a_zero=None, **kw):
+        y = self.shard(x, a_scale, a_zero, **kw)
+        if self.gather_output and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            parts = [torch.empty_like(y) for _ in range(dist.get_world_size(self.group))]
+            dist.all_gather(parts, y.contiguous(), group=self.group)
+            y = torch.cat(parts, dim=-1)
+        return y
+
+
+class RowParallelLinearFLH(torch.nn.Module):
+    def __init__(self, shard: LinearFLH, group=None):
+        super().__init__()
+        self.shard, self.group = shard, group
+
+    def forward(self, x, a_scale=None, a_zero=None, **kw):
+        """x, a_scale, a_zero: this rank's slice of the quantised activations."""
+        y = self.shard(x, a_scale, a_zero, **kw)
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        return y

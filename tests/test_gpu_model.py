@@ -1,0 +1,42 @@
+"""The Llama-shaped W4A4 decoder on the CUDA kernels against its PyTorch twin (forward_origin /
+forward_torch on the same packed weights), and the KV-cache decode step against the prefill."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _twin(monkeypatch):
+    from flh_b200.nn import ActQuantizer, LinearFLH
+    monkeypatch.setattr(ActQuantizer, "forward", lambda self, x: ActQuantizer.forward_origin(self, x))
+    monkeypatch.setattr(LinearFLH, "forward",
+                        lambda self, x, a_scale=None, a_zero=None, **kw: LinearFLH.forward_torch(self, x, a_scale, a_zero).half())
+
+
+@pytest.mark.parametrize("mode", ["group_sym", "token_asym"])
+def test_decoder_matches_pytorch_twin(cuda, monkeypatch, mode):
+    from flh_b200.model import Decoder, DecoderConfig
+    cfg = DecoderConfig(hidden=256, n_heads=4, n_kv_heads=2, ffn=512, n_layers=2, vocab=128, act_mode=mode)
+    m = Decoder(cfg, torch.device("cuda"), seed=3)
+    ids = torch.randint(0, 128, (2, 40), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    y = m(ids).float()
+    with monkeypatch.context() as mp:
+        _twin(mp)
+        y_ref = m(ids).float()
+    # whole-model tolerance: 2 % of the logit scale (f16 accumulation, and the rare activation code that
+    # flips by one step between the binary16/binary32 kernels and the float64/float32 twins)
+    err = (y - y_ref).abs().max() / y_ref.abs().max()
+    assert err < 2e-2, err
+
+
+def test_decode_step_matches_prefill(cuda):
+    from flh_b200.model import Decoder, DecoderConfig
+    cfg = DecoderConfig(hidden=256, n_heads=4, n_kv_heads=4, ffn=512, n_layers=2, vocab=128, act_mode="group_sym")
+    m = Decoder(cfg, torch.device("cuda"), seed=5)
+    ids = torch.randint(0, 128, (3, 17), device="cuda", generator=torch.Generator(device="cuda").manual_seed(2))
+    full = m(ids).float()                              # logits of the last position, no cache
+    cache = m.new_cache(3, 32)
+    m(ids[:, :16], cache=cache, start=0)
+    step = m(ids[:, 16:], cache=cache, start=16).float()
+    err = (full - step).abs().max() / full.abs().max()
+    assert err < 2e-2, err

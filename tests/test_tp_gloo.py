@@ -1,0 +1,98 @@
+"""Tensor-parallel sharding and the row-parallel all-reduce on CPU: two gloo ranks, with the GEMM
+served by the CPU oracle in place of the CUDA library (the sharding, the scale/zero bookkeeping and
+the collective are what is under test)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _oracle_backend():
+    """Stand-ins for flh_b200._CUDA entry points, computing with the CPU oracle on CPU tensors."""
+    from oracle import oracle as O
+
+    def gemm(A, B, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=None, out_dtype=torch.float16, algo=0, out=None):
+        d = O.gemm_i4_dequant(A.numpy(), B.numpy(), A_scale.numpy(), B_scale.numpy(),
+                              a_zero=None if A_zero is None else A_zero.numpy(),
+                              bias=None if bias is None else bias.numpy())
+        return torch.from_numpy(d.copy())
+
+    def rowsum(B, group):
+        return torch.from_numpy(O.weight_rowsum(B.numpy(), group))
+
+    return gemm, rowsum
+
+
+def _worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import flh_b200
+        from flh_b200.nn import LinearFLH
+        from flh_b200.tp import ColumnParallelLinearFLH, RowParallelLinearFLH, shard_column, shard_row
+        from oracle import oracle as O
+        gemm, rowsum = _oracle_backend()
+        flh_b200._CUDA.gemm_i4_dequant = gemm
+        flh_b200._CUDA.weight_rowsum = rowsum
+
+        g = torch.Generator().manual_seed(7)                 # same weights on every rank
+        K, N, M = 512, 256, 5
+        for gs, asym in ((128, False), (-1, True)):
+            lin = torch.nn.Linear(K, N, bias=True)
+            lin.weight.data = torch.randn(N, K, generator=g) * 0.02
+            lin.bias.data = torch.randn(N, generator=g) * 0.1
+            full = LinearFLH.from_float(lin.half(), weight_group_size=gs, in_group_size=128)
+            x = torch.randn(M, K, generator=g).half().numpy()
+            if asym:
+                q, s, z = O.quant_token_asym(x, False)
+                qs = [O.quant_token_asym(np.ascontiguousarray(x[:, r * K // world:(r + 1) * K // world]), False) for r in range(world)]
+                args_full = (torch.from_numpy(q), torch.from_numpy(s).view(M, 1), torch.from_numpy(z).view(M, 1))
+                args_mine = tuple(torch.from_numpy(a).view(M, -1) for a in qs[rank])
+            else:
+                q, s = O.quant_group_sym(x.reshape(-1, 128), False)
+                q, s = q.reshape(M, K // 2), s.reshape(M, K // 128)
+                kk = K // world
+                args_full = (torch.from_numpy(q), torch.from_numpy(s), None)
+                args_mine = (torch.from_numpy(q[:, rank * kk // 2:(rank + 1) * kk // 2].copy()),
+                             torch.from_numpy(s[:, rank * kk // 128:(rank + 1) * kk // 128].copy()), None)
+            y_full = full(*args_full)
+
+            # column-parallel: the gathered shards are the full output, bit for bit
+            col = ColumnParallelLinearFLH(shard_column(full, rank, world), gather_output=True)
+            y_col = col(*args_full)
+            assert torch.equal(y_col.view(torch.int16), y_full.view(torch.int16)), "column-parallel"
+
+            # row-parallel: all-reduced f16 partials == the f16 sum of the two partials, and close to
+            # the single-device result
+            row = RowParallelLinearFLH(shard_row(full, rank, world))
+            part = row.shard(*args_mine)
+            parts = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(parts, part)
+            y_row = row(*args_mine)
+            want = (parts[0].float() + parts[1].float()).half()
+            assert torch.equal(y_row.view(torch.int16), want.view(torch.int16)), "row-parallel sum"
+            if not asym:    # same quantised activations as the full layer: only the summation order differs
+                err = (y_row.float() - y_full.float()).abs().max() / y_full.float().abs().max()
+                assert err < 2e-3, f"row-parallel vs single device: {err}"
+        if rank == 0:
+            open(os.path.join(tmp, "ok"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_column_and_row_parallel_two_gloo_ranks(tmp_path):
+    port = _free_port()
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok").exists()
