@@ -1,10 +1,13 @@
 // int4 x int4 GEMM with fused dequantisation on the 5th-generation tensor cores.
 //
 //   TMA (cp.async.bulk.tensor.2d)  packed int4 tiles of A [128 x 64 B] and B [BN x 64 B] -> smem ring
-//   4 converter warps              nibbles -> int8 (x16, see below) written in the K-major
+//   6 converter warps              nibbles -> int8 (x16, see below) written in the K-major
 //                                  128-byte-swizzled layout tcgen05 reads, fence.proxy.async
 //   1 elected thread               tcgen05.mma.cta_group::1.kind::i8, int32 accumulators in TMEM
-//   4 epilogue warps               tcgen05.ld, dequantise (per 128-K group or once), f16/bf16 store
+//   1-2 epilogue warpgroups        tcgen05.ld, dequantise (per 128-K group or once), f16/bf16 store
+// The kernel is persistent (one CTA per SM walks the tile list) and the accumulator is double-buffered
+// in TMEM, so the epilogue of one tile or K-group overlaps the tensor-core work of the next;
+// setmaxnreg moves registers from the producer/converter warps to the epilogue warps.
 //
 // There is no int4 MMA kind on sm_100, so the expansion to int8 happens in shared memory.  It is
 // exact and needs no sign extension: (w << 4) & 0xF0F0F0F0 and w & 0xF0F0F0F0 leave each nibble in
@@ -26,7 +29,6 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 128;                 // int8 elements per stage = one 128-byte swizzle row
-constexpr int kConvWarp0 = 2, kEpiWarp0 = 6, kThreads = 320;
 
 __device__ int g_status[4];             // [0] = first error code, [1] = block, [2] = kb
 
@@ -109,7 +111,12 @@ struct TcParams {
     int M, N, K;
     int ga_cols, gb_cols;
     int out_bf16;
+    int num_tiles, m_blocks;
 };
+
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (and TMEM owner), warps 2..7 = converters,
+// then one epilogue warpgroup per 128 output columns.
+constexpr int kNonEpiThreads = 256, kConvThreads = 192, kConvTid0 = 64;
 
 template <int BN>
 struct SmemPlan {
@@ -118,9 +125,10 @@ struct SmemPlan {
     static constexpr int kPkStage = (BM + BN) * (BK / 2);     // packed bytes
     static constexpr int kExpOff = 0;
     static constexpr int kPkOff = kStages * kExpStage;
-    static constexpr int kAuxOff = kPkOff + kStages * kPkStage;   // sb/rs/bias staging: 4 x BN x 4 B
-    static constexpr int kBarOff = kAuxOff + 4 * BN * 4;
+    static constexpr int kAuxOff = kPkOff + kStages * kPkStage;   // weight scales [2][BN] f32, row sums [2][BN] s32, bias [BN] f32
+    static constexpr int kBarOff = kAuxOff + 5 * BN * 4;
     static constexpr int kBytes = kBarOff + 256 + 1024;           // + slack to align the base to 1024
+    static constexpr int kEpiRegs = BN == 256 ? 192 : 232;        // registers per epilogue thread after setmaxnreg
 };
 
 __device__ __forceinline__ void store_row_chunk(void *D, bool bf16, long off, const float (&v)[32]) {
@@ -149,12 +157,17 @@ __device__ __forceinline__ void store_row_chunk(void *D, bool bf16, long off, co
     }
 }
 
+// Persistent: CTA b works on output tiles b, b + gridDim.x, ... (row blocks fastest, so the CTAs that
+// run together share the same weight columns).  Barrier phases and the TMEM accumulator buffer are
+// driven by running counters: `it` counts 128-K stages, `u` counts accumulator uses (one per K-block
+// with group scales, one per tile otherwise); buffer u & 1 is filled while buffer (u - 1) & 1 drains.
 template <int BN, bool GROUPED, bool A_UNSIGNED>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kNonEpiThreads + BN, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const TcParams p) {
     using Plan = SmemPlan<BN>;
     constexpr int S = Plan::kStages;
+    constexpr int kTmemCols = 2 * BN;
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -171,23 +184,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     volatile int *abort_flag = reinterpret_cast<volatile int *>(sm + Plan::kBarOff + 8 * 20 + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int KB = p.K / BK;
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(pk_full(s), 1);
-            mbar_init(pk_empty(s), 128);
-            mbar_init(ex_full(s), 128);
+            mbar_init(pk_empty(s), kConvThreads);
+            mbar_init(ex_full(s), kConvThreads);
             mbar_init(ex_empty(s), 1);
         }
-        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 128); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), BN); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -195,175 +207,199 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < KB; ++kb) {
-                const int s = kb % S;
-                if (!mbar_wait(pk_empty(s), ((kb / S) & 1) ^ 1, abort_flag, 1)) break;
-                mbar_expect_tx(pk_full(s), Plan::kPkStage);
-                const uint32_t dst = base + Plan::kPkOff + s * Plan::kPkStage;
-                tma_load_2d(dst, &map_a, kb * (BK / 2), m0, pk_full(s));
-                tma_load_2d(dst + BM * (BK / 2), &map_b, kb * (BK / 2), n0, pk_full(s));
-                issued = kb + 1;
-            }
-            if (*abort_flag) {
-                // let the copies already issued land before the CTA leaves
-                for (int kb = issued > S ? issued - S : 0; kb < issued; ++kb) {
-                    const uint64_t t0 = gtimer();
-                    while (!mbar_try(pk_full(kb % S), (kb / S) & 1) && gtimer() - t0 < 100000000ull) {}
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = (2u << 4) | ((A_UNSIGNED ? 0u : 1u) << 7) | (1u << 10) |
-                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            for (int kb = 0; kb < KB; ++kb) {
-                const int s = kb % S;
-                const int buf = GROUPED ? (kb & 1) : 0;
-                if (GROUPED && kb >= 2) {
-                    if (!mbar_wait(acc_empty(buf), ((kb >> 1) & 1) ^ 1, abort_flag, 2)) break;
-                }
-                if (!mbar_wait(ex_full(s), (kb / S) & 1, abort_flag, 3)) break;
-                tc_fence_after();
-                const uint32_t a_addr = base + Plan::kExpOff + s * Plan::kExpStage;
-                const uint64_t adesc = make_smem_desc(a_addr), bdesc = make_smem_desc(a_addr + BM * BK);
-#pragma unroll
-                for (int k4 = 0; k4 < BK / 32; ++k4) {
-                    const uint32_t accum = GROUPED ? (k4 > 0) : (kb > 0 || k4 > 0);
-                    tc_mma_i8(tmem + buf * BN, adesc + 2 * k4, bdesc + 2 * k4, idesc, accum);
-                }
-                tc_commit(ex_empty(s));
-                if (GROUPED || kb == KB - 1) tc_commit(acc_full(buf));
-            }
-        }
-    } else if (warp < kEpiWarp0) {
-        // ------------------------------------------------------------ int4 -> int8 converters
-        const int ct = tid - kConvWarp0 * 32;          // 0..127
-        for (int kb = 0; kb < KB; ++kb) {
-            const int s = kb % S;
-            if (!mbar_wait(pk_full(s), (kb / S) & 1, abort_flag, 4)) break;
-            if (!mbar_wait(ex_empty(s), ((kb / S) & 1) ^ 1, abort_flag, 5)) break;
-            const uint8_t *pk = sm + Plan::kPkOff + s * Plan::kPkStage;
-            uint8_t *ex = sm + Plan::kExpOff + s * Plan::kExpStage;
-            constexpr int kChunks = (BM + BN) * 4;
-#pragma unroll 4
-            for (int ch = ct; ch < kChunks; ch += 128) {
-                const int row = ch >> 2, c = ch & 3;     // row over A rows then B rows
-                const uint4 w = *reinterpret_cast<const uint4 *>(pk + row * 64 + c * 16);
-                uint4 e, o;
-                e.x = (w.x << 4) & 0xF0F0F0F0u; e.y = (w.y << 4) & 0xF0F0F0F0u;
-                e.z = (w.z << 4) & 0xF0F0F0F0u; e.w = (w.w << 4) & 0xF0F0F0F0u;
-                o.x = w.x & 0xF0F0F0F0u; o.y = w.y & 0xF0F0F0F0u; o.z = w.z & 0xF0F0F0F0u; o.w = w.w & 0xF0F0F0F0u;
-                uint8_t *dst = ex + row * 128;           // the B tile follows the A tile: (row - BM) * 128 + BM * 128
-                const int sw = row & 7;
-                *reinterpret_cast<uint4 *>(dst + (((2 * c) ^ sw) << 4)) = e;
-                *reinterpret_cast<uint4 *>(dst + (((2 * c + 1) ^ sw) << 4)) = o;
-            }
-            fence_proxy_async();
-            mbar_arrive(ex_full(s));
-            mbar_arrive(pk_empty(s));
-        }
-    } else {
-        // ------------------------------------------------------------ epilogue
-        const int et = tid - kEpiWarp0 * 32;            // 0..127
-        const int wq = warp & 3;                         // TMEM lane quarter this warp may read
-        const int row = m0 + wq * 32 + lane;
-        const int rowc = row < p.M ? row : p.M - 1;
-        float *sbuf = reinterpret_cast<float *>(sm + Plan::kAuxOff);        // [2][BN] weight scales
-        int *rbuf = reinterpret_cast<int *>(sm + Plan::kAuxOff + 2 * BN * 4); // [2][BN] weight row sums
-        const bool has_zero = p.a_zero != nullptr;
-        const uint32_t tlane = tmem + ((uint32_t)(wq * 32) << 16);
-
-        if (GROUPED) {
-            const int G = KB;
-            float acc[BN];
-#pragma unroll
-            for (int i = 0; i < BN; ++i) acc[i] = 0.0f;
-            const int gbs = p.gb_cols == 1 ? 0 : 1, gas = p.ga_cols == 1 ? 0 : 1;
-            for (int c = et; c < BN; c += 128) {
-                sbuf[c] = __half2float(p.b_scale[(long)(n0 + c) * p.gb_cols]);
-                rbuf[c] = has_zero ? p.b_rowsum[(long)(n0 + c) * G] : 0;
-            }
-            bar_sync_named(1, 128);
-            bool ok = true;
-            for (int kb = 0; kb < KB && ok; ++kb) {
-                const int buf = kb & 1;
-                // prefetch the next group's column data (BN == 128: one column per thread)
-                float nsb = 0.f; int nrs = 0;
-                if (kb + 1 < KB) {
-                    nsb = __half2float(p.b_scale[(long)(n0 + et) * p.gb_cols + gbs * (kb + 1)]);
-                    if (has_zero) nrs = p.b_rowsum[(long)(n0 + et) * G + kb + 1];
-                }
-                const float sa = __half2float(p.a_scale[(long)rowc * p.ga_cols + gas * kb]) * (1.0f / 256.0f);
-                const int za = has_zero ? (int)__half2float(p.a_zero[(long)rowc * p.ga_cols + gas * kb]) : 0;
-                ok = mbar_wait(acc_full(buf), (kb >> 1) & 1, abort_flag, 6);
-                if (!ok) break;
-                tc_fence_after();
-                const float *sb = sbuf + buf * BN;
-                const int *rs = rbuf + buf * BN;
-#pragma unroll
-                for (int cc = 0; cc < BN / 32; ++cc) {
-                    uint32_t v[32];
-                    tc_ld32(tlane + buf * BN + cc * 32, v);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int col = cc * 32 + j;
-                        // v = 256 * sum; the zero-point term is scaled alike so the difference stays exact
-                        const int I = (int)v[j] - ((za * rs[col]) << 8);
-                        acc[col] = __fmaf_rn((float)I, __fmul_rn(sa, sb[col]), acc[col]);
+    if (warp < 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::);
+        if (warp == 0) {
+            // -------------------------------------------------------- TMA producer
+            if (lane == 0) {
+                int it = 0;
+                bool ok = true;
+                for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                    const int m0 = (tile % p.m_blocks) * BM, n0 = (tile / p.m_blocks) * BN;
+                    for (int kb = 0; kb < KB; ++kb, ++it) {
+                        const int s = it % S;
+                        if (!mbar_wait(pk_empty(s), ((it / S) & 1) ^ 1, abort_flag, 1)) { ok = false; break; }
+                        mbar_expect_tx(pk_full(s), Plan::kPkStage);
+                        const uint32_t dst = base + Plan::kPkOff + s * Plan::kPkStage;
+                        tma_load_2d(dst, &map_a, kb * (BK / 2), m0, pk_full(s));
+                        tma_load_2d(dst + BM * (BK / 2), &map_b, kb * (BK / 2), n0, pk_full(s));
                     }
                 }
-                tc_fence_before();
-                mbar_arrive(acc_empty(buf));
-                if (kb + 1 < KB) { sbuf[(buf ^ 1) * BN + et] = nsb; rbuf[(buf ^ 1) * BN + et] = nrs; }
-                bar_sync_named(1, 128);
-            }
-            if (ok && row < p.M) {
-#pragma unroll
-                for (int cc = 0; cc < BN / 32; ++cc) {
-                    float o[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        o[j] = acc[cc * 32 + j];
-                        if (p.bias) o[j] = __fadd_rn(o[j], __half2float(p.bias[n0 + cc * 32 + j]));
+                if (*abort_flag) {
+                    // let the copies already issued land before the CTA leaves
+                    for (int j = it > S ? it - S : 0; j < it; ++j) {
+                        const uint64_t t0 = gtimer();
+                        while (!mbar_try(pk_full(j % S), (j / S) & 1) && gtimer() - t0 < 100000000ull) {}
                     }
-                    store_row_chunk(p.D, p.out_bf16, (long)row * p.N + n0 + cc * 32, o);
+                }
+            }
+        } else if (warp == 1) {
+            // -------------------------------------------------------- MMA issuer
+            if (lane == 0) {
+                const uint32_t idesc = (2u << 4) | ((A_UNSIGNED ? 0u : 1u) << 7) | (1u << 10) |
+                                       ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                int it = 0, u = 0;
+                bool ok = true;
+                for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                    for (int kb = 0; kb < KB; ++kb, ++it) {
+                        const int s = it % S;
+                        const int buf = u & 1;
+                        if ((GROUPED || kb == 0) && u >= 2) {
+                            if (!mbar_wait(acc_empty(buf), ((u >> 1) & 1) ^ 1, abort_flag, 2)) { ok = false; break; }
+                        }
+                        if (!mbar_wait(ex_full(s), (it / S) & 1, abort_flag, 3)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t a_addr = base + Plan::kExpOff + s * Plan::kExpStage;
+                        const uint64_t adesc = make_smem_desc(a_addr), bdesc = make_smem_desc(a_addr + BM * BK);
+#pragma unroll
+                        for (int k4 = 0; k4 < BK / 32; ++k4) {
+                            const uint32_t accum = GROUPED ? (k4 > 0) : (kb > 0 || k4 > 0);
+                            tc_mma_i8(tmem + buf * BN, adesc + 2 * k4, bdesc + 2 * k4, idesc, accum);
+                        }
+                        tc_commit(ex_empty(s));
+                        if (GROUPED || kb == KB - 1) { tc_commit(acc_full(buf)); ++u; }
+                    }
                 }
             }
         } else {
-            float *bbuf = reinterpret_cast<float *>(sm + Plan::kAuxOff + 3 * BN * 4);
-            for (int c = et; c < BN; c += 128) {
-                sbuf[c] = __half2float(p.b_scale[n0 + c]);
-                rbuf[c] = has_zero ? p.b_rowsum[n0 + c] : 0;
-                bbuf[c] = p.bias ? __half2float(p.bias[n0 + c]) : 0.0f;
+            // -------------------------------------------------------- int4 -> int8 converters
+            const int ct = tid - kConvTid0;                 // 0..191
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % S;
+                    if (!mbar_wait(pk_full(s), (it / S) & 1, abort_flag, 4)) { ok = false; break; }
+                    if (!mbar_wait(ex_empty(s), ((it / S) & 1) ^ 1, abort_flag, 5)) { ok = false; break; }
+                    const uint8_t *pk = sm + Plan::kPkOff + s * Plan::kPkStage;
+                    uint8_t *ex = sm + Plan::kExpOff + s * Plan::kExpStage;
+                    constexpr int kChunks = (BM + BN) * 4;
+#pragma unroll 4
+                    for (int ch = ct; ch < kChunks; ch += kConvThreads) {
+                        const int row = ch >> 2, c = ch & 3;     // rows of A, then rows of B
+                        const uint4 w = *reinterpret_cast<const uint4 *>(pk + row * 64 + c * 16);
+                        uint4 e, o;
+                        e.x = (w.x << 4) & 0xF0F0F0F0u; e.y = (w.y << 4) & 0xF0F0F0F0u;
+                        e.z = (w.z << 4) & 0xF0F0F0F0u; e.w = (w.w << 4) & 0xF0F0F0F0u;
+                        o.x = w.x & 0xF0F0F0F0u; o.y = w.y & 0xF0F0F0F0u; o.z = w.z & 0xF0F0F0F0u; o.w = w.w & 0xF0F0F0F0u;
+                        uint8_t *dst = ex + row * 128;
+                        const int sw = row & 7;
+                        *reinterpret_cast<uint4 *>(dst + (((2 * c) ^ sw) << 4)) = e;
+                        *reinterpret_cast<uint4 *>(dst + (((2 * c + 1) ^ sw) << 4)) = o;
+                    }
+                    fence_proxy_async();
+                    mbar_arrive(ex_full(s));
+                    mbar_arrive(pk_empty(s));
+                }
             }
-            bar_sync_named(1, 128);
-            const float sa = __half2float(p.a_scale[rowc]) * (1.0f / 256.0f);
-            const int za = has_zero ? (int)__half2float(p.a_zero[rowc]) : 0;
-            if (mbar_wait(acc_full(0), 0, abort_flag, 7)) {
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Plan::kEpiRegs));
+        const int wg = (warp - 8) >> 2;                  // which 128 columns of the tile
+        const int et = tid - kNonEpiThreads - wg * 128;  // 0..127 within the warpgroup
+        const int wq = warp & 3;                         // TMEM lane quarter this warp may read
+        float *sbuf = reinterpret_cast<float *>(sm + Plan::kAuxOff);               // [2][BN] weight scales
+        int *rbuf = reinterpret_cast<int *>(sm + Plan::kAuxOff + 2 * BN * 4);      // [2][BN] weight row sums
+        float *bbuf = reinterpret_cast<float *>(sm + Plan::kAuxOff + 4 * BN * 4);  // [BN] bias
+        const uint32_t tlane = tmem + ((uint32_t)(wq * 32) << 16) + wg * 128;
+        const int cbase = wg * 128;                      // first tile column of this warpgroup
+        int u = 0;
+        bool ok = true;
+
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile % p.m_blocks) * BM, n0 = (tile / p.m_blocks) * BN;
+            const int row = m0 + wq * 32 + lane;
+            const int rowc = row < p.M ? row : p.M - 1;
+            const int gcol = n0 + cbase + et;            // the column this thread stages
+            if (GROUPED) {
+                const int G = KB;
+                const int gbs = p.gb_cols == 1 ? 0 : 1, gas = p.ga_cols == 1 ? 0 : 1;
+                uint64_t acc[64];
+#pragma unroll
+                for (int i = 0; i < 64; ++i) acc[i] = 0ull;
+                sbuf[cbase + et] = __half2float(p.b_scale[(long)gcol * p.gb_cols]);
+                if (A_UNSIGNED) rbuf[cbase + et] = p.b_rowsum[(long)gcol * G];
+                bar_sync_named(1 + wg, 128);
+                for (int kb = 0; kb < KB; ++kb, ++u) {
+                    const int buf = u & 1, slot = kb & 1;
+                    float nsb = 0.f; int nrs = 0;
+                    if (kb + 1 < KB) {                   // next group's column data, fetched early
+                        nsb = __half2float(p.b_scale[(long)gcol * p.gb_cols + gbs * (kb + 1)]);
+                        if (A_UNSIGNED) nrs = p.b_rowsum[(long)gcol * G + kb + 1];
+                    }
+                    // 256 * sum arrives from the tensor core; without zero-points the 1/256 rides in the scale
+                    float sa = __half2float(p.a_scale[(long)rowc * p.ga_cols + gas * kb]);
+                    if (!A_UNSIGNED) sa *= (1.0f / 256.0f);
+                    const int za = A_UNSIGNED ? (int)__half2float(p.a_zero[(long)rowc * p.ga_cols + gas * kb]) : 0;
+                    const uint64_t sa2 = pack2(sa, sa);
+                    if (!mbar_wait(acc_full(buf), (u >> 1) & 1, abort_flag, 6)) { ok = false; break; }
+                    tc_fence_after();
+                    const float *sb = sbuf + slot * BN + cbase;
+                    const int *rs = rbuf + slot * BN + cbase;
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        uint32_t v[32];
+                        tc_ld32(tlane + buf * BN + cc * 32, v);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const int col = cc * 32 + j;
+                            const float2 sbp = *reinterpret_cast<const float2 *>(sb + col);
+                            int i0 = (int)v[j], i1 = (int)v[j + 1];
+                            if (A_UNSIGNED) { i0 = (i0 >> 8) - za * rs[col]; i1 = (i1 >> 8) - za * rs[col + 1]; }
+                            const uint64_t p2 = mul2(sa2, pack2(sbp.x, sbp.y));
+                            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[col >> 1]) : "l"(pack2((float)i0, (float)i1)), "l"(p2));
+                        }
+                    }
+                    tc_fence_before();
+                    mbar_arrive(acc_empty(buf));
+                    if (kb + 1 < KB) { sbuf[(slot ^ 1) * BN + cbase + et] = nsb; if (A_UNSIGNED) rbuf[(slot ^ 1) * BN + cbase + et] = nrs; }
+                    bar_sync_named(1 + wg, 128);
+                }
+                if (ok && row < p.M) {
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        float o[32];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) unpack2(acc[cc * 16 + j], o[2 * j], o[2 * j + 1]);
+                        if (p.bias) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) o[j] = __fadd_rn(o[j], __half2float(p.bias[n0 + cbase + cc * 32 + j]));
+                        }
+                        store_row_chunk(p.D, p.out_bf16, (long)row * p.N + n0 + cbase + cc * 32, o);
+                    }
+                }
+            } else {
+                sbuf[cbase + et] = __half2float(p.b_scale[gcol]);
+                rbuf[cbase + et] = A_UNSIGNED ? p.b_rowsum[gcol] : 0;
+                bbuf[cbase + et] = p.bias ? __half2float(p.bias[gcol]) : 0.0f;
+                bar_sync_named(1 + wg, 128);
+                const float sa = __half2float(p.a_scale[rowc]) * (1.0f / 256.0f);
+                const int za = A_UNSIGNED ? (int)__half2float(p.a_zero[rowc]) : 0;
+                const int buf = u & 1;
+                if (!mbar_wait(acc_full(buf), (u >> 1) & 1, abort_flag, 7)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll 1
-                for (int cc = 0; cc < BN / 32; ++cc) {
+                for (int cc = 0; cc < 4; ++cc) {
                     uint32_t v[32];
-                    tc_ld32(tlane + cc * 32, v);
+                    tc_ld32(tlane + buf * BN + cc * 32, v);
                     tc_wait_ld();
                     float o[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int col = cc * 32 + j;
+                        const int col = cbase + cc * 32 + j;
                         const int I = (int)v[j] - ((za * rbuf[col]) << 8);
                         float r = __fmaf_rn((float)I, __fmul_rn(sa, sbuf[col]), 0.0f);
                         if (p.bias) r = __fadd_rn(r, bbuf[col]);
                         o[j] = r;
                     }
-                    if (row < p.M) store_row_chunk(p.D, p.out_bf16, (long)row * p.N + n0 + cc * 32, o);
+                    if (row < p.M) store_row_chunk(p.D, p.out_bf16, (long)row * p.N + n0 + cbase + cc * 32, o);
                 }
                 tc_fence_before();
+                mbar_arrive(acc_empty(buf));
+                ++u;
+                bar_sync_named(1 + wg, 128);             // the staging arrays are rewritten for the next tile
             }
         }
     }
@@ -371,7 +407,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -414,8 +450,17 @@ int launch_t(const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &p, cu
     const int smem = SmemPlan<BN>::kBytes;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_status(e, "gemm_tcgen05 attribute");
-    dim3 grid((unsigned)(p.N / BN), (unsigned)((p.M + BM - 1) / BM));
-    kern<<<grid, kThreads, smem, stream>>>(ma, mb, p);
+    TcParams q = p;
+    q.m_blocks = (p.M + BM - 1) / BM;
+    q.num_tiles = q.m_blocks * (p.N / BN);
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = kNumSMs;
+    }
+    const int grid = q.num_tiles < sms ? q.num_tiles : sms;        // one persistent CTA per SM
+    kern<<<grid, kNonEpiThreads + BN, smem, stream>>>(ma, mb, q);
     return cuda_status(cudaGetLastError(), "gemm_tcgen05 launch");
 }
 
@@ -434,13 +479,14 @@ int launch_gemm_tcgen05(const uint8_t *A, const uint8_t *B, const void *a_scale,
     p.ga_cols = (int)(K / a_group); p.gb_cols = (int)(K / b_group);
     p.out_bf16 = out_dtype == FLH_B200_BF16;
     const bool grouped = a_group < K || b_group < K;
-    const int bn = (!grouped && N % 256 == 0) ? 256 : 128;
+    const int bn = (N % 256 == 0) ? 256 : 128;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, BM);
     if (rc) return rc;
     rc = make_map(&mb, B, N, K, bn);
     if (rc) return rc;
     const bool u = a_zero != nullptr;
+    if (grouped && bn == 256) return u ? launch_t<256, true, true>(ma, mb, p, stream) : launch_t<256, true, false>(ma, mb, p, stream);
     if (grouped) return u ? launch_t<128, true, true>(ma, mb, p, stream) : launch_t<128, true, false>(ma, mb, p, stream);
     if (bn == 256) return u ? launch_t<256, false, true>(ma, mb, p, stream) : launch_t<256, false, false>(ma, mb, p, stream);
     return u ? launch_t<128, false, true>(ma, mb, p, stream) : launch_t<128, false, false>(ma, mb, p, stream);

@@ -255,7 +255,9 @@ class LinearFLH(torch.nn.Module):
 
     def forward_torch(self, x, a_scale=None, a_zero=None, x_is_packed=True, is_symmetric=None):
         """PyTorch twin (flh/nn/linear.py:134-152): unpack, (q - zero) * scale, F.linear."""
-        signed = a_zero is None if is_symmetric is None else is_symmetric
+        if is_symmetric is None:      # as the reference infers it: symmetric unless a non-zero zero-point is given
+            is_symmetric = a_zero is None or not bool(torch.any(a_zero != 0))
+        signed = is_symmetric
         q = unpack_i4(x, signed=signed).float()
         g = a_scale.shape[-1]
         qg = q.view(*q.shape[:-1], g, -1)

@@ -34,6 +34,18 @@ def test_tcgen05_shapes(cuda, m, n, k):
     run_case(cuda, TC, make_case(m + n + 1, m, n, k, 0, 0, True, bias=True), bf16=True)
 
 
+@pytest.mark.parametrize("mode", MODES)
+def test_tcgen05_more_tiles_than_sms(cuda, mode):
+    # 3 row blocks x 60 column blocks = 180 tiles: the persistent CTAs each take more than one tile
+    run_case(cuda, TC, make_case(77, 300, 15360, 512, *mode))
+
+
+def test_tcgen05_n_multiple_of_128_only(cuda):
+    # N = 384 is not a multiple of 256: the 128-column variant
+    run_case(cuda, TC, make_case(78, 260, 384, 1024, 128, 128, False))
+    run_case(cuda, TC, make_case(79, 260, 384, 1024, 0, 0, True, bias=True))
+
+
 def test_tcgen05_prefill_size_against_mma_path(cuda):
     # BASELINE shape 4096 -> 12288 at M = 2048: too big for the CPU oracle in seconds, so the two
     # independent GPU paths must agree bit for bit, and sampled rows are checked against the oracle.
