@@ -279,7 +279,8 @@ def run_ours(args, world, rank, local, dist):
             tokens = B
         steps, warmup = min(steps, 20), min(warmup, 5)
         with ClockSampler(local) as cs:
-            t = timed_loop(fn, steps, max(warmup, 3), dist, device, sampler=cs)
+            # a decode step is ~600 short launches: it is recorded once into a CUDA graph and replayed
+            t = timed_loop(fn, steps, max(warmup, 3), dist, device, sampler=cs, graph=(not prefill and world == 1))
         out.update(metric="w4a4_llama_%s_tok_per_s" % ("prefill" if prefill else "decode"), unit="tok/s",
                    value=tokens * steps / t, ms_per_step=t / steps * 1e3, dtype="int4 codes, s32 accumulate, f16 activations",
                    steps=steps, warmup=max(warmup, 3), scaling="strong" if world > 1 else "weak", clocks=cs.summary(),

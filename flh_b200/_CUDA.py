@@ -20,7 +20,7 @@ from . import _lib
 from .hadamard import get_hadK
 
 F16, BF16 = 0, 1
-GEMM_AUTO, GEMM_TCGEN05, GEMM_MMA_SYNC, GEMM_STREAM = 0, 1, 2, 3
+GEMM_AUTO, GEMM_TCGEN05, GEMM_MMA_SYNC, GEMM_STREAM, GEMM_STREAM_SPLITK, GEMM_TCGEN05_DIRECT = 0, 1, 2, 3, 4, 5
 
 
 def _check(cond: bool, msg: str) -> None:
@@ -181,6 +181,20 @@ def weight_rowsum(B, group: int):
     return rs
 
 
+_WORKSPACES: dict = {}
+
+
+def _workspace(device, stream: int, nbytes: int):
+    """Zero-initialised scratch for the split-K decode kernel, one per (device, stream): launches on one
+    stream run in order, so they may share it; the kernel leaves its counters zeroed."""
+    key = (str(device), stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 8 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
 def gemm_i4_dequant(A, B, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=None,
                     out_dtype=torch.float16, algo: int = GEMM_AUTO, out=None):
     """General form of the GEMM (include/flh_b200.h: flh_b200_gemm_i4_dequant).  Scale granularity
@@ -194,11 +208,15 @@ def gemm_i4_dequant(A, B, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=Non
     _check(B_scale.shape[1] > 0 and K % B_scale.shape[1] == 0, "B_scale columns must divide K")
     ag, bg = K // A_scale.shape[1], K // B_scale.shape[1]
     D = out if out is not None else torch.empty((M, N), dtype=out_dtype, device=A.device)
+    lib = _lib.load()
     with torch.cuda.device(A.device):
-        _lib.check(_lib.load().flh_b200_gemm_i4_dequant(
+        stream = _stream(A)
+        need = lib.flh_b200_gemm_workspace_bytes(M, N, K, ag, bg, algo) if M <= 32 else 0
+        ws = _workspace(A.device, stream, need) if need else None
+        _lib.check(lib.flh_b200_gemm_i4_dequant(
             _ptr(A), _ptr(B), _ptr(A_scale), _ptr(A_zero), _ptr(B_scale), _ptr(B_rowsum), _ptr(bias), _ptr(D),
-            M, N, K, ag, bg, BF16 if D.dtype == torch.bfloat16 else F16, algo, None, 0, _stream(A)),
-            "gemm_i4_dequant")
+            M, N, K, ag, bg, BF16 if D.dtype == torch.bfloat16 else F16, algo, _ptr(ws), ws.numel() if ws is not None else 0,
+            stream), "gemm_i4_dequant")
     return D
 
 

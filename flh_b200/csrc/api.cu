@@ -37,9 +37,11 @@ int launch_gemm_mma_tile(const uint8_t *, const uint8_t *, const void *, const v
                          cudaStream_t);
 int launch_gemm_stream(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
                        const int32_t *, const void *, void *, long, long, long, long, long, int,
-                       cudaStream_t);
+                       int, void *, cudaStream_t);
+int stream_splits(long M, long N, long K);
+size_t stream_scratch_bytes(long M, long N, int splits);
 int launch_gemm_tcgen05(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
-                        const int32_t *, const void *, void *, long, long, long, long, long, int,
+                        const int32_t *, const void *, void *, long, long, long, long, long, int, int,
                         cudaStream_t);
 
 int gemm_tcgen05_status(int *);
@@ -134,21 +136,21 @@ int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t
 }
 
 int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group) {
-    (void)N; (void)K; (void)a_group; (void)b_group;
-    if (M <= 32) return FLH_B200_GEMM_STREAM;
+    (void)a_group; (void)b_group;
+    if (M <= 32) return stream_splits(M, N, K) > 1 ? FLH_B200_GEMM_STREAM_SPLITK : FLH_B200_GEMM_STREAM;
     return FLH_B200_GEMM_TCGEN05;
 }
 
 size_t flh_b200_gemm_workspace_bytes(long M, long N, long K, long a_group, long b_group, int algo) {
-    (void)M; (void)N; (void)K; (void)a_group; (void)b_group; (void)algo;
-    return 0;
+    if (algo == FLH_B200_GEMM_AUTO) algo = flh_b200_gemm_pick_algo(M, N, K, a_group, b_group);
+    if (algo != FLH_B200_GEMM_STREAM_SPLITK || M > 32) return 0;
+    return stream_scratch_bytes(M, N, stream_splits(M, N, K));
 }
 
 int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_scale, const void *a_zero,
                              const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D,
                              long M, long N, long K, long a_group, long b_group, int out_dtype, int algo,
                              void *workspace, size_t workspace_bytes, void *stream) {
-    (void)workspace; (void)workspace_bytes;
     FLH_REQUIRE(M >= 0 && N >= 0 && K > 0, FLH_B200_EINVAL, "bad shape M=%ld N=%ld K=%ld", M, N, K);
     FLH_REQUIRE(K % 128 == 0 && K <= 65536, FLH_B200_EINVAL, "K must be a multiple of 128 and <= 65536 (got %ld)", K);
     FLH_REQUIRE(N % 128 == 0, FLH_B200_EINVAL, "N must be a multiple of 128 (got %ld)", N);
@@ -160,16 +162,35 @@ int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_s
     FLH_REQUIRE(!a_zero || b_rowsum, FLH_B200_EINVAL, "a_zero needs b_rowsum");
     FLH_REQUIRE(aligned16(A) && aligned16(B), FLH_B200_EALIGN, "A and B must be 16-byte aligned");
     FLH_REQUIRE((reinterpret_cast<uintptr_t>(D) & 15) == 0, FLH_B200_EALIGN, "D must be 16-byte aligned");
-    if (algo == FLH_B200_GEMM_AUTO) algo = flh_b200_gemm_pick_algo(M, N, K, a_group, b_group);
+    if (algo == FLH_B200_GEMM_AUTO) {
+        algo = flh_b200_gemm_pick_algo(M, N, K, a_group, b_group);
+        // without (enough) scratch the split-K form quietly gives way to the plain streaming kernel
+        if (algo == FLH_B200_GEMM_STREAM_SPLITK &&
+            (!workspace || workspace_bytes < stream_scratch_bytes(M, N, stream_splits(M, N, K))))
+            algo = FLH_B200_GEMM_STREAM;
+    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (algo) {
         case FLH_B200_GEMM_STREAM:
             FLH_REQUIRE(M <= 32, FLH_B200_EINVAL, "the streaming kernel serves M <= 32 (got %ld)", M);
-            return launch_gemm_stream(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, s);
+            return launch_gemm_stream(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, 1, nullptr, s);
+        case FLH_B200_GEMM_STREAM_SPLITK: {
+            FLH_REQUIRE(M <= 32, FLH_B200_EINVAL, "the streaming kernel serves M <= 32 (got %ld)", M);
+            const int splits = stream_splits(M, N, K);
+            if (splits <= 1)
+                return launch_gemm_stream(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, 1, nullptr, s);
+            const size_t need = stream_scratch_bytes(M, N, splits);
+            FLH_REQUIRE(workspace && workspace_bytes >= need, FLH_B200_EINVAL,
+                        "split-K needs %zu bytes of zero-initialised workspace (got %zu)", need, workspace_bytes);
+            FLH_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, FLH_B200_EALIGN, "workspace must be 256-byte aligned");
+            return launch_gemm_stream(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, splits, workspace, s);
+        }
         case FLH_B200_GEMM_MMA_SYNC:
             return launch_gemm_mma_tile(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, s);
         case FLH_B200_GEMM_TCGEN05:
-            return launch_gemm_tcgen05(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, s);
+            return launch_gemm_tcgen05(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, 0, s);
+        case FLH_B200_GEMM_TCGEN05_DIRECT:
+            return launch_gemm_tcgen05(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, 1, s);
         default:
             return fail(FLH_B200_EINVAL, "unknown algo %d", algo);
     }

@@ -24,6 +24,9 @@ struct GemmParams {
     int ga_cols, gb_cols;   // scale columns: K / a_group, K / b_group
     int grouped;            // 1: dequantise every 128-K block; 0: one integer sum over all of K
     int out_bf16;
+    int splits;             // split-K (streaming kernel): CTAs along K per row slab; 1 = none
+    int *counters;          // split-K scratch: one arrival counter per row slab (zero between launches)
+    float *partials;        // split-K scratch: [splits][8 * NT][N] partial sums (raw 32-bit words)
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
@@ -250,7 +253,10 @@ __device__ __forceinline__ void mma_w_by_tok(int32_t (&c)[4], uint32_t a0, uint3
                      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int WARPS, int NT, bool A_UNSIGNED, bool GROUPED>
+// SPLIT: blockIdx.y selects a contiguous range of 256-K stages; every CTA of a row slab writes its partial
+// sums (int32 without group scales — exact; binary32 chains with them) to scratch, and the last one to
+// arrive (a counter per slab) adds them in split order, finishes the epilogue and re-zeroes the counter.
+template <int WARPS, int NT, bool A_UNSIGNED, bool GROUPED, bool SPLIT>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_stream_kernel(const GemmParams p) {
     using Plan = StreamPlan<WARPS, NT>;
@@ -262,6 +268,12 @@ gemm_stream_kernel(const GemmParams p) {
     const int KB = p.K / 128, KB2 = (KB + 1) / 2;
     const long ldk = p.K / 2;
     const bool has_zero = A_UNSIGNED;
+    int st_begin = 0, st_end = KB2;                    // this CTA's range of 256-K stages
+    if (SPLIT) {
+        const int per = (KB2 + p.splits - 1) / p.splits;
+        st_begin = blockIdx.y * per;
+        st_end = min(KB2, st_begin + per);
+    }
     // 4-byte copies of two adjacent f16 scales need an even number of groups per row
     const bool pair_ok = (KB & 1) == 0;
 
@@ -339,17 +351,18 @@ gemm_stream_kernel(const GemmParams p) {
 
 #pragma unroll
     for (int s = 0; s < SSTAGES - 1; ++s) {
-        if (s < KB2) load_stage(s, s);
+        if (st_begin + s < st_end) load_stage(s, st_begin + s);
         cp_async_commit();
     }
 
-    for (int kb2 = 0; kb2 < KB2; ++kb2) {
+    for (int kb2 = st_begin; kb2 < st_end; ++kb2) {
+        const int rel = kb2 - st_begin;
         cp_async_wait<SSTAGES - 2>();
         __syncthreads();
-        if (kb2 + SSTAGES - 1 < KB2) load_stage((kb2 + SSTAGES - 1) % SSTAGES, kb2 + SSTAGES - 1);
+        if (kb2 + SSTAGES - 1 < st_end) load_stage((rel + SSTAGES - 1) % SSTAGES, kb2 + SSTAGES - 1);
         cp_async_commit();
 
-        const uint8_t *st = smem + (kb2 % SSTAGES) * Plan::kStage;
+        const uint8_t *st = smem + (rel % SSTAGES) * Plan::kStage;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int kb = kb2 * 2 + half;
@@ -401,6 +414,46 @@ gemm_stream_kernel(const GemmParams p) {
     }
     cp_async_wait<0>();
 
+    if (SPLIT) {
+        __shared__ int s_last;
+        constexpr int TOKP = 8 * NT;
+        // raw 32-bit partials: int32 (x256) without group scales, binary32 chains with them
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int tok = i * 8 + 2 * t + j;
+                    const float w = GROUPED ? acc[i][2 * h + j] : __int_as_float(c[i][2 * h + j]);
+                    p.partials[((long)blockIdx.y * TOKP + tok) * p.N + ch0 + 8 * h] = w;
+                }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) s_last = atomicAdd(&p.counters[blockIdx.x], 1) == p.splits - 1;
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int tok = i * 8 + 2 * t + j;
+                    float fsum = 0.0f;
+                    int isum = 0;
+                    for (int sp = 0; sp < p.splits; ++sp) {
+                        const float w = __ldcg(&p.partials[((long)sp * TOKP + tok) * p.N + ch0 + 8 * h]);
+                        if (GROUPED) fsum = sp == 0 ? w : __fadd_rn(fsum, w);
+                        else isum += __float_as_int(w);
+                    }
+                    acc[i][2 * h + j] = fsum;
+                    c[i][2 * h + j] = isum;
+                }
+        if (tid == 0) p.counters[blockIdx.x] = 0;       // ready for the next launch
+    }
+
 #pragma unroll
     for (int i = 0; i < NT; ++i)
 #pragma unroll
@@ -439,6 +492,7 @@ GemmParams make_params(const uint8_t *A, const uint8_t *B, const void *a_scale, 
     p.ga_cols = (int)(K / a_group); p.gb_cols = (int)(K / b_group);
     p.grouped = (a_group < K || b_group < K) ? 1 : 0;
     p.out_bf16 = out_dtype == FLH_B200_BF16;
+    p.splits = 1; p.counters = nullptr; p.partials = nullptr;
     return p;
 }
 
@@ -464,30 +518,57 @@ int launch_gemm_mma_tile(const uint8_t *A, const uint8_t *B, const void *a_scale
     return cuda_status(cudaGetLastError(), "gemm_tile launch");
 }
 
-template <int WARPS, int NT, bool U, bool G>
+template <int WARPS, int NT, bool U, bool G, bool SPLIT>
 static int launch_stream_t(const GemmParams &p, cudaStream_t stream) {
     const int smem = SSTAGES * StreamPlan<WARPS, NT>::kStage;
-    auto kern = gemm_stream_kernel<WARPS, NT, U, G>;
+    auto kern = gemm_stream_kernel<WARPS, NT, U, G, SPLIT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_status(e, "gemm_stream attribute");
-    kern<<<(unsigned)(p.N / (16 * WARPS)), WARPS * 32, smem, stream>>>(p);
+    dim3 grid((unsigned)(p.N / (16 * WARPS)), (unsigned)(SPLIT ? p.splits : 1));
+    kern<<<grid, WARPS * 32, smem, stream>>>(p);
     return cuda_status(cudaGetLastError(), "gemm_stream launch");
 }
 
 template <int WARPS, int NT>
 static int launch_stream_w(const GemmParams &p, bool u, cudaStream_t stream) {
-    if (p.grouped) return u ? launch_stream_t<WARPS, NT, true, true>(p, stream) : launch_stream_t<WARPS, NT, false, true>(p, stream);
-    return u ? launch_stream_t<WARPS, NT, true, false>(p, stream) : launch_stream_t<WARPS, NT, false, false>(p, stream);
+    if (p.splits > 1) {
+        if (p.grouped) return u ? launch_stream_t<WARPS, NT, true, true, true>(p, stream) : launch_stream_t<WARPS, NT, false, true, true>(p, stream);
+        return u ? launch_stream_t<WARPS, NT, true, false, true>(p, stream) : launch_stream_t<WARPS, NT, false, false, true>(p, stream);
+    }
+    if (p.grouped) return u ? launch_stream_t<WARPS, NT, true, true, false>(p, stream) : launch_stream_t<WARPS, NT, false, true, false>(p, stream);
+    return u ? launch_stream_t<WARPS, NT, true, false, false>(p, stream) : launch_stream_t<WARPS, NT, false, false, false>(p, stream);
+}
+
+// Split-K plan of the streaming kernel: how many CTAs share a 32-row slab along K, and the scratch they need.
+// The slabs alone fill the GPU when there are at least two per SM; otherwise K is cut so that about three
+// CTAs per SM exist, keeping at least four 256-K stages per CTA.
+int stream_splits(long M, long N, long K) {
+    (void)M;
+    const long slabs = N / 32;
+    if (slabs >= 2 * kNumSMs) return 1;
+    const long stages = (K / 128 + 1) / 2;
+    long s = (3 * kNumSMs + slabs - 1) / slabs;
+    if (s > stages / 4) s = stages / 4;
+    if (s > 8) s = 8;
+    return s < 2 ? 1 : (int)s;
+}
+size_t stream_scratch_bytes(long M, long N, int splits) {
+    if (splits <= 1) return 0;
+    const long tokp = M <= 8 ? 8 : (M <= 16 ? 16 : 32);
+    return 4096 + (size_t)splits * tokp * N * 4;           // 4 KB of slab counters, then the partial sums
 }
 
 int launch_gemm_stream(const uint8_t *A, const uint8_t *B, const void *a_scale, const void *a_zero,
                        const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D,
                        long M, long N, long K, long a_group, long b_group, int out_dtype,
-                       cudaStream_t stream) {
-    const GemmParams p = make_params(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype);
+                       int splits, void *scratch, cudaStream_t stream) {
+    GemmParams p = make_params(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype);
+    p.splits = splits > 1 ? splits : 1;
+    p.counters = static_cast<int *>(scratch);
+    p.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(scratch) + 4096);
     const bool u = a_zero != nullptr;
     // 32-row CTAs unless that would be more than ~8 CTAs per SM; N is a multiple of 128
-    const bool wide = N / 32 > 8 * kNumSMs;
+    const bool wide = splits <= 1 && N / 32 > 8 * kNumSMs;
     if (M <= 8) return wide ? launch_stream_w<4, 1>(p, u, stream) : launch_stream_w<2, 1>(p, u, stream);
     if (M <= 16) return wide ? launch_stream_w<4, 2>(p, u, stream) : launch_stream_w<2, 2>(p, u, stream);
     return wide ? launch_stream_w<4, 4>(p, u, stream) : launch_stream_w<2, 4>(p, u, stream);

@@ -108,6 +108,7 @@ struct TcParams {
     const __half *a_scale, *a_zero, *b_scale, *bias;
     const int32_t *b_rowsum;
     void *D;
+    const uint8_t *A, *B;       // packed operands (direct-load variant)
     int M, N, K;
     int ga_cols, gb_cols;
     int out_bf16;
@@ -128,8 +129,14 @@ struct SmemPlan {
     static constexpr int kAuxOff = kPkOff + kStages * kPkStage;   // weight scales [2][BN] f32, row sums [2][BN] s32, bias [BN] f32
     static constexpr int kBarOff = kAuxOff + 5 * BN * 4;
     static constexpr int kBytes = kBarOff + 256 + 1024;           // + slack to align the base to 1024
-    static constexpr int kEpiRegs = BN == 256 ? 192 : 232;        // registers per epilogue thread after setmaxnreg
+    // registers per thread after setmaxnreg: the 256 producer/converter threads drop to kLowRegs, the BN
+    // epilogue threads rise to kEpiRegs; 256 * kLowRegs + BN * kEpiRegs must fit the 64 K register file
+    static constexpr int kLowRegs(bool direct) { return direct ? 80 : 64; }
+    static constexpr int kEpiRegs(bool direct) { return BN == 256 ? (direct ? 176 : 192) : 232; }
 };
+static_assert(256 * SmemPlan<256>::kLowRegs(true) + 256 * SmemPlan<256>::kEpiRegs(true) <= 65536, "register budget");
+static_assert(256 * SmemPlan<256>::kLowRegs(false) + 256 * SmemPlan<256>::kEpiRegs(false) <= 65536, "register budget");
+static_assert(256 * SmemPlan<128>::kLowRegs(true) + 128 * SmemPlan<128>::kEpiRegs(true) <= 384 * 168, "register budget");
 
 __device__ __forceinline__ void store_row_chunk(void *D, bool bf16, long off, const float (&v)[32]) {
     if (bf16) {
@@ -161,7 +168,12 @@ __device__ __forceinline__ void store_row_chunk(void *D, bool bf16, long off, co
 // run together share the same weight columns).  Barrier phases and the TMEM accumulator buffer are
 // driven by running counters: `it` counts 128-K stages, `u` counts accumulator uses (one per K-block
 // with group scales, one per tile otherwise); buffer u & 1 is filled while buffer (u - 1) & 1 drains.
-template <int BN, bool GROUPED, bool A_UNSIGNED>
+// DIRECT: the converter warps fetch the packed operands from global memory (L2) straight into registers,
+// one stage ahead, instead of reading tiles that TMA staged in shared memory.  Shared memory then carries
+// only the int8 tiles (written once, read once by the tensor core), which is what bounds this kernel:
+// per 128x256x128 stage 96 KB cross the shared-memory port instead of 144 KB.  Warp 0 turns into an L2
+// prefetcher that runs a few stages ahead.
+template <int BN, bool GROUPED, bool A_UNSIGNED, bool DIRECT>
 __global__ void __launch_bounds__(kNonEpiThreads + BN, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const TcParams p) {
@@ -208,8 +220,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem = *tmem_slot;
 
     if (warp < 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::);
-        if (warp == 0) {
+        if (DIRECT) asm volatile("setmaxnreg.dec.sync.aligned.u32 80;" ::);
+        else asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::);
+        if (warp == 0 && DIRECT) {
+            // -------------------------------------------------------- L2 prefetcher (direct-load variant)
+            constexpr int kAhead = 6;                      // stages ahead of the converters
+            const long ldk = p.K / 2;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+                const int m0 = (tile % p.m_blocks) * BM, n0 = (tile / p.m_blocks) * BN;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    // stay at most kAhead stages ahead: the converters publish progress through ex_full
+                    if (it >= kAhead) {
+                        const int j = it - kAhead, sj = j % S;
+                        if (!mbar_wait(ex_full(sj), (j / S) & 1, abort_flag, 8)) goto prefetch_done;
+                    }
+                    for (int r = lane; r < BM + BN; r += 32) {
+                        const uint8_t *src = r < BM ? p.A + (long)min(m0 + r, p.M - 1) * ldk
+                                                    : p.B + (long)(n0 + r - BM) * ldk;
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(src + kb * 64));
+                    }
+                }
+            }
+        prefetch_done:;
+        } else if (warp == 0) {
             // -------------------------------------------------------- TMA producer
             if (lane == 0) {
                 int it = 0;
@@ -264,38 +298,79 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         } else {
             // -------------------------------------------------------- int4 -> int8 converters
             const int ct = tid - kConvTid0;                 // 0..191
+            constexpr int kChunks = (BM + BN) * 4;          // 16-byte packed chunks per stage
+            auto expand_store = [&](uint8_t *ex, int ch, const uint4 &w) {
+                const int row = ch >> 2, c = ch & 3;        // rows of A, then rows of B
+                uint4 e, o;
+                e.x = (w.x << 4) & 0xF0F0F0F0u; e.y = (w.y << 4) & 0xF0F0F0F0u;
+                e.z = (w.z << 4) & 0xF0F0F0F0u; e.w = (w.w << 4) & 0xF0F0F0F0u;
+                o.x = w.x & 0xF0F0F0F0u; o.y = w.y & 0xF0F0F0F0u; o.z = w.z & 0xF0F0F0F0u; o.w = w.w & 0xF0F0F0F0u;
+                uint8_t *dst = ex + row * 128;
+                const int sw = row & 7;
+                *reinterpret_cast<uint4 *>(dst + (((2 * c) ^ sw) << 4)) = e;
+                *reinterpret_cast<uint4 *>(dst + (((2 * c + 1) ^ sw) << 4)) = o;
+            };
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int s = it % S;
-                    if (!mbar_wait(pk_full(s), (it / S) & 1, abort_flag, 4)) { ok = false; break; }
-                    if (!mbar_wait(ex_empty(s), ((it / S) & 1) ^ 1, abort_flag, 5)) { ok = false; break; }
-                    const uint8_t *pk = sm + Plan::kPkOff + s * Plan::kPkStage;
-                    uint8_t *ex = sm + Plan::kExpOff + s * Plan::kExpStage;
-                    constexpr int kChunks = (BM + BN) * 4;
-#pragma unroll 4
-                    for (int ch = ct; ch < kChunks; ch += kConvThreads) {
-                        const int row = ch >> 2, c = ch & 3;     // rows of A, then rows of B
-                        const uint4 w = *reinterpret_cast<const uint4 *>(pk + row * 64 + c * 16);
-                        uint4 e, o;
-                        e.x = (w.x << 4) & 0xF0F0F0F0u; e.y = (w.y << 4) & 0xF0F0F0F0u;
-                        e.z = (w.z << 4) & 0xF0F0F0F0u; e.w = (w.w << 4) & 0xF0F0F0F0u;
-                        o.x = w.x & 0xF0F0F0F0u; o.y = w.y & 0xF0F0F0F0u; o.z = w.z & 0xF0F0F0F0u; o.w = w.w & 0xF0F0F0F0u;
-                        uint8_t *dst = ex + row * 128;
-                        const int sw = row & 7;
-                        *reinterpret_cast<uint4 *>(dst + (((2 * c) ^ sw) << 4)) = e;
-                        *reinterpret_cast<uint4 *>(dst + (((2 * c + 1) ^ sw) << 4)) = o;
+            if (DIRECT) {
+                constexpr int kPer = (kChunks + kConvThreads - 1) / kConvThreads;   // chunks per thread per stage
+                const long ldk = p.K / 2;
+                uint4 w[kPer];
+                const uint8_t *src[kPer];
+                auto set_tile = [&](int tile) {
+                    const int m0 = (tile % p.m_blocks) * BM, n0 = (tile / p.m_blocks) * BN;
+#pragma unroll
+                    for (int j = 0; j < kPer; ++j) {
+                        const int ch = ct + j * kConvThreads;
+                        const int row = ch >> 2, c = ch & 3;
+                        if (ch >= kChunks) src[j] = nullptr;
+                        else if (row < BM) src[j] = (m0 + row < p.M) ? p.A + (long)(m0 + row) * ldk + c * 16 : nullptr;
+                        else src[j] = p.B + (long)(n0 + row - BM) * ldk + c * 16;
                     }
-                    fence_proxy_async();
-                    mbar_arrive(ex_full(s));
-                    mbar_arrive(pk_empty(s));
+                };
+                auto fetch = [&](int kb) {
+#pragma unroll
+                    for (int j = 0; j < kPer; ++j)
+                        w[j] = src[j] ? ldg_nc_v4(src[j] + kb * 64) : make_uint4(0, 0, 0, 0);
+                };
+                int tile = blockIdx.x;
+                if (tile < p.num_tiles) { set_tile(tile); fetch(0); }
+                for (; tile < p.num_tiles && ok; tile += gridDim.x) {
+                    for (int kb = 0; kb < KB; ++kb, ++it) {
+                        const int s = it % S;
+                        if (!mbar_wait(ex_empty(s), ((it / S) & 1) ^ 1, abort_flag, 5)) { ok = false; break; }
+                        uint8_t *ex = sm + Plan::kExpOff + s * Plan::kExpStage;
+#pragma unroll
+                        for (int j = 0; j < kPer; ++j)
+                            if (ct + j * kConvThreads < kChunks) expand_store(ex, ct + j * kConvThreads, w[j]);
+                        // next stage's operands: issued now, consumed one stage later
+                        if (kb + 1 < KB) fetch(kb + 1);
+                        else if (tile + (int)gridDim.x < p.num_tiles) { set_tile(tile + gridDim.x); fetch(0); }
+                        fence_proxy_async();
+                        mbar_arrive(ex_full(s));
+                    }
+                }
+            } else {
+                for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                    for (int kb = 0; kb < KB; ++kb, ++it) {
+                        const int s = it % S;
+                        if (!mbar_wait(pk_full(s), (it / S) & 1, abort_flag, 4)) { ok = false; break; }
+                        if (!mbar_wait(ex_empty(s), ((it / S) & 1) ^ 1, abort_flag, 5)) { ok = false; break; }
+                        const uint8_t *pk = sm + Plan::kPkOff + s * Plan::kPkStage;
+                        uint8_t *ex = sm + Plan::kExpOff + s * Plan::kExpStage;
+#pragma unroll 4
+                        for (int ch = ct; ch < kChunks; ch += kConvThreads)
+                            expand_store(ex, ch, *reinterpret_cast<const uint4 *>(pk + (ch >> 2) * 64 + (ch & 3) * 16));
+                        fence_proxy_async();
+                        mbar_arrive(ex_full(s));
+                        mbar_arrive(pk_empty(s));
+                    }
                 }
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Plan::kEpiRegs));
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Plan::kEpiRegs(DIRECT)));
         const int wg = (warp - 8) >> 2;                  // which 128 columns of the tile
         const int et = tid - kNonEpiThreads - wg * 128;  // 0..127 within the warpgroup
         const int wq = warp & 3;                         // TMEM lane quarter this warp may read
@@ -444,9 +519,9 @@ int make_map(CUtensorMap *map, const uint8_t *ptr, long rows, long K, int box_ro
     return 0;
 }
 
-template <int BN, bool GROUPED, bool U>
+template <int BN, bool GROUPED, bool U, bool DIRECT>
 int launch_t(const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &p, cudaStream_t stream) {
-    auto kern = gemm_tcgen05_kernel<BN, GROUPED, U>;
+    auto kern = gemm_tcgen05_kernel<BN, GROUPED, U, DIRECT>;
     const int smem = SmemPlan<BN>::kBytes;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_status(e, "gemm_tcgen05 attribute");
@@ -468,8 +543,9 @@ int launch_t(const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &p, cu
 
 int launch_gemm_tcgen05(const uint8_t *A, const uint8_t *B, const void *a_scale, const void *a_zero,
                         const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D, long M,
-                        long N, long K, long a_group, long b_group, int out_dtype, cudaStream_t stream) {
+                        long N, long K, long a_group, long b_group, int out_dtype, int direct, cudaStream_t stream) {
     TcParams p;
+    p.A = A; p.B = B;
     p.a_scale = static_cast<const __half *>(a_scale);
     p.a_zero = static_cast<const __half *>(a_zero);
     p.b_scale = static_cast<const __half *>(b_scale);
@@ -486,10 +562,14 @@ int launch_gemm_tcgen05(const uint8_t *A, const uint8_t *B, const void *a_scale,
     rc = make_map(&mb, B, N, K, bn);
     if (rc) return rc;
     const bool u = a_zero != nullptr;
-    if (grouped && bn == 256) return u ? launch_t<256, true, true>(ma, mb, p, stream) : launch_t<256, true, false>(ma, mb, p, stream);
-    if (grouped) return u ? launch_t<128, true, true>(ma, mb, p, stream) : launch_t<128, true, false>(ma, mb, p, stream);
-    if (bn == 256) return u ? launch_t<256, false, true>(ma, mb, p, stream) : launch_t<256, false, false>(ma, mb, p, stream);
-    return u ? launch_t<128, false, true>(ma, mb, p, stream) : launch_t<128, false, false>(ma, mb, p, stream);
+#define FLH_TC(BN_, G_) \
+    (direct ? (u ? launch_t<BN_, G_, true, true>(ma, mb, p, stream) : launch_t<BN_, G_, false, true>(ma, mb, p, stream)) \
+            : (u ? launch_t<BN_, G_, true, false>(ma, mb, p, stream) : launch_t<BN_, G_, false, false>(ma, mb, p, stream)))
+    if (grouped && bn == 256) return FLH_TC(256, true);
+    if (grouped) return FLH_TC(128, true);
+    if (bn == 256) return FLH_TC(256, false);
+    return FLH_TC(128, false);
+#undef FLH_TC
 }
 
 // Host-side read of the device status word the bounded waits write (synchronises the device).

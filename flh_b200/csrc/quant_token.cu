@@ -287,23 +287,27 @@ quant_token_asym_kernel(const TokenParams p) {
     if (lane == 0) { red[0][warp] = vmin; red[1][warp] = vmax; }
     __syncthreads();            // also: all reads of buf are complete, cb may alias it
     if (warp == 0) {
+        // one warp finishes the reduction and derives scale, reciprocal and zero-point for the row
         const int nw = (blockDim.x + 31) >> 5;
         float a = lane < nw ? red[0][lane] : 0.0f;
         float b = lane < nw ? red[1][lane] : 0.0f;
         a = warp_min(a); b = warp_max(b);
-        if (lane == 0) { bcast[0] = a; bcast[1] = b; }
+        if (lane == 0) {
+            float zmin = __fmul_rn(a, p.clip), zmax = __fmul_rn(b, p.clip);
+            if (zmin == 0.0f && zmax == 0.0f) { zmin = -1.0f; zmax = 1.0f; }
+            float scale32 = __fdiv_rn(__fsub_rn(zmax, zmin), 15.0f);
+            scale32 = __fdiv_rn(scale32, p.c);
+            __half sh = __float2half_rn(scale32);
+            if ((__half_as_ushort(sh) & 0x7fffu) == 0) sh = __ushort_as_half(0x0001u);
+            const float d = __fmul_rn(p.c, __half2float(sh));
+            const float rd0 = __frcp_rn(d);
+            const float zf0 = rintf(__fmul_rn(-zmin, rd0));
+            bcast[0] = rd0; bcast[1] = zf0;
+            p.scale[row] = sh; p.zero[row] = __float2half_rn(zf0);
+        }
     }
     __syncthreads();
-    float zmin = __fmul_rn(bcast[0], p.clip), zmax = __fmul_rn(bcast[1], p.clip);
-    if (zmin == 0.0f && zmax == 0.0f) { zmin = -1.0f; zmax = 1.0f; }
-    float scale32 = __fdiv_rn(__fsub_rn(zmax, zmin), 15.0f);
-    scale32 = __fdiv_rn(scale32, p.c);
-    __half sh = __float2half_rn(scale32);
-    if ((__half_as_ushort(sh) & 0x7fffu) == 0) sh = __ushort_as_half(0x0001u);
-    const float d = __fmul_rn(p.c, __half2float(sh));
-    const float rd = __frcp_rn(d);
-    const float zf = rintf(__fmul_rn(-zmin, rd));
-    if (t == 0) { p.scale[row] = sh; p.zero[row] = __float2half_rn(zf); }
+    const float rd = bcast[0], zf = bcast[1];
 
     // codes: clamp(rint(z * rd), -zero, 15 - zero) + zero; adding 1.5 * 2^23 rounds to the
     // nearest integer (ties to even) and leaves it in the low mantissa bits.

@@ -44,6 +44,9 @@ extern "C" {
 #define FLH_B200_GEMM_TCGEN05 1 /* TMA + int4->int8 expand in smem + tcgen05.mma kind::i8, TMEM accumulators */
 #define FLH_B200_GEMM_MMA_SYNC 2 /* legacy mma.sync m16n8k32 s8 path (bring-up cross-check, any M)           */
 #define FLH_B200_GEMM_STREAM 3  /* weight-streaming small-M path (M <= 32)                                    */
+#define FLH_B200_GEMM_TCGEN05_DIRECT 5 /* tcgen05 path whose converter warps load the packed operands from L2
+                                         straight into registers (no TMA staging): less shared-memory traffic */
+#define FLH_B200_GEMM_STREAM_SPLITK 4 /* the same with K cut across CTAs; needs workspace (see below)           */
 
 int flh_b200_version(void);
 const char *flh_b200_last_error(void);
@@ -113,7 +116,13 @@ int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t
  *   flh_gemm_i4_dequant_o16_kernel (flh/kernels/gemm_and_dequant_i4.cu:287-313, 315-469).
  *   N % 128 == 0 and K % 128 == 0 are required (as the reference kernel assumes), K <= 65536.
  *   algo: FLH_B200_GEMM_*.  workspace: device scratch of at least
- *   flh_b200_gemm_workspace_bytes(...) bytes (may be NULL when that is 0).
+ *   flh_b200_gemm_workspace_bytes(...) bytes, 256-byte aligned (may be NULL when that is 0).  Only the
+ *   split-K streaming kernel uses it (decode shapes whose N alone cannot fill the GPU): its first 4 KB
+ *   are arrival counters that must be ZERO before the first launch and are left zero by every launch;
+ *   launches that share a workspace must not overlap on the GPU.  With AUTO and no (or too small a)
+ *   workspace the plain streaming kernel runs instead.  Split-K adds the per-split binary32 chains in
+ *   split order, so with group scales its outputs can differ from the single chain in the last bit
+ *   (<= 1e-3 relative); without group scales the partial sums are int32 and the result is identical.
  * Replaces flhDenseLayerGEMM_i4_o16 (flh/kernels/gemm_and_dequant_i4.cu:471-508) and
  * flhDenseLayerGEMM_i4_o16_gs (flh/kernels/gemm_and_dequant_i4_gs.h); bound as
  * gemm_i4_dequant_o16(_gs) (flh/cuda/flh_cuda_bindings.cpp:75-113, 253-299). */

@@ -17,9 +17,18 @@ def _status_clean(cuda):
     assert st[0] == 0, f"a bounded wait in the tcgen05 kernel ran out: code {st[0]} in CTA {st[1]}"
 
 
+TCD = 5        # the direct-load variant (converter warps fetch packed operands from L2 into registers)
+
+
 @pytest.mark.parametrize("mode", MODES)
 def test_tcgen05_single_tile(cuda, mode):
     run_case(cuda, TC, make_case(31, 128, 256, 512, *mode))
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (1, 384, 1024), (515, 384, 1024), (300, 15360, 512), (256, 1024, 4096)])
+def test_tcgen05_direct_variant(cuda, mode, m, n, k):
+    run_case(cuda, TCD, make_case(m + n + k, m, n, k, *mode))
 
 
 @pytest.mark.parametrize("mode", MODES)

@@ -42,7 +42,10 @@ def test_argument_validation_without_a_device():
     # empty problems succeed without touching the device
     assert lib.flh_b200_quant_group_sym_i4(None, 0, 128, 1, None, None, None) == 0
     assert lib.flh_b200_gemm_i4_dequant(None, None, None, None, None, None, None, None, 0, 128, 256, 128, 128, 0, 0, None, 0, None) == 0
-    assert lib.flh_b200_gemm_pick_algo(16, 4096, 4096, 128, 128) == 3
+    assert lib.flh_b200_gemm_pick_algo(16, 22016, 4096, 128, 128) == 3      # enough row slabs: plain streaming
+    assert lib.flh_b200_gemm_pick_algo(16, 4096, 4096, 128, 128) == 4       # few slabs: split-K
+    assert lib.flh_b200_gemm_workspace_bytes(16, 4096, 4096, 128, 128, 0) == 4096 + 4 * 16 * 4096 * 4
+    assert lib.flh_b200_gemm_workspace_bytes(2048, 4096, 4096, 128, 128, 0) == 0
     assert lib.flh_b200_gemm_pick_algo(2048, 4096, 4096, 128, 128) == 1
 
 
