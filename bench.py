@@ -225,6 +225,26 @@ def run_ours(args, world, rank, local, dist):
             out["extra"] = extras(C, device, peaks)
             if world == 1:
                 out["cpu_baseline"] = cpu_had_quant(K, sample_rows=1024, reps=8)
+    elif args.workload == "had_quant_group":
+        # FLH's own CUDA contract: group-128 binary16 transform + symmetric int4 + pack
+        M, K = 16384, 4096
+        xs = [synth_activations(M, K, 100 + i + 10 * rank, device).view(-1, 128) for i in range(3)]
+        step_bytes = M * (2 * K + K // 2 + 2 * (K // 128))
+
+        def fn(i):
+            C.hadamard_and_quantize_i4(xs[i % 3])
+
+        with ClockSampler(local) as cs:
+            t = timed_loop(fn, steps, warmup, dist, device, sampler=cs)
+        ach = step_bytes * steps / t / 1e9
+        out.update(metric="had_quant_group128_GBps", unit="GB/s", value=world * ach, ms_per_step=t / steps * 1e3, dtype="f16",
+                   config={"workload": "fused group-128 Hadamard (binary16) + symmetric int4 quant + pack, f16 X[16384,4096] per GPU",
+                           "M_per_gpu": M, "K": K, "bytes_per_step_per_gpu": step_bytes,
+                           "l2": "three rotating 134 MB inputs, each larger than the 126 MB L2",
+                           "parallelism": f"token-sharded x{world}, no collective"},
+                   clocks=cs.summary(), gpu_launches=steps,
+                   roofline={"kernel": "quant_group_sym_kernel<7,true>", "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"],
+                             "peak_src": peaks["src"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None})
     elif args.workload in ("gemm_prefill", "gemm_decode"):
         prefill = args.workload == "gemm_prefill"
         M, K, N = (2048, 4096, 12288) if prefill else (16, 4096, 22016)

@@ -7,9 +7,14 @@ GEMM with fused dequantisation) on hand-written sm_100a kernels behind a C ABI.
 
 Importing the package loads libflh_b200.so and fails if it is missing: there is no fallback.
 """
+import sys
+
 from . import _lib
 
-_lib.load()
+# `python -m flh_b200.build` imports this package before the library exists (or while it is stale);
+# every other import loads the library now and fails if that is impossible.
+if "flh_b200.build" not in getattr(sys, "orig_argv", []):
+    _lib.load()
 
 from . import _CUDA, functional, hadamard, nn  # noqa: E402
 

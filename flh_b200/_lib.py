@@ -26,6 +26,8 @@ SIGNATURES = {
     "flh_b200_weight_rowsum": (c_int, [c_void_p, c_long, c_long, c_long, c_void_p, c_void_p]),
     "flh_b200_gemm_i4_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_long, c_long, c_long, c_long, c_long, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "flh_b200_gemm_i4_dequant_decode_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                        c_void_p, c_long, c_long, c_long, c_long, c_long, c_int, c_void_p]),
     "flh_b200_gemm_workspace_bytes": (c_size_t, [c_long, c_long, c_long, c_long, c_long, c_int]),
     "flh_b200_gemm_pick_algo": (c_int, [c_long, c_long, c_long, c_long, c_long]),
     "flh_b200_gemm_status": (c_int, [c_void_p]),

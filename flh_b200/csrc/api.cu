@@ -38,6 +38,8 @@ int launch_gemm_mma_tile(const uint8_t *, const uint8_t *, const void *, const v
 int launch_gemm_stream(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
                        const int32_t *, const void *, void *, long, long, long, long, long, int,
                        int, void *, cudaStream_t);
+int launch_gemm_stream_static(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
+                              const int32_t *, const void *, void *, long, long, long, long, long, int, cudaStream_t);
 int stream_splits(long M, long N, long K);
 size_t stream_scratch_bytes(long M, long N, int splits);
 int launch_gemm_tcgen05(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
@@ -194,6 +196,25 @@ int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_s
         default:
             return fail(FLH_B200_EINVAL, "unknown algo %d", algo);
     }
+}
+
+int flh_b200_gemm_i4_dequant_decode_noalloc(const uint8_t *A, const uint8_t *B, const void *a_scale, const void *a_zero,
+                                            const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D,
+                                            long M, long N, long K, long a_group, long b_group, int out_dtype,
+                                            void *stream) {
+    FLH_REQUIRE(M >= 0 && N >= 0 && K > 0, FLH_B200_EINVAL, "bad shape M=%ld N=%ld K=%ld", M, N, K);
+    FLH_REQUIRE(M <= 32, FLH_B200_EINVAL, "the decode entry point serves M <= 32 (got %ld)", M);
+    FLH_REQUIRE(K % 128 == 0 && K <= 65536, FLH_B200_EINVAL, "K must be a multiple of 128 and <= 65536 (got %ld)", K);
+    FLH_REQUIRE(N % 128 == 0, FLH_B200_EINVAL, "N must be a multiple of 128 (got %ld)", N);
+    FLH_REQUIRE(a_group == 128 || a_group == K, FLH_B200_EINVAL, "a_group must be 128 or K (got %ld)", a_group);
+    FLH_REQUIRE(b_group == 128 || b_group == K, FLH_B200_EINVAL, "b_group must be 128 or K (got %ld)", b_group);
+    FLH_REQUIRE(out_dtype == FLH_B200_F16 || out_dtype == FLH_B200_BF16, FLH_B200_EINVAL, "out_dtype must be F16 or BF16");
+    if (M == 0 || N == 0) return 0;
+    FLH_REQUIRE(A && B && a_scale && b_scale && D, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(!a_zero || b_rowsum, FLH_B200_EINVAL, "a_zero needs b_rowsum");
+    FLH_REQUIRE(aligned16(A) && aligned16(B), FLH_B200_EALIGN, "A and B must be 16-byte aligned");
+    return launch_gemm_stream_static(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group,
+                                     out_dtype, static_cast<cudaStream_t>(stream));
 }
 
 int flh_b200_gemm_status(int *out) {

@@ -574,6 +574,47 @@ int launch_gemm_stream(const uint8_t *A, const uint8_t *B, const void *a_scale, 
     return wide ? launch_stream_w<4, 4>(p, u, stream) : launch_stream_w<2, 4>(p, u, stream);
 }
 
+// --------------------------------------------------------------------------------------------
+// Split-K decode GEMM for callers that cannot allocate device memory: the scratch the kernel needs
+// (slab counters + per-split partial sums) lives in this file-scope device array instead of a caller
+// buffer.  Every GPU that loads the library holds the array until the process exits.
+constexpr size_t kStaticScratchBytes = 4096 + (2u << 20);      // counters + 2 MiB of partial sums
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle for the runtime, never a device address: the address
+// is asked for once per device, with that device current, and remembered.
+static void *g_static_scratch_addr[64];
+
+size_t stream_static_scratch_capacity() { return kStaticScratchBytes; }
+
+int launch_gemm_stream_static(const uint8_t *A, const uint8_t *B, const void *a_scale, const void *a_zero,
+                              const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D,
+                              long M, long N, long K, long a_group, long b_group, int out_dtype,
+                              cudaStream_t stream) {
+    const int splits = stream_splits(M, N, K);
+    if (splits <= 1)        // this shape fills the GPU without cutting K: no scratch is involved at all
+        return launch_gemm_stream(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, 1, nullptr, stream);
+    const size_t need = stream_scratch_bytes(M, N, splits);
+    if (need > kStaticScratchBytes)
+        return fail(FLH_B200_EINVAL,
+                    "M=%ld N=%ld K=%ld needs %zu bytes of split-K scratch, more than the %zu bytes built into the library; "
+                    "use flh_b200_gemm_i4_dequant with a caller workspace", M, N, K, need, (size_t)kStaticScratchBytes);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_status(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(FLH_B200_EUNSUPPORTED, "device ordinal %d is outside the table of 64", dev);
+    void *ptr = g_static_scratch_addr[dev];
+    if (!ptr) {             // first call on this device (do it before any stream capture)
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess) return cuda_status(e, "cudaGetSymbolAddress(static scratch)");
+        g_static_scratch_addr[dev] = ptr;
+    }
+    // the array keeps whatever the previous call left: the arrival counters must start at zero
+    e = cudaMemsetAsync(ptr, 0, 4096, stream);
+    if (e != cudaSuccess) return cuda_status(e, "clearing the static scratch counters");
+    return launch_gemm_stream(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, splits, ptr, stream);
+}
+
 // rowsum[n, g] = sum of signed nibbles of row n over K-group g.  One warp per (row, group chunk).
 __global__ void weight_rowsum_kernel(const uint8_t *__restrict__ B, int N, int K, int group,
                                      int32_t *__restrict__ rs) {

@@ -137,6 +137,27 @@ size_t flh_b200_gemm_workspace_bytes(long M, long N, long K, long a_group, long 
 /* Which algorithm FLH_B200_GEMM_AUTO resolves to for this shape (one of FLH_B200_GEMM_*). */
 int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group);
 
+/* Decode GEMM (M <= 32) for callers that must not allocate.  Same arguments and results as
+ * flh_b200_gemm_i4_dequant with algo = FLH_B200_GEMM_STREAM_SPLITK, but the split-K scratch is not a
+ * caller buffer: it is a 4 KiB + 2 MiB array built into the library's device image, so a serving loop
+ * that runs inside a fixed memory budget, a plugin host that owns every cudaMalloc, or code running
+ * where allocation is forbidden (between two graph launches, inside a real-time section) can still use
+ * the split-K kernel.  This entry point calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   - Limit: shapes whose split-K scratch exceeds the built-in array (for example M = 32, N = 9216) are
+ *     rejected with FLH_B200_EINVAL and a message naming the size; use the workspace form for those.
+ *     Shapes that need no split (many output columns) run the plain streaming kernel, scratch untouched.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ *     that first call outside any stream capture.  Every GPU that loads the library carries the array
+ *     until the process exits.
+ *   - All calls on a device share the one array and it keeps the previous call's contents; each call
+ *     re-zeroes the counters on `stream` before the kernel.  Two calls whose kernels could overlap on the
+ *     GPU (different streams, no ordering between them) race on it: order them or use the workspace form.
+ * No counterpart in FLH (its GEMM takes no scratch). */
+int flh_b200_gemm_i4_dequant_decode_noalloc(const uint8_t *A, const uint8_t *B, const void *a_scale,
+                                            const void *a_zero, const void *b_scale, const int32_t *b_rowsum,
+                                            const void *bias, void *D, long M, long N, long K, long a_group,
+                                            long b_group, int out_dtype, void *stream);
+
 /* Reads (and clears) the device status words of the tcgen05 GEMM: out[0] = 0, or the code of the
  * first bounded wait that ran out (1 TMA producer, 2/3 MMA issuer, 4/5 converters, 6/7 epilogue),
  * out[1] = the CTA that reported it.  SYNCHRONISES the device; for tests and post-mortems only.
