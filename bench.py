@@ -248,13 +248,14 @@ def run_ours(args, world, rank, local, dist):
     elif args.workload in ("gemm_prefill", "gemm_decode"):
         prefill = args.workload == "gemm_prefill"
         M, K, N = (2048, 4096, 12288) if prefill else (16, 4096, 22016)
-        sets = [gemm_inputs(C, M, N, K, True, False, device, seed=s + 10 * rank) for s in range(3 if not prefill else 1)]
+        asym = args.act_mode == "token_asym"          # per-token asymmetric x per-channel weights, else group-128 symmetric
+        sets = [gemm_inputs(C, M, N, K, not asym, asym, device, seed=s + 10 * rank) for s in range(3 if not prefill else 1)]
         D = torch.empty((M, N), dtype=torch.float16, device=device)
         flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device) if prefill else None
 
         def fn(i):
             A, B, sa, sb, za, rs = sets[i % len(sets)]
-            C.gemm_i4_dequant(A, B, sa, sb, out=D)
+            C.gemm_i4_dequant(A, B, sa, sb, A_zero=za, B_rowsum=rs, out=D)
 
         with ClockSampler(local) as cs:
             t = timed_loop(fn, steps, warmup, dist, device, graph=not prefill, sampler=cs)
@@ -266,13 +267,15 @@ def run_ours(args, world, rank, local, dist):
                                  "peak": 2 * peaks["bf16_tflops"], "peak_src": peaks["src"] + " bf16 x2 (dense INT8 runs at twice the bf16 rate)",
                                  "unit": "TOPS", "frac": ops * steps / t / 1e12 / (2 * peaks["bf16_tflops"]), "traffic": None})
         else:
-            b = N * K // 2 + 2 * N * (K // 128) + M * K // 2 + 2 * M * (K // 128) + 2 * M * N
+            gcols = 1 if asym else K // 128
+            b = N * K // 2 + 2 * N * gcols + M * K // 2 + 2 * M * gcols + 2 * M * N
             value = world * b * steps / t / 1e9
             out.update(metric="int4_gemm_decode_GBps", unit="GB/s", value=value, dtype="s8 x s8 -> s32 (int4 codes)",
                        roofline={"bound": "hbm", "achieved": b * steps / t / 1e9, "peak": peaks["hbm_gbs"],
                                  "peak_src": peaks["src"], "unit": "GB/s", "frac": b * steps / t / 1e9 / peaks["hbm_gbs"], "traffic": None})
         out.update(ms_per_step=t / steps * 1e3, clocks=cs.summary(), gpu_launches=steps,
-                   config={"workload": f"int4 GEMM + group-128 dequant, M={M}, {K}->{N}, f16 out", "M": M, "N": N, "K": K,
+                   config={"workload": f"int4 GEMM + {'per-token asymmetric x per-channel' if asym else 'group-128'} dequant, M={M}, {K}->{N}, f16 out",
+                           "M": M, "N": N, "K": K,
                            "l2": "weights of three rotating problems (3 x 45 MB > L2); the K steps run as one CUDA graph" if not prefill else "operands re-used across steps (compute-bound)",
                            "parallelism": f"replicated x{world}, no collective"})
     elif args.workload in ("llama7b_prefill", "llama7b_decode", "llama70b_prefill", "llama70b_decode"):

@@ -388,26 +388,31 @@ gemm_stream_kernel(const GemmParams p) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) c[i][k] += c2[k];
                 if (GROUPED) {
-                    // c[i][2h + j]: channel ch0 + 8h, token i*8 + 2t + j
-                    const __half *sbS = reinterpret_cast<const __half *>(st + Plan::kSB);
-                    const int32_t *rsS = reinterpret_cast<const int32_t *>(st + Plan::kRS);
-                    const __half *saS = reinterpret_cast<const __half *>(st + Plan::kSA);
-                    const __half *zaS = reinterpret_cast<const __half *>(st + Plan::kZA);
+                    // c[i][2h + j]: channel ch0 + 8h, token i*8 + 2t + j.  Scales of this K-group come from the
+                    // stage in shared memory; without zero-points the x256 of the accumulator rides in the scale.
+                    const int r0 = warp * 16 + g;
+                    float sbv[2], sav[2];
+                    int rsv[2] = {0, 0}, zav[2] = {0, 0};
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        const int rr = warp * 16 + g + 8 * h;
-                        const float sb = p.gb_cols == 1 ? sb_c[h] : __half2float(sbS[2 * rr + half]);
-                        const int rs = has_zero ? rsS[2 * rr + half] : 0;
+                        sbv[h] = p.gb_cols == 1 ? sb_c[h] : __half2float(reinterpret_cast<const __half *>(st + Plan::kSB)[2 * (r0 + 8 * h) + half]);
+                        if (has_zero) rsv[h] = reinterpret_cast<const int32_t *>(st + Plan::kRS)[2 * (r0 + 8 * h) + half];
+                    }
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int tk = i * 8 + 2 * t + j;
+                        sav[j] = p.ga_cols == 1 ? sa_c[i][j] : __half2float(reinterpret_cast<const __half *>(st + Plan::kSA)[2 * tk + half]);
+                        if (has_zero) zav[j] = p.ga_cols == 1 ? za_c[i][j] : (int)__half2float(reinterpret_cast<const __half *>(st + Plan::kZA)[2 * tk + half]);
+                        if (!has_zero) sav[j] *= (1.0f / 256.0f);
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            const int tk = i * 8 + 2 * t + j;
-                            const float sa = p.ga_cols == 1 ? sa_c[i][j] : __half2float(saS[2 * tk + half]);
-                            const int za = !has_zero ? 0 : (p.ga_cols == 1 ? za_c[i][j] : (int)__half2float(zaS[2 * tk + half]));
-                            const int32_t I = (c[i][2 * h + j] >> 8) - za * rs;
-                            acc[i][2 * h + j] = __fmaf_rn((float)I, __fmul_rn(sa, sb), acc[i][2 * h + j]);
+                            const int32_t I = has_zero ? (c[i][2 * h + j] >> 8) - zav[j] * rsv[h] : c[i][2 * h + j];
+                            acc[i][2 * h + j] = __fmaf_rn((float)I, __fmul_rn(sav[j], sbv[h]), acc[i][2 * h + j]);
                             c[i][2 * h + j] = 0;
                         }
-                    }
                 }
             }
         }

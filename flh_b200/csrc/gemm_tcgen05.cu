@@ -358,9 +358,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         if (!mbar_wait(ex_empty(s), ((it / S) & 1) ^ 1, abort_flag, 5)) { ok = false; break; }
                         const uint8_t *pk = sm + Plan::kPkOff + s * Plan::kPkStage;
                         uint8_t *ex = sm + Plan::kExpOff + s * Plan::kExpStage;
-#pragma unroll 4
-                        for (int ch = ct; ch < kChunks; ch += kConvThreads)
-                            expand_store(ex, ch, *reinterpret_cast<const uint4 *>(pk + (ch >> 2) * 64 + (ch & 3) * 16));
+                        // the packed chunks are fetched in batches (independent shared loads in flight) and then
+                        // expanded; with group scales the epilogue owns the registers, so the batches are smaller
+                        constexpr int kPerT = (kChunks + kConvThreads - 1) / kConvThreads;
+                        constexpr int kBatch = GROUPED ? 4 : kPerT;
+#pragma unroll
+                        for (int j0 = 0; j0 < kPerT; j0 += kBatch) {
+                            uint4 wv[kBatch];
+#pragma unroll
+                            for (int j = 0; j < kBatch; ++j) {
+                                const int ch = ct + (j0 + j) * kConvThreads;
+                                if (j0 + j < kPerT && ch < kChunks) wv[j] = *reinterpret_cast<const uint4 *>(pk + (ch >> 2) * 64 + (ch & 3) * 16);
+                            }
+#pragma unroll
+                            for (int j = 0; j < kBatch; ++j) {
+                                const int ch = ct + (j0 + j) * kConvThreads;
+                                if (j0 + j < kPerT && ch < kChunks) expand_store(ex, ch, wv[j]);
+                            }
+                        }
                         fence_proxy_async();
                         mbar_arrive(ex_full(s));
                         mbar_arrive(pk_empty(s));

@@ -105,19 +105,21 @@ quant_group_sym_kernel(const uint4 *__restrict__ x, uint32_t *__restrict__ q,
             if (__half2float(sh) <= __half2float(__float2half_rn(1e-6f))) sh = __float2half_rn(1.0f);
             const float rcp = __frcp_rn(__half2float(sh));
 
-            // q = clamp(rint(half(x * rcp)), -8, 7); adding 1032 (= 1024 + 8) in binary16 rounds
-            // to the nearest integer, ties to even, and leaves q + 8 in the low four bits.
-            const __half2 lo = __float2half2_rn(-8.0f), hi = __float2half2_rn(7.0f);
+            // q = rint(half(x * rcp)): |x| <= max and scale = half(max / 7) keep |q| <= 7 for finite input, so
+            // the reference's clamp never acts.  Adding 1032 (= 1024 + 8) in binary16 rounds to the nearest
+            // integer, ties to even, and leaves q + 8 in the low four bits of each half.
             const __half2 magic = __float2half2_rn(1032.0f);
-            uint32_t packed = 0;
+            uint32_t nib[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float2 f = __half22float2(h[j]);
-                __half2 t = __floats2half2_rn(__fmul_rn(f.x, rcp), __fmul_rn(f.y, rcp));
-                t = __hmax2(__hmin2(t, hi), lo);
-                const uint32_t w = (h22u(__hadd2(t, magic)) & 0x000F000Fu) ^ 0x00080008u;
-                packed |= ((w | (w >> 12)) & 0xFFu) << (8 * j);
+                const __half2 t = __floats2half2_rn(__fmul_rn(f.x, rcp), __fmul_rn(f.y, rcp));
+                nib[j] = (h22u(__hadd2(t, magic)) & 0x000F000Fu) ^ 0x00080008u;   // two's-complement nibbles at bits 0-3, 16-19
             }
+            // nib[j] = [even code, 0, odd code, 0] as bytes; gather evens and odds, then byte j = even | odd << 4
+            const uint32_t a01 = nib[1] * 256u + nib[0], a23 = nib[3] * 256u + nib[2];
+            const uint32_t ev = __byte_perm(a01, a23, 0x5410), od = __byte_perm(a01, a23, 0x7632);
+            const uint32_t packed = od * 16u + ev;
             if (c < total_chunks) {
                 q[c] = packed;
                 if (lig == 0) scales[c / L] = sh;

@@ -71,7 +71,7 @@ def test_fht_inplace_bit_exact(cuda, n, rows):
     assert np.array_equal(y.cpu().numpy().view(np.uint16), O.fht_f16(x).view(np.uint16))
 
 
-TOKEN_SHAPES = [(1, 4096), (16, 4096), (5, 8192), (3, 16384), (2, 32768), (3, 64), (3, 128), (4, 256), (3, 512),
+TOKEN_SHAPES = [(1, 4096), (16, 4096), (5, 4096), (2, 2048), (5, 8192), (3, 16384), (2, 32768), (3, 64), (3, 128), (4, 256), (3, 512),
                 (3, 1024), (3, 2048), (4, 11008), (3, 14336), (2, 28672), (3, 3584), (3, 7168), (2, 1536), (2, 768)]
 
 

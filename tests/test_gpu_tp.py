@@ -1,0 +1,65 @@
+"""Column/row-parallel W4A4 linears on two GPUs (NCCL) against the single-GPU layer."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import flh_b200
+        from flh_b200.nn import ActQuantizer, LinearFLH
+        from flh_b200.tp import ColumnParallelLinearFLH, RowParallelLinearFLH, shard_column, shard_row
+        dev = torch.device("cuda", rank)
+        g = torch.Generator().manual_seed(11)
+        K, N, M = 2048, 1024, 96
+        for gs, sym in ((128, True), (-1, False)):
+            lin = torch.nn.Linear(K, N, bias=False)
+            lin.weight.data = torch.randn(N, K, generator=g) * 0.02
+            full = LinearFLH.from_float(lin.half(), weight_group_size=gs, in_group_size=128).to(dev)
+            x = torch.randn(M, K, generator=g).half().to(dev)
+            aq = ActQuantizer(bits=4, group_size=128 if sym else -1, sym=sym, use_hadamard=False, packed_output=True)
+            s, z, q = aq(x)
+            y_full = full(q, s, z)
+            col = ColumnParallelLinearFLH(shard_column(full, rank, world), gather_output=True)
+            y_col = col(q, s, z)
+            assert torch.equal(y_col.view(torch.int16), y_full.view(torch.int16)), "column-parallel"
+            # row-parallel: every rank quantises its own K-slice of the activations
+            kk = K // world
+            s2, z2, q2 = aq(x[:, rank * kk:(rank + 1) * kk].contiguous())
+            row = RowParallelLinearFLH(shard_row(full, rank, world))
+            y_row = row(q2, s2, z2)
+            ref = x.float() @ full.get_weight(torch.float32).t()
+            err_full = (y_full.float() - ref).abs().max() / ref.abs().max()
+            err_row = (y_row.float() - ref).abs().max() / ref.abs().max()
+            assert err_row < 2.0 * err_full + 1e-2, (err_row, err_full)    # same quantisation noise level
+            if sym:     # group-128 quantisation is unchanged by the K split: only the f16 summation differs
+                rel = (y_row.float() - y_full.float()).abs().max() / y_full.float().abs().max()
+                assert rel < 2e-3, rel
+        if rank == 0:
+            open(os.path.join(tmp, "ok"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp2_nccl(cuda, tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok").exists()
