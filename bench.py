@@ -204,7 +204,10 @@ def run_ours(args, world, rank, local, dist):
         ach = step_bytes * steps / t / 1e9
         out["roofline"] = {"kernel": "quant_token_asym_kernel<6,0,false,true>", "bound": "hbm", "achieved": ach,
                            "peak": peaks["hbm_gbs"], "peak_src": peaks["src"], "unit": "GB/s",
-                           "frac": ach / peaks["hbm_gbs"], "traffic": None}
+                           "frac": ach / peaks["hbm_gbs"],
+                           # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
+                           # summarised in profiles/quant_token_asym_M16384_K4096.md (134.3 MB + 17.9 MB)
+                           "traffic": 152.2e6, "traffic_unit": "bytes/launch (ncu)", "algorithmic_bytes": step_bytes}
         # ---- end to end through the public API with host buffers ----
         xh = [x.cpu().pin_memory() for x in xs[:2]]
         qh = torch.empty((M, K // 2), dtype=torch.uint8).pin_memory()
@@ -303,13 +306,19 @@ def run_ours(args, world, rank, local, dist):
         steps, warmup = min(steps, 20), min(warmup, 5)
         with ClockSampler(local) as cs:
             # a decode step is ~600 short launches: it is recorded once into a CUDA graph and replayed
-            t = timed_loop(fn, steps, max(warmup, 3), dist, device, sampler=cs, graph=(not prefill and world == 1))
+            try:
+                t = timed_loop(fn, steps, max(warmup, 3), dist, device, sampler=cs, graph=not prefill)
+                graphed = not prefill
+            except Exception as e:          # a capture that fails (e.g. a collective that refuses it) falls back to plain launches
+                sys.stderr.write(f"CUDA graph capture failed ({e}); timing plain launches\n")
+                t = timed_loop(fn, steps, max(warmup, 3), dist, device, sampler=cs, graph=False)
+                graphed = False
         out.update(metric="w4a4_llama_%s_tok_per_s" % ("prefill" if prefill else "decode"), unit="tok/s",
                    value=tokens * steps / t, ms_per_step=t / steps * 1e3, dtype="int4 codes, s32 accumulate, f16 activations",
                    steps=steps, warmup=max(warmup, 3), scaling="strong" if world > 1 else "weak", clocks=cs.summary(),
                    config={"workload": args.workload, **shape, "act_mode": args.act_mode, "batch": B,
                            "seq_or_ctx": 2048 if prefill else 1024, "parallelism": f"tp{world}" if world > 1 else "single GPU",
-                           "weights": "random int4 codes and scales (no checkpoint)"})
+                           "weights": "random int4 codes and scales (no checkpoint)", "cuda_graph": graphed})
     else:
         raise SystemExit(f"unknown workload {args.workload}")
     st = C.gemm_status()
