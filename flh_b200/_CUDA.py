@@ -143,19 +143,20 @@ def _sign_bits(n: int, device):
         return 1, None
     key = (k, str(device))
     if key not in _SIGN_CACHE:
-        words = (k + 31) // 32
         s8 = np.ascontiguousarray(signs, dtype=np.int8)
-        out = np.zeros((k, words), dtype=np.uint32)
+        out = np.zeros((_lib.load().flh_b200_sign_table_bytes(k) + 3) // 4, dtype=np.uint32)
         _lib.check(_lib.load().flh_b200_pack_signs(s8.ctypes.data_as(ctypes.c_void_p), k,
                                                    out.ctypes.data_as(ctypes.c_void_p)), "pack_signs")
         _SIGN_CACHE[key] = torch.from_numpy(out.view(np.int32)).to(device)
     return k, _SIGN_CACHE[key]
 
 
-def quant_token_asym_i4(x, hadamard: bool = True, clip: float = 1.0):
+def quant_token_asym_i4(x, hadamard: bool = True, clip: float = 1.0, exact_factor: bool = False):
     """x [M, K] f16/bf16 (row stride allowed) -> (q u8[M,K/2] codes 0..15, scale f16[M], zero f16[M]).
     hadamard=True applies the full-width transform of matmul_hadU (flh/functional/hadamard.py:92-113)
-    before the per-token asymmetric quantiser of fake_quant/quant_utils.py:94-128."""
+    before the per-token asymmetric quantiser of fake_quant/quant_utils.py:94-128.  For K = kfac * 2^m the
+    kfac x kfac factor runs on the tensor cores; exact_factor=True sums it sequentially instead (bit-exact
+    with the CPU oracle, slower)."""
     _check(x.is_cuda, "Input tensor must be on CUDA")
     _check(x.dtype in (torch.float16, torch.bfloat16), "Input tensor must be float16 or bfloat16")
     _check(x.dim() == 2 and x.stride(1) == 1, "Input tensor must be 2D with unit inner stride")
@@ -166,7 +167,8 @@ def quant_token_asym_i4(x, hadamard: bool = True, clip: float = 1.0):
     z = torch.empty((M,), dtype=torch.float16, device=x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.load().flh_b200_quant_token_asym_i4(
-            _ptr(x), BF16 if x.dtype == torch.bfloat16 else F16, M, K, x.stride(0) if M > 1 else K, int(hadamard), kfac,
+            _ptr(x), BF16 if x.dtype == torch.bfloat16 else F16, M, K, x.stride(0) if M > 1 else K,
+            (2 if exact_factor else 1) if hadamard else 0, kfac,
             _ptr(bits), float(clip), _ptr(q), _ptr(s), _ptr(z), _stream(x)), "quant_token_asym_i4")
     return q, s, z
 
@@ -211,7 +213,7 @@ def gemm_i4_dequant(A, B, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=Non
     lib = _lib.load()
     with torch.cuda.device(A.device):
         stream = _stream(A)
-        need = lib.flh_b200_gemm_workspace_bytes(M, N, K, ag, bg, algo) if M <= 32 else 0
+        need = lib.flh_b200_gemm_workspace_bytes(M, N, K, ag, bg, algo) if M <= 64 else 0
         ws = _workspace(A.device, stream, need) if need else None
         _lib.check(lib.flh_b200_gemm_i4_dequant(
             _ptr(A), _ptr(B), _ptr(A_scale), _ptr(A_zero), _ptr(B_scale), _ptr(B_rowsum), _ptr(bias), _ptr(D),
@@ -224,6 +226,13 @@ def gemm_status():
     """[code, cta, 0, 0] of the tcgen05 GEMM's bounded waits; synchronises.  0 = clean."""
     out = (ctypes.c_int * 4)()
     _lib.check(_lib.load().flh_b200_gemm_status(out), "gemm_status")
+    return list(out)
+
+
+def gemm_wait_profile():
+    """Nanoseconds the tcgen05 GEMM's roles waited on each other since the last call (see the header)."""
+    out = (ctypes.c_ulonglong * 8)()
+    _lib.check(_lib.load().flh_b200_gemm_wait_profile(out), "gemm_wait_profile")
     return list(out)
 
 

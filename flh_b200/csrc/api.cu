@@ -47,6 +47,7 @@ int launch_gemm_tcgen05(const uint8_t *, const uint8_t *, const void *, const vo
                         cudaStream_t);
 
 int gemm_tcgen05_status(int *);
+int gemm_tcgen05_wait_profile(unsigned long long *);
 int gemm_tcgen05_status_clear();
 
 static bool is_pow2(long v) { return v > 0 && (v & (v - 1)) == 0; }
@@ -99,6 +100,7 @@ int flh_b200_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, lo
     FLH_REQUIRE(M >= 0 && K > 0, FLH_B200_EINVAL, "bad shape M=%ld K=%ld", M, K);
     FLH_REQUIRE(in_dtype == FLH_B200_F16 || in_dtype == FLH_B200_BF16, FLH_B200_EINVAL, "in_dtype must be F16 or BF16");
     FLH_REQUIRE(K % 64 == 0 && K <= 32768, FLH_B200_EINVAL, "K must be a multiple of 64 and <= 32768 (got %ld)", K);
+    FLH_REQUIRE(hadamard >= 0 && hadamard <= 2, FLH_B200_EINVAL, "hadamard must be 0, 1 or 2 (got %d)", hadamard);
     FLH_REQUIRE(ld >= K && ld % 8 == 0, FLH_B200_EALIGN, "row stride must be >= K and a multiple of 8 elements (got %ld)", ld);
     FLH_REQUIRE(clip > 0.0f && clip <= 1.0f, FLH_B200_EINVAL, "clip ratio must be in (0, 1]");
     if (hadamard) {
@@ -114,17 +116,31 @@ int flh_b200_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, lo
     FLH_REQUIRE(x && q && scale && zero, FLH_B200_EINVAL, "null pointer");
     FLH_REQUIRE(aligned16(x), FLH_B200_EALIGN, "x must be 16-byte aligned");
     FLH_REQUIRE((reinterpret_cast<uintptr_t>(q) & 7) == 0, FLH_B200_EALIGN, "q must be 8-byte aligned");
-    return launch_quant_token_asym(x, in_dtype, M, K, ld, hadamard != 0, kfac, sign_bits, clip, q, scale,
+    FLH_REQUIRE(kfac == 1 || aligned16(sign_bits), FLH_B200_EALIGN, "the factor table must be 16-byte aligned");
+    return launch_quant_token_asym(x, in_dtype, M, K, ld, hadamard, kfac, sign_bits, clip, q, scale,
                                    zero, static_cast<cudaStream_t>(stream));
+}
+
+size_t flh_b200_sign_table_bytes(int kfac) {
+    if (kfac <= 0) return 0;
+    const size_t bits_bytes = ((size_t)kfac * ((kfac + 31) / 32) * 4 + 15) / 16 * 16;
+    const size_t kp = (size_t)(kfac + 15) / 16 * 16;
+    return bits_bytes + kp * kp * 2;
 }
 
 int flh_b200_pack_signs(const int8_t *signs, int kfac, uint32_t *out) {
     FLH_REQUIRE(signs && out && kfac > 0, FLH_B200_EINVAL, "bad arguments");
     const int words = (kfac + 31) / 32;
-    memset(out, 0, sizeof(uint32_t) * (size_t)kfac * words);
+    memset(out, 0, flh_b200_sign_table_bytes(kfac));
     for (int k = 0; k < kfac; ++k)
         for (int j = 0; j < kfac; ++j)
             if (signs[k * kfac + j] < 0) out[k * words + (j >> 5)] |= 1u << (j & 31);
+    // the same matrix as bfloat16 +-1 (0x3F80 / 0xBF80), padded with zeros to a multiple of 16
+    const size_t bits_bytes = ((size_t)kfac * words * 4 + 15) / 16 * 16;
+    uint16_t *mat = reinterpret_cast<uint16_t *>(reinterpret_cast<uint8_t *>(out) + bits_bytes);
+    const int kp = (kfac + 15) / 16 * 16;
+    for (int k = 0; k < kfac; ++k)
+        for (int j = 0; j < kfac; ++j) mat[(size_t)k * kp + j] = signs[k * kfac + j] < 0 ? 0xBF80u : 0x3F80u;
     return 0;
 }
 
@@ -139,13 +155,13 @@ int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t
 
 int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group) {
     (void)a_group; (void)b_group;
-    if (M <= 32) return stream_splits(M, N, K) > 1 ? FLH_B200_GEMM_STREAM_SPLITK : FLH_B200_GEMM_STREAM;
+    if (M <= 64) return stream_splits(M, N, K) > 1 ? FLH_B200_GEMM_STREAM_SPLITK : FLH_B200_GEMM_STREAM;
     return FLH_B200_GEMM_TCGEN05;
 }
 
 size_t flh_b200_gemm_workspace_bytes(long M, long N, long K, long a_group, long b_group, int algo) {
     if (algo == FLH_B200_GEMM_AUTO) algo = flh_b200_gemm_pick_algo(M, N, K, a_group, b_group);
-    if (algo != FLH_B200_GEMM_STREAM_SPLITK || M > 32) return 0;
+    if (algo != FLH_B200_GEMM_STREAM_SPLITK || M > 64) return 0;
     return stream_scratch_bytes(M, N, stream_splits(M, N, K));
 }
 
@@ -174,10 +190,10 @@ int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_s
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (algo) {
         case FLH_B200_GEMM_STREAM:
-            FLH_REQUIRE(M <= 32, FLH_B200_EINVAL, "the streaming kernel serves M <= 32 (got %ld)", M);
+            FLH_REQUIRE(M <= 64, FLH_B200_EINVAL, "the streaming kernel serves M <= 64 (got %ld)", M);
             return launch_gemm_stream(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, 1, nullptr, s);
         case FLH_B200_GEMM_STREAM_SPLITK: {
-            FLH_REQUIRE(M <= 32, FLH_B200_EINVAL, "the streaming kernel serves M <= 32 (got %ld)", M);
+            FLH_REQUIRE(M <= 64, FLH_B200_EINVAL, "the streaming kernel serves M <= 64 (got %ld)", M);
             const int splits = stream_splits(M, N, K);
             if (splits <= 1)
                 return launch_gemm_stream(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, 1, nullptr, s);
@@ -203,7 +219,7 @@ int flh_b200_gemm_i4_dequant_decode_noalloc(const uint8_t *A, const uint8_t *B, 
                                             long M, long N, long K, long a_group, long b_group, int out_dtype,
                                             void *stream) {
     FLH_REQUIRE(M >= 0 && N >= 0 && K > 0, FLH_B200_EINVAL, "bad shape M=%ld N=%ld K=%ld", M, N, K);
-    FLH_REQUIRE(M <= 32, FLH_B200_EINVAL, "the decode entry point serves M <= 32 (got %ld)", M);
+    FLH_REQUIRE(M <= 64, FLH_B200_EINVAL, "the decode entry point serves M <= 64 (got %ld)", M);
     FLH_REQUIRE(K % 128 == 0 && K <= 65536, FLH_B200_EINVAL, "K must be a multiple of 128 and <= 65536 (got %ld)", K);
     FLH_REQUIRE(N % 128 == 0, FLH_B200_EINVAL, "N must be a multiple of 128 (got %ld)", N);
     FLH_REQUIRE(a_group == 128 || a_group == K, FLH_B200_EINVAL, "a_group must be 128 or K (got %ld)", a_group);
@@ -222,6 +238,11 @@ int flh_b200_gemm_status(int *out) {
     int rc = gemm_tcgen05_status(out);
     if (rc) return rc;
     return out[0] ? gemm_tcgen05_status_clear() : 0;
+}
+
+int flh_b200_gemm_wait_profile(unsigned long long *out) {
+    FLH_REQUIRE(out, FLH_B200_EINVAL, "null pointer");
+    return gemm_tcgen05_wait_profile(out);
 }
 
 void flhDenseLayerGEMM_i4_o16(const uint8_t *A, const uint8_t *B, const void *A_scale, const void *B_scale,

@@ -31,13 +31,14 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
 }
 
 // Packed binary32 pairs (sm_100): two IEEE adds / fused multiply-adds per instruction.
+// Written as plain integer arithmetic (not an opaque asm mov) so that the compiler can keep the two
+// halves in an aligned register pair without moving them.
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
+    return (static_cast<uint64_t>(__float_as_uint(hi)) << 32) | __float_as_uint(lo);
 }
 __device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    lo = __uint_as_float(static_cast<uint32_t>(v));
+    hi = __uint_as_float(static_cast<uint32_t>(v >> 32));
 }
 __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     uint64_t r;

@@ -2,7 +2,7 @@
 // (mma.sync.m16n8k32 s8), two kernels:
 //   * gemm_tile_kernel    128x128x128 CTA tiles, cp.async ring; any M.  Bring-up cross-check for
 //                         the tcgen05 kernel and the "legacy mma.sync" line of the benchmark.
-//   * gemm_stream_kernel  decode shapes (M <= 32): every CTA streams a 32- or 64-row slab of packed
+//   * gemm_stream_kernel  decode shapes (M <= 64): every CTA streams a 32- or 64-row slab of packed
 //                         weights through an 8-deep cp.async ring; HBM-bound on the weight bytes.
 //
 // Both feed the tensor cores without unpacking to natural order.  A packed 32-bit word holds eight
@@ -210,7 +210,7 @@ gemm_tile_kernel(const GemmParams p) {
 }
 
 // --------------------------------------------------------------------------------------------
-// Streaming kernel for decode (M <= 32): HBM-bound on the packed weight bytes.
+// Streaming kernel for decode (M <= 64): HBM-bound on the packed weight bytes.
 //
 // The weights are the ROW operand of mma.m16n8k32 (16 output channels per warp), the tokens the
 // column operand (8 per mma), so a warp spends 2 shared-memory loads, 24 logic ops and 4 mma per
@@ -224,6 +224,7 @@ constexpr int SSTAGES = 6;
 template <int WARPS, int NT>
 struct StreamPlan {
     static constexpr int BN = 16 * WARPS, TOK = 8 * NT;
+    static constexpr int TS = NT == 1 ? 1 : (NT == 2 ? 2 : 4);   // warps sharing one weight tile, each with NT / TS token tiles
     static constexpr int kB = 0;                              // weights  BN x 128 B
     static constexpr int kA = kB + BN * 128;                  // tokens   TOK x 128 B
     static constexpr int kSB = kA + TOK * 128;                // weight scales  [BN][2] half
@@ -257,12 +258,15 @@ __device__ __forceinline__ void mma_w_by_tok(int32_t (&c)[4], uint32_t a0, uint3
 // sums (int32 without group scales — exact; binary32 chains with them) to scratch, and the last one to
 // arrive (a counter per slab) adds them in split order, finishes the epilogue and re-zeroes the counter.
 template <int WARPS, int NT, bool A_UNSIGNED, bool GROUPED, bool SPLIT>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * StreamPlan<WARPS, NT>::TS * 32)
 gemm_stream_kernel(const GemmParams p) {
     using Plan = StreamPlan<WARPS, NT>;
-    constexpr int BN = Plan::BN, TOK = Plan::TOK, NTHREADS = WARPS * 32;
+    constexpr int BN = Plan::BN, TOK = Plan::TOK, TS = Plan::TS, NTW = NT / TS, NTHREADS = WARPS * TS * 32;
     extern __shared__ __align__(128) uint8_t smem[];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    // warp (wr, wt): 16 weight rows wr, token tiles [wt * NTW, (wt + 1) * NTW) — the warps of a token split
+    // read the same weight tile from shared memory, so more warps hide latency at no extra HBM traffic
+    const int warp = (tid >> 5) % WARPS, wt = (tid >> 5) / WARPS;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * BN;
     const int KB = p.K / 128, KB2 = (KB + 1) / 2;
@@ -328,24 +332,25 @@ gemm_stream_kernel(const GemmParams p) {
         }
     };
 
-    int32_t c[NT][4];
-    float acc[NT][4];
+    int32_t c[NTW][4];
+    float acc[NTW][4];
 #pragma unroll
-    for (int i = 0; i < NT; ++i)
+    for (int i = 0; i < NTW; ++i)
 #pragma unroll
         for (int k = 0; k < 4; ++k) { c[i][k] = 0; acc[i][k] = 0.0f; }
 
     // quantities that do not depend on the K-group
-    float sb_c[2] = {0.f, 0.f}, sa_c[NT][2];
-    int za_c[NT][2];
+    float sb_c[2] = {0.f, 0.f}, sa_c[NTW][2];
+    int za_c[NTW][2];
     const int ch0 = n0 + warp * 16 + g;                  // this thread's channels: ch0, ch0 + 8
 #pragma unroll
-    for (int i = 0; i < NT; ++i)
+    for (int ii = 0; ii < NTW; ++ii)
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
+            const int i = wt * NTW + ii;
             const int tok = min(i * 8 + 2 * t + j, p.M - 1);
-            sa_c[i][j] = p.ga_cols == 1 ? __half2float(p.a_scale[tok]) : 0.f;
-            za_c[i][j] = (has_zero && p.ga_cols == 1) ? (int)__half2float(p.a_zero[tok]) : 0;
+            sa_c[ii][j] = p.ga_cols == 1 ? __half2float(p.a_scale[tok]) : 0.f;
+            za_c[ii][j] = (has_zero && p.ga_cols == 1) ? (int)__half2float(p.a_zero[tok]) : 0;
         }
     if (p.gb_cols == 1) { sb_c[0] = __half2float(p.b_scale[ch0]); sb_c[1] = __half2float(p.b_scale[ch0 + 8]); }
 
@@ -376,17 +381,18 @@ gemm_stream_kernel(const GemmParams p) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) { a0[q] = even16(wl[q]); a1[q] = even16(wh[q]); a2[q] = odd16(wl[q]); a3[q] = odd16(wh[q]); }
 #pragma unroll
-            for (int i = 0; i < NT; ++i) {
+            for (int ii = 0; ii < NTW; ++ii) {
+                const int i = wt * NTW + ii;
                 const int tr = i * 8 + g;
                 const uint4 xv = *reinterpret_cast<const uint4 *>(st + Plan::kA + tr * 128 + ((chunk ^ ((tr & 1) << 2)) << 4));
                 const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
                 int32_t c2[4] = {0, 0, 0, 0};          // second chain: the four mma no longer depend on each other in a row
-                mma_w_by_tok<A_UNSIGNED>(c[i], a0[0], a1[0], a2[0], a3[0], even16(xw[0]), odd16(xw[0]));
+                mma_w_by_tok<A_UNSIGNED>(c[ii], a0[0], a1[0], a2[0], a3[0], even16(xw[0]), odd16(xw[0]));
                 mma_w_by_tok<A_UNSIGNED>(c2, a0[1], a1[1], a2[1], a3[1], even16(xw[1]), odd16(xw[1]));
-                mma_w_by_tok<A_UNSIGNED>(c[i], a0[2], a1[2], a2[2], a3[2], even16(xw[2]), odd16(xw[2]));
+                mma_w_by_tok<A_UNSIGNED>(c[ii], a0[2], a1[2], a2[2], a3[2], even16(xw[2]), odd16(xw[2]));
                 mma_w_by_tok<A_UNSIGNED>(c2, a0[3], a1[3], a2[3], a3[3], even16(xw[3]), odd16(xw[3]));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) c[i][k] += c2[k];
+                for (int k = 0; k < 4; ++k) c[ii][k] += c2[k];
                 if (GROUPED) {
                     // c[i][2h + j]: channel ch0 + 8h, token i*8 + 2t + j.  Scales of this K-group come from the
                     // stage in shared memory; without zero-points the x256 of the accumulator rides in the scale.
@@ -401,17 +407,17 @@ gemm_stream_kernel(const GemmParams p) {
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         const int tk = i * 8 + 2 * t + j;
-                        sav[j] = p.ga_cols == 1 ? sa_c[i][j] : __half2float(reinterpret_cast<const __half *>(st + Plan::kSA)[2 * tk + half]);
-                        if (has_zero) zav[j] = p.ga_cols == 1 ? za_c[i][j] : (int)__half2float(reinterpret_cast<const __half *>(st + Plan::kZA)[2 * tk + half]);
+                        sav[j] = p.ga_cols == 1 ? sa_c[ii][j] : __half2float(reinterpret_cast<const __half *>(st + Plan::kSA)[2 * tk + half]);
+                        if (has_zero) zav[j] = p.ga_cols == 1 ? za_c[ii][j] : (int)__half2float(reinterpret_cast<const __half *>(st + Plan::kZA)[2 * tk + half]);
                         if (!has_zero) sav[j] *= (1.0f / 256.0f);
                     }
 #pragma unroll
                     for (int h = 0; h < 2; ++h)
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
-                            const int32_t I = has_zero ? (c[i][2 * h + j] >> 8) - zav[j] * rsv[h] : c[i][2 * h + j];
-                            acc[i][2 * h + j] = __fmaf_rn((float)I, __fmul_rn(sav[j], sbv[h]), acc[i][2 * h + j]);
-                            c[i][2 * h + j] = 0;
+                            const int32_t I = has_zero ? (c[ii][2 * h + j] >> 8) - zav[j] * rsv[h] : c[ii][2 * h + j];
+                            acc[ii][2 * h + j] = __fmaf_rn((float)I, __fmul_rn(sav[j], sbv[h]), acc[ii][2 * h + j]);
+                            c[ii][2 * h + j] = 0;
                         }
                 }
             }
@@ -424,13 +430,14 @@ gemm_stream_kernel(const GemmParams p) {
         constexpr int TOKP = 8 * NT;
         // raw 32-bit partials: int32 (x256) without group scales, binary32 chains with them
 #pragma unroll
-        for (int i = 0; i < NT; ++i)
+        for (int ii = 0; ii < NTW; ++ii)
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
+                    const int i = wt * NTW + ii;
                     const int tok = i * 8 + 2 * t + j;
-                    const float w = GROUPED ? acc[i][2 * h + j] : __int_as_float(c[i][2 * h + j]);
+                    const float w = GROUPED ? acc[ii][2 * h + j] : __int_as_float(c[ii][2 * h + j]);
                     p.partials[((long)blockIdx.y * TOKP + tok) * p.N + ch0 + 8 * h] = w;
                 }
         __threadfence();
@@ -440,11 +447,12 @@ gemm_stream_kernel(const GemmParams p) {
         if (!s_last) return;
         __threadfence();
 #pragma unroll
-        for (int i = 0; i < NT; ++i)
+        for (int ii = 0; ii < NTW; ++ii)
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
+                    const int i = wt * NTW + ii;
                     const int tok = i * 8 + 2 * t + j;
                     float fsum = 0.0f;
                     int isum = 0;
@@ -453,26 +461,27 @@ gemm_stream_kernel(const GemmParams p) {
                         if (GROUPED) fsum = sp == 0 ? w : __fadd_rn(fsum, w);
                         else isum += __float_as_int(w);
                     }
-                    acc[i][2 * h + j] = fsum;
-                    c[i][2 * h + j] = isum;
+                    acc[ii][2 * h + j] = fsum;
+                    c[ii][2 * h + j] = isum;
                 }
         if (tid == 0) p.counters[blockIdx.x] = 0;       // ready for the next launch
     }
 
 #pragma unroll
-    for (int i = 0; i < NT; ++i)
+    for (int ii = 0; ii < NTW; ++ii)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
+            const int i = wt * NTW + ii;
             const int ch = ch0 + 8 * h;
             const float bias = p.bias ? __half2float(p.bias[ch]) : 0.f;
             const int rs = (!GROUPED && has_zero) ? p.b_rowsum[ch] : 0;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int tok = i * 8 + 2 * t + j;
-                float v = acc[i][2 * h + j];
+                float v = acc[ii][2 * h + j];
                 if (!GROUPED) {
-                    const int32_t I = (c[i][2 * h + j] >> 8) - za_c[i][j] * rs;
-                    v = __fmaf_rn((float)I, __fmul_rn(sa_c[i][j], sb_c[h]), 0.0f);
+                    const int32_t I = (c[ii][2 * h + j] >> 8) - za_c[ii][j] * rs;
+                    v = __fmaf_rn((float)I, __fmul_rn(sa_c[ii][j], sb_c[h]), 0.0f);
                 }
                 if (p.bias) v = __fadd_rn(v, bias);
                 if (tok < p.M) {
@@ -530,7 +539,7 @@ static int launch_stream_t(const GemmParams &p, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_status(e, "gemm_stream attribute");
     dim3 grid((unsigned)(p.N / (16 * WARPS)), (unsigned)(SPLIT ? p.splits : 1));
-    kern<<<grid, WARPS * 32, smem, stream>>>(p);
+    kern<<<grid, WARPS * StreamPlan<WARPS, NT>::TS * 32, smem, stream>>>(p);
     return cuda_status(cudaGetLastError(), "gemm_stream launch");
 }
 
@@ -559,7 +568,7 @@ int stream_splits(long M, long N, long K) {
 }
 size_t stream_scratch_bytes(long M, long N, int splits) {
     if (splits <= 1) return 0;
-    const long tokp = M <= 8 ? 8 : (M <= 16 ? 16 : 32);
+    const long tokp = M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
     return 4096 + (size_t)splits * tokp * N * 4;           // 4 KB of slab counters, then the partial sums
 }
 
@@ -576,7 +585,8 @@ int launch_gemm_stream(const uint8_t *A, const uint8_t *B, const void *a_scale, 
     const bool wide = splits <= 1 && N / 32 > 8 * kNumSMs;
     if (M <= 8) return wide ? launch_stream_w<4, 1>(p, u, stream) : launch_stream_w<2, 1>(p, u, stream);
     if (M <= 16) return wide ? launch_stream_w<4, 2>(p, u, stream) : launch_stream_w<2, 2>(p, u, stream);
-    return wide ? launch_stream_w<4, 4>(p, u, stream) : launch_stream_w<2, 4>(p, u, stream);
+    if (M <= 32) return wide ? launch_stream_w<4, 4>(p, u, stream) : launch_stream_w<2, 4>(p, u, stream);
+    return launch_stream_w<2, 8>(p, u, stream);
 }
 
 // --------------------------------------------------------------------------------------------

@@ -31,6 +31,10 @@ constexpr int BM = 128;
 constexpr int BK = 128;                 // int8 elements per stage = one 128-byte swizzle row
 
 __device__ int g_status[4];             // [0] = first error code, [1] = block, [2] = kb
+// Nanoseconds spent inside bounded waits, summed over CTAs, one representative thread per role:
+// [1] producer on pk_empty, [2] MMA on acc_empty, [3] MMA on ex_full, [4] converter on pk_full,
+// [5] converter on ex_empty, [6]/[7] epilogue on acc_full.  Diagnostic only (flh_b200_gemm_wait_profile).
+__device__ unsigned long long g_wait_ns[8];
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
@@ -54,11 +58,15 @@ __device__ __forceinline__ uint64_t gtimer() {
     return t;
 }
 // Bounded wait: false when two seconds pass or another thread of the CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code,
+                                          unsigned long long *waited = nullptr) {
     if (mbar_try(bar, parity)) return true;
     const uint64_t t0 = gtimer();
     for (int it = 0;; ++it) {
-        if (mbar_try(bar, parity)) return true;
+        if (mbar_try(bar, parity)) {
+            if (waited) *waited += gtimer() - t0;
+            return true;
+        }
         if ((it & 63) == 63) {
             if (*abort_flag) return false;
             if (gtimer() - t0 > 2000000000ull) {
@@ -115,9 +123,18 @@ struct TcParams {
     int num_tiles, m_blocks;
 };
 
-// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (and TMEM owner), warps 2..7 = converters,
-// then one epilogue warpgroup per 128 output columns.
-constexpr int kNonEpiThreads = 256, kConvThreads = 192, kConvTid0 = 64;
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer (and TMEM owner), then the converter warps, then
+// the epilogue warps.  With group scales the epilogue is the heavy role: 6 converter warps and one epilogue
+// warpgroup per 128 output columns (which also receive registers through setmaxnreg).  Without them the
+// converters are: 12 converter warps and a single epilogue warpgroup that walks all columns of a tile while
+// the next tile is already being multiplied.
+constexpr int kConvTid0 = 64;
+template <bool GROUPED> struct Roles {
+    static constexpr int kConvWarps = GROUPED ? 6 : 12;
+    static constexpr int kConvThreads = 32 * kConvWarps;
+    static constexpr int kNonEpi = kConvTid0 + kConvThreads;          // 256 or 448
+    static constexpr int epi_threads(int bn) { return GROUPED ? bn : 128; }
+};
 
 template <int BN>
 struct SmemPlan {
@@ -174,12 +191,14 @@ __device__ __forceinline__ void store_row_chunk(void *D, bool bf16, long off, co
 // per 128x256x128 stage 96 KB cross the shared-memory port instead of 144 KB.  Warp 0 turns into an L2
 // prefetcher that runs a few stages ahead.
 template <int BN, bool GROUPED, bool A_UNSIGNED, bool DIRECT>
-__global__ void __launch_bounds__(kNonEpiThreads + BN, 1)
+__global__ void __launch_bounds__(Roles<GROUPED>::kNonEpi + Roles<GROUPED>::epi_threads(BN), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const TcParams p) {
     using Plan = SmemPlan<BN>;
+    using R = Roles<GROUPED>;
     constexpr int S = Plan::kStages;
     constexpr int kTmemCols = 2 * BN;
+    constexpr int kConvThreads = R::kConvThreads, kNonEpiThreads = R::kNonEpi, kEpiThreads = R::epi_threads(BN);
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -205,7 +224,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(ex_full(s), kConvThreads);
             mbar_init(ex_empty(s), 1);
         }
-        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), BN); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), kEpiThreads); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
@@ -219,9 +238,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp < 8) {
-        if (DIRECT) asm volatile("setmaxnreg.dec.sync.aligned.u32 80;" ::);
-        else asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::);
+    if (tid < kNonEpiThreads) {
+        if (GROUPED) {
+            if (DIRECT) asm volatile("setmaxnreg.dec.sync.aligned.u32 80;" ::);
+            else asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::);
+        }
         if (warp == 0 && DIRECT) {
             // -------------------------------------------------------- L2 prefetcher (direct-load variant)
             constexpr int kAhead = 6;                      // stages ahead of the converters
@@ -248,17 +269,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (lane == 0) {
                 int it = 0;
                 bool ok = true;
+                unsigned long long w1 = 0;
                 for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
                     const int m0 = (tile % p.m_blocks) * BM, n0 = (tile / p.m_blocks) * BN;
                     for (int kb = 0; kb < KB; ++kb, ++it) {
                         const int s = it % S;
-                        if (!mbar_wait(pk_empty(s), ((it / S) & 1) ^ 1, abort_flag, 1)) { ok = false; break; }
+                        if (!mbar_wait(pk_empty(s), ((it / S) & 1) ^ 1, abort_flag, 1, &w1)) { ok = false; break; }
                         mbar_expect_tx(pk_full(s), Plan::kPkStage);
                         const uint32_t dst = base + Plan::kPkOff + s * Plan::kPkStage;
                         tma_load_2d(dst, &map_a, kb * (BK / 2), m0, pk_full(s));
                         tma_load_2d(dst + BM * (BK / 2), &map_b, kb * (BK / 2), n0, pk_full(s));
                     }
                 }
+                atomicAdd(&g_wait_ns[1], w1);
                 if (*abort_flag) {
                     // let the copies already issued land before the CTA leaves
                     for (int j = it > S ? it - S : 0; j < it; ++j) {
@@ -274,14 +297,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                        ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
                 int it = 0, u = 0;
                 bool ok = true;
+                unsigned long long w2 = 0, w3 = 0;
                 for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
                     for (int kb = 0; kb < KB; ++kb, ++it) {
                         const int s = it % S;
                         const int buf = u & 1;
                         if ((GROUPED || kb == 0) && u >= 2) {
-                            if (!mbar_wait(acc_empty(buf), ((u >> 1) & 1) ^ 1, abort_flag, 2)) { ok = false; break; }
+                            if (!mbar_wait(acc_empty(buf), ((u >> 1) & 1) ^ 1, abort_flag, 2, &w2)) { ok = false; break; }
                         }
-                        if (!mbar_wait(ex_full(s), (it / S) & 1, abort_flag, 3)) { ok = false; break; }
+                        if (!mbar_wait(ex_full(s), (it / S) & 1, abort_flag, 3, &w3)) { ok = false; break; }
                         tc_fence_after();
                         const uint32_t a_addr = base + Plan::kExpOff + s * Plan::kExpStage;
                         const uint64_t adesc = make_smem_desc(a_addr), bdesc = make_smem_desc(a_addr + BM * BK);
@@ -294,6 +318,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         if (GROUPED || kb == KB - 1) { tc_commit(acc_full(buf)); ++u; }
                     }
                 }
+                atomicAdd(&g_wait_ns[2], w2);
+                atomicAdd(&g_wait_ns[3], w3);
             }
         } else {
             // -------------------------------------------------------- int4 -> int8 converters
@@ -312,6 +338,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             };
             int it = 0;
             bool ok = true;
+            unsigned long long w4 = 0, w5 = 0;
             if (DIRECT) {
                 constexpr int kPer = (kChunks + kConvThreads - 1) / kConvThreads;   // chunks per thread per stage
                 const long ldk = p.K / 2;
@@ -351,29 +378,43 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             } else {
+                // this thread's chunks are the same in every stage: their offsets are computed once
+                constexpr int kPerT = (kChunks + kConvThreads - 1) / kConvThreads;
+                constexpr int kBatch = GROUPED ? 4 : kPerT;
+                int pk_off[kPerT], ex_off[kPerT];
+#pragma unroll
+                for (int j = 0; j < kPerT; ++j) {
+                    const int ch = ct + j * kConvThreads;
+                    const int row = ch >> 2, c = ch & 3;      // rows of A, then rows of B
+                    pk_off[j] = ch < kChunks ? row * 64 + c * 16 : -1;
+                    ex_off[j] = row * 128 + (((2 * c) ^ (row & 7)) << 4);
+                }
                 for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
                     for (int kb = 0; kb < KB; ++kb, ++it) {
                         const int s = it % S;
-                        if (!mbar_wait(pk_full(s), (it / S) & 1, abort_flag, 4)) { ok = false; break; }
-                        if (!mbar_wait(ex_empty(s), ((it / S) & 1) ^ 1, abort_flag, 5)) { ok = false; break; }
+                        if (!mbar_wait(pk_full(s), (it / S) & 1, abort_flag, 4, &w4)) { ok = false; break; }
+                        if (!mbar_wait(ex_empty(s), ((it / S) & 1) ^ 1, abort_flag, 5, &w5)) { ok = false; break; }
                         const uint8_t *pk = sm + Plan::kPkOff + s * Plan::kPkStage;
                         uint8_t *ex = sm + Plan::kExpOff + s * Plan::kExpStage;
                         // the packed chunks are fetched in batches (independent shared loads in flight) and then
                         // expanded; with group scales the epilogue owns the registers, so the batches are smaller
-                        constexpr int kPerT = (kChunks + kConvThreads - 1) / kConvThreads;
-                        constexpr int kBatch = GROUPED ? 4 : kPerT;
 #pragma unroll
                         for (int j0 = 0; j0 < kPerT; j0 += kBatch) {
                             uint4 wv[kBatch];
 #pragma unroll
-                            for (int j = 0; j < kBatch; ++j) {
-                                const int ch = ct + (j0 + j) * kConvThreads;
-                                if (j0 + j < kPerT && ch < kChunks) wv[j] = *reinterpret_cast<const uint4 *>(pk + (ch >> 2) * 64 + (ch & 3) * 16);
-                            }
+                            for (int j = 0; j < kBatch; ++j)
+                                if (j0 + j < kPerT && pk_off[j0 + j] >= 0) wv[j] = *reinterpret_cast<const uint4 *>(pk + pk_off[j0 + j]);
 #pragma unroll
                             for (int j = 0; j < kBatch; ++j) {
-                                const int ch = ct + (j0 + j) * kConvThreads;
-                                if (j0 + j < kPerT && ch < kChunks) expand_store(ex, ch, wv[j]);
+                                if (j0 + j < kPerT && pk_off[j0 + j] >= 0) {
+                                    const uint4 w = wv[j];
+                                    uint4 e, o;
+                                    e.x = (w.x << 4) & 0xF0F0F0F0u; e.y = (w.y << 4) & 0xF0F0F0F0u;
+                                    e.z = (w.z << 4) & 0xF0F0F0F0u; e.w = (w.w << 4) & 0xF0F0F0F0u;
+                                    o.x = w.x & 0xF0F0F0F0u; o.y = w.y & 0xF0F0F0F0u; o.z = w.z & 0xF0F0F0F0u; o.w = w.w & 0xF0F0F0F0u;
+                                    *reinterpret_cast<uint4 *>(ex + ex_off[j0 + j]) = e;          // 16-byte chunk 2c   ^ (row & 7)
+                                    *reinterpret_cast<uint4 *>(ex + (ex_off[j0 + j] ^ 16)) = o;   // 16-byte chunk 2c+1 ^ (row & 7)
+                                }
                             }
                         }
                         fence_proxy_async();
@@ -382,12 +423,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             }
+            if (ct == 0) { atomicAdd(&g_wait_ns[4], w4); atomicAdd(&g_wait_ns[5], w5); }
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Plan::kEpiRegs(DIRECT)));
-        const int wg = (warp - 8) >> 2;                  // which 128 columns of the tile
-        const int et = tid - kNonEpiThreads - wg * 128;  // 0..127 within the warpgroup
+        if (GROUPED) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Plan::kEpiRegs(DIRECT)));
+        const int wg = (tid - kNonEpiThreads) >> 7;      // warpgroup index: which 128 columns (group scales); 0 otherwise
+        const int et = (tid - kNonEpiThreads) & 127;     // 0..127 within the warpgroup
         const int wq = warp & 3;                         // TMEM lane quarter this warp may read
         float *sbuf = reinterpret_cast<float *>(sm + Plan::kAuxOff);               // [2][BN] weight scales
         int *rbuf = reinterpret_cast<int *>(sm + Plan::kAuxOff + 2 * BN * 4);      // [2][BN] weight row sums
@@ -396,6 +438,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int cbase = wg * 128;                      // first tile column of this warpgroup
         int u = 0;
         bool ok = true;
+        unsigned long long w6 = 0;
 
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
             const int m0 = (tile % p.m_blocks) * BM, n0 = (tile / p.m_blocks) * BN;
@@ -423,7 +466,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (!A_UNSIGNED) sa *= (1.0f / 256.0f);
                     const int za = A_UNSIGNED ? (int)__half2float(p.a_zero[(long)rowc * p.ga_cols + gas * kb]) : 0;
                     const uint64_t sa2 = pack2(sa, sa);
-                    if (!mbar_wait(acc_full(buf), (u >> 1) & 1, abort_flag, 6)) { ok = false; break; }
+                    if (!mbar_wait(acc_full(buf), (u >> 1) & 1, abort_flag, 6, &w6)) { ok = false; break; }
                     tc_fence_after();
                     const float *sb = sbuf + slot * BN + cbase;
                     const int *rs = rbuf + slot * BN + cbase;
@@ -461,37 +504,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             } else {
-                sbuf[cbase + et] = __half2float(p.b_scale[gcol]);
-                rbuf[cbase + et] = A_UNSIGNED ? p.b_rowsum[gcol] : 0;
-                bbuf[cbase + et] = p.bias ? __half2float(p.bias[gcol]) : 0.0f;
-                bar_sync_named(1 + wg, 128);
+                // one warpgroup serves the whole tile: stage scale, row sum and bias of all BN columns
+                for (int c = et; c < BN; c += 128) {
+                    sbuf[c] = __half2float(p.b_scale[n0 + c]);
+                    rbuf[c] = A_UNSIGNED ? p.b_rowsum[n0 + c] : 0;
+                    bbuf[c] = p.bias ? __half2float(p.bias[n0 + c]) : 0.0f;
+                }
+                bar_sync_named(1, 128);
                 const float sa = __half2float(p.a_scale[rowc]) * (1.0f / 256.0f);
                 const int za = A_UNSIGNED ? (int)__half2float(p.a_zero[rowc]) : 0;
                 const int buf = u & 1;
-                if (!mbar_wait(acc_full(buf), (u >> 1) & 1, abort_flag, 7)) { ok = false; break; }
+                if (!mbar_wait(acc_full(buf), (u >> 1) & 1, abort_flag, 7, &w6)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll 1
-                for (int cc = 0; cc < 4; ++cc) {
+                for (int cc = 0; cc < BN / 32; ++cc) {
                     uint32_t v[32];
                     tc_ld32(tlane + buf * BN + cc * 32, v);
                     tc_wait_ld();
                     float o[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int col = cbase + cc * 32 + j;
+                        const int col = cc * 32 + j;
                         const int I = (int)v[j] - ((za * rbuf[col]) << 8);
                         float r = __fmaf_rn((float)I, __fmul_rn(sa, sbuf[col]), 0.0f);
                         if (p.bias) r = __fadd_rn(r, bbuf[col]);
                         o[j] = r;
                     }
-                    if (row < p.M) store_row_chunk(p.D, p.out_bf16, (long)row * p.N + n0 + cbase + cc * 32, o);
+                    if (row < p.M) store_row_chunk(p.D, p.out_bf16, (long)row * p.N + n0 + cc * 32, o);
                 }
                 tc_fence_before();
                 mbar_arrive(acc_empty(buf));
                 ++u;
-                bar_sync_named(1 + wg, 128);             // the staging arrays are rewritten for the next tile
+                bar_sync_named(1, 128);                  // the staging arrays are rewritten for the next tile
             }
         }
+        if (et == 0 && wg == 0) atomicAdd(&g_wait_ns[6], w6);
     }
 
     __syncthreads();
@@ -550,7 +597,7 @@ int launch_t(const CUtensorMap &ma, const CUtensorMap &mb, const TcParams &p, cu
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = kNumSMs;
     }
     const int grid = q.num_tiles < sms ? q.num_tiles : sms;        // one persistent CTA per SM
-    kern<<<grid, kNonEpiThreads + BN, smem, stream>>>(ma, mb, q);
+    kern<<<grid, Roles<GROUPED>::kNonEpi + Roles<GROUPED>::epi_threads(BN), smem, stream>>>(ma, mb, q);
     return cuda_status(cudaGetLastError(), "gemm_tcgen05 launch");
 }
 
@@ -591,6 +638,13 @@ int launch_gemm_tcgen05(const uint8_t *A, const uint8_t *B, const void *a_scale,
 int gemm_tcgen05_status(int *out4) {
     cudaError_t e = cudaMemcpyFromSymbol(out4, g_status, sizeof(int) * 4);
     return cuda_status(e, "status read");
+}
+// Reads and clears the wait-time counters (8 x unsigned long long, nanoseconds summed over CTAs).
+int gemm_tcgen05_wait_profile(unsigned long long *out8) {
+    cudaError_t e = cudaMemcpyFromSymbol(out8, g_wait_ns, sizeof(unsigned long long) * 8);
+    if (e != cudaSuccess) return cuda_status(e, "wait profile read");
+    unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    return cuda_status(cudaMemcpyToSymbol(g_wait_ns, z, sizeof(z)), "wait profile clear");
 }
 int gemm_tcgen05_status_clear() {
     int z[4] = {0, 0, 0, 0};

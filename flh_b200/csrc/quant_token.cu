@@ -91,6 +91,10 @@ struct TokenParams {
     int kfac;
     int P;         // n / kfac
     const uint32_t *sign_bits;
+    long M;                          // rows; CTAs walk rows blockIdx.x, blockIdx.x + gridDim.x, ...
+    const __nv_bfloat16 *sign_mat;   // kp x kp matrix of +-1 (0 in the padding), row-major; tensor-core factor stage
+    int kp;                          // kfac rounded up to a multiple of 16
+    int factor_exact;                // 1: sequential binary32 factor stage on the CUDA cores (bit-exact with the oracle)
     float clip;
     float c;       // sqrtf(n) with the transform, 1 without
     uint8_t *q;
@@ -110,8 +114,23 @@ quant_token_asym_kernel(const TokenParams p) {
 
     const int t = threadIdx.x;
     const int lane = t & 31, warp = t >> 5;
-    const long row = blockIdx.x;
     const bool active = t < p.T;
+
+    // Tensor-core factor stage: the sign matrix lives in shared memory for the whole (persistent) CTA,
+    // rows padded by 16 bytes so that ldmatrix reads are conflict-free.
+    const int smat_ld = p.kp + 8;                                              // bf16 elements per row
+    __nv_bfloat16 *smat = reinterpret_cast<__nv_bfloat16 *>(smem_raw + ((((size_t)p.T * 70 + 64) * 4 + 15) & ~(size_t)15));
+    if (HAD && FACTOR && !p.factor_exact) {
+        const int cpr = p.kp >> 3;                                             // 16-byte chunks per row
+        for (int i = t; i < p.kp * cpr; i += blockDim.x) {
+            const int r = i / cpr, c = i - r * cpr;
+            *reinterpret_cast<uint4 *>(smat + r * smat_ld + c * 8) =
+                *reinterpret_cast<const uint4 *>(p.sign_mat + (size_t)r * p.kp + c * 8);
+        }
+        __syncthreads();
+    }
+
+    for (long row = blockIdx.x; row < p.M; row += gridDim.x) {
     float x[64];
 
     // ---------------- pass 1: load 64 consecutive inputs, bits 0-5 -------------------------
@@ -233,7 +252,7 @@ quant_token_asym_kernel(const TokenParams p) {
     // thread <-> (kb, w): k = 4 kb + v (v < 4); j = 2 w + b + (P/8) u (b < 2, u < 8);
     // register idx = v * 16 + 2 u + b.
     int f_kb = 0, f_w = 0;
-    if (HAD && FACTOR) {
+    if (HAD && FACTOR && p.factor_exact) {
         const int words = (p.kfac + 31) >> 5;
         uint32_t *sgn = reinterpret_cast<uint32_t *>(buf + (p.T * 70 + 64));   // after the data area
         for (int i = t; i < p.kfac * words; i += blockDim.x) sgn[i] = p.sign_bits[i];
@@ -274,6 +293,86 @@ quant_token_asym_kernel(const TokenParams p) {
             }
 #pragma unroll
             for (int i = 0; i < 32; ++i) unpack2(acc[i], x[2 * i], x[2 * i + 1]);
+        }
+    }
+
+    // ---------------- factor stage on the tensor cores ---------------------------------------
+    // y = S x with S the kfac x kfac sign matrix: mma.sync m16n8k16 bf16 -> f32, rows = output chunk k,
+    // contraction = input chunk k', columns = position j inside the chunk.  x is binary32; it is split
+    // EXACTLY into three bfloat16 terms (8 + 8 + 8 significand bits), the products with +-1 are exact and
+    // the sums accumulate in binary32, so the result differs from the sequential sum only by the order of
+    // the binary32 roundings.  A warp owns 8 columns: it reads them for every k', keeps all output rows in
+    // registers (up to 11 tiles x 4), then writes them back in place.
+    if (HAD && FACTOR && !p.factor_exact) {
+        const int MTr = p.kp >> 4;
+        const int ntiles = p.P >> 3, nwarps = blockDim.x >> 5;
+        const int g = lane >> 2, tq = lane & 3;
+        for (int nt = warp; nt < ntiles; nt += nwarps) {
+            float acc[11][4];
+#pragma unroll
+            for (int mt = 0; mt < 11; ++mt)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[mt][q] = 0.0f;
+            const int j = nt * 8 + g;
+            for (int kt = 0; kt < MTr; ++kt) {
+                float v[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int kq = kt * 16 + 2 * tq + (q & 1) + 8 * (q >> 1);
+                    const int i = kq * p.P + j;
+                    v[q] = kq < p.kfac ? buf[phys<B2>(i >> 6, i & 63)] : 0.0f;
+                }
+                uint32_t b[3][2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float lo = v[2 * h], hi = v[2 * h + 1];
+#pragma unroll
+                    for (int sp = 0; sp < 3; ++sp) {
+                        const __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
+                        const uint32_t bits = *reinterpret_cast<const uint32_t *>(&pr);
+                        b[sp][h] = bits;
+                        lo = __fsub_rn(lo, __uint_as_float(bits << 16));
+                        hi = __fsub_rn(hi, __uint_as_float(bits & 0xffff0000u));
+                    }
+                }
+#pragma unroll
+                for (int mt = 0; mt < 11; ++mt) {
+                    if (mt < MTr) {
+                        uint32_t a0, a1, a2, a3;
+                        const uint32_t addr = smem_u32(smat + (mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * smat_ld + kt * 16 + 8 * (lane >> 4));
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(addr));
+#pragma unroll
+                        for (int sp = 0; sp < 3; ++sp)
+                            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                         : "+f"(acc[mt][0]), "+f"(acc[mt][1]), "+f"(acc[mt][2]), "+f"(acc[mt][3])
+                                         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b[sp][0]), "r"(b[sp][1]));
+                    }
+                }
+            }
+            __syncwarp();           // every lane has read its columns before any lane overwrites them
+            const int j0 = nt * 8 + 2 * tq;
+#pragma unroll
+            for (int mt = 0; mt < 11; ++mt) {
+                if (mt < MTr) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int k = mt * 16 + g + 8 * h;
+                        if (k < p.kfac) {
+                            const int i = k * p.P + j0;
+                            *reinterpret_cast<float2 *>(buf + phys<B2>(i >> 6, i & 63)) = make_float2(acc[mt][2 * h], acc[mt][2 * h + 1]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        if (active) {               // back to 64 consecutive values per thread for the quantiser
+#pragma unroll
+            for (int e = 0; e < 64; e += 4) {
+                const float4 f = *reinterpret_cast<const float4 *>(buf + phys<B2>(t, e));
+                x[e] = f.x; x[e + 1] = f.y; x[e + 2] = f.z; x[e + 3] = f.w;
+            }
         }
     }
 
@@ -334,9 +433,11 @@ quant_token_asym_kernel(const TokenParams p) {
             for (int u = 0; u < 2; ++u) {
                 const int id = idx + u;
                 int e;
-                if (HAD && FACTOR) {
+                if (HAD && FACTOR && p.factor_exact) {
                     const int v4 = id >> 4, uu = (id >> 1) & 7, b = id & 1;
                     e = (4 * f_kb + v4) * p.P + 2 * f_w + b + (p.P >> 3) * uu;
+                } else if (HAD && FACTOR) {
+                    e = 64 * t + id;
                 } else if (HAD && B3 > 0) {
                     const int m = id & ((1 << B3) - 1), r = id >> B3;
                     e = ebase + m * 4096 + r * (64 << B3);
@@ -364,15 +465,19 @@ quant_token_asym_kernel(const TokenParams p) {
         }
         qrow[c] = make_uint2(o[0] | (o[1] << 16), o[2] | (o[3] << 16));
     }
+    __syncthreads();            // the staged codes are consumed before the next row reuses the space
+    }                           // row loop
 }
 
 template <int B2, int B3, bool FACTOR, bool HAD>
 int launch_one(const TokenParams &p, long M, cudaStream_t stream) {
-    const int threads = ((p.T + 31) / 32) * 32;
+    int threads = ((p.T + 31) / 32) * 32;
+    if (FACTOR && !p.factor_exact && threads < 256) threads = 256;     // eight warps for the tensor-core factor stage
     size_t smem = (size_t)p.n * 2;                               // staged input row (codes reuse it)
     if (HAD && (B2 > 0 || FACTOR)) {
         smem = ((size_t)p.T * 70 + 64) * 4;
-        if (FACTOR) smem += (size_t)p.kfac * ((p.kfac + 31) / 32) * 4;
+        if (FACTOR && p.factor_exact) smem += (size_t)p.kfac * ((p.kfac + 31) / 32) * 4;
+        if (FACTOR && !p.factor_exact) smem = ((smem + 15) & ~(size_t)15) + (size_t)p.kp * (p.kp + 8) * 2;
         if (smem < (size_t)p.n * 2) smem = (size_t)p.n * 2;
     }
     auto kern = quant_token_asym_kernel<B2, B3, FACTOR, HAD>;
@@ -380,7 +485,15 @@ int launch_one(const TokenParams &p, long M, cudaStream_t stream) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_status(e, "quant_token smem attribute");
     }
-    kern<<<(unsigned)M, threads, smem, stream>>>(p);
+    long grid = M;
+    if (FACTOR && !p.factor_exact) {        // persistent: the sign matrix is staged once per CTA
+        int occ = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, smem) != cudaSuccess || occ < 1) occ = 1;
+        if (grid > (long)occ * kNumSMs) grid = (long)occ * kNumSMs;
+    }
+    TokenParams q = p;
+    q.M = M;
+    kern<<<(unsigned)grid, threads, smem, stream>>>(q);
     return cuda_status(cudaGetLastError(), "quant_token_asym launch");
 }
 
@@ -390,6 +503,15 @@ int launch_quant_token_asym(const void *x, int in_dtype, long M, long K, long ld
                             int kfac, const uint32_t *sign_bits, float clip, uint8_t *q,
                             void *scale, void *zero, cudaStream_t stream) {
     TokenParams p;
+    // factor table layout (flh_b200_pack_signs): bit rows, then (16-byte aligned) the bf16 matrix
+    p.kp = (kfac + 15) / 16 * 16;
+    // the tensor-core factor stage pays off for the large orders (108 ... 172); the small ones (12 ... 60) are
+    // cheaper summed directly, which is also the oracle's order
+    p.factor_exact = hadamard == 2 || kfac < 64;
+    {
+        const size_t bits_bytes = ((size_t)kfac * ((kfac + 31) / 32) * 4 + 15) / 16 * 16;
+        p.sign_mat = reinterpret_cast<const __nv_bfloat16 *>(reinterpret_cast<const uint8_t *>(sign_bits) + bits_bytes);
+    }
     p.x = x; p.ld = ld; p.bf16 = in_dtype == FLH_B200_BF16; p.n = (int)K; p.T = (int)(K / 64);
     p.kfac = kfac; p.P = (int)(K / kfac); p.sign_bits = sign_bits; p.clip = clip;
     p.c = hadamard ? sqrtf((float)K) : 1.0f;

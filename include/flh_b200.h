@@ -43,7 +43,7 @@ extern "C" {
 #define FLH_B200_GEMM_AUTO 0
 #define FLH_B200_GEMM_TCGEN05 1 /* TMA + int4->int8 expand in smem + tcgen05.mma kind::i8, TMEM accumulators */
 #define FLH_B200_GEMM_MMA_SYNC 2 /* legacy mma.sync m16n8k32 s8 path (bring-up cross-check, any M)           */
-#define FLH_B200_GEMM_STREAM 3  /* weight-streaming small-M path (M <= 32)                                    */
+#define FLH_B200_GEMM_STREAM 3  /* weight-streaming small-M path (M <= 64)                                    */
 #define FLH_B200_GEMM_TCGEN05_DIRECT 5 /* tcgen05 path whose converter warps load the packed operands from L2
                                          straight into registers (no TMA staging): less shared-memory traffic */
 #define FLH_B200_GEMM_STREAM_SPLITK 4 /* the same with K cut across CTAs; needs workspace (see below)           */
@@ -75,11 +75,15 @@ int flh_b200_hadamard_f16_inplace(void *x, long rows, int n, void *stream);
 
 /* (Optional full-width Hadamard +) per-token asymmetric int4 quantiser + packing.
  * x [M, K] f16 or bf16 with row stride ld (elements, multiple of 8; x 16-byte aligned).
- * hadamard = 0: quantise x itself.  hadamard = 1: quantise (hadK (x) H_p) x / sqrt(K) with
+ * hadamard = 0: quantise x itself.  hadamard = 1 or 2: quantise (hadK (x) H_p) x / sqrt(K) with
  * K = kfac * p, p a power of two >= 64; kfac = 1 for a power-of-two K, otherwise one of the
- * orders get_hadK knows (flh/functional/hadamard.py:39-89) with sign_bits = that matrix packed
- * by flh_b200_pack_signs (device pointer).  The transform runs in binary32 in the order of
- * matmul_hadU (flh/functional/hadamard.py:92-113); 1/sqrt(K) is folded into the scale.
+ * orders get_hadK knows (flh/functional/hadamard.py:39-89) with sign_bits = the factor table made
+ * by flh_b200_pack_signs (copied to the device, 16-byte aligned).  The butterflies run in binary32
+ * in the order of matmul_hadU (flh/functional/hadamard.py:92-113); 1/sqrt(K) is folded into the
+ * scale.  The kfac x kfac factor is applied on the tensor cores with hadamard = 1 and kfac >= 64 (exact 3-term
+ * bfloat16 split of the binary32 inputs, binary32 accumulation: same value up to the order of the
+ * roundings; the reference's own matmul has no fixed order either) or, with hadamard = 2, summed
+ * k' ascending on the CUDA cores (bit-exact with the CPU oracle, ~10x slower for kfac = 172).
  * Quantiser: ActQuantizer.find_params / asym_quant (fake_quant/quant_utils.py:94-128, 17-21)
  * with the scale rounded to f16 before use.  q [M, K/2] codes 0..15; scale, zero [M] f16.
  * clip = the quantiser's clip_ratio in (0, 1]. */
@@ -87,9 +91,12 @@ int flh_b200_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, lo
                                  int hadamard, int kfac, const uint32_t *sign_bits, float clip,
                                  uint8_t *q, void *scale, void *zero, void *stream);
 
-/* HOST helper: pack a kfac x kfac matrix of +1/-1 (int8, row-major, host memory) into the
- * bit rows the kernel reads: out[k * words + w] bit b = 1 when signs[k][32 w + b] < 0,
- * words = (kfac + 31) / 32.  out holds kfac * words uint32 (host memory). */
+/* HOST helpers: build the factor table of a kfac x kfac matrix of +1/-1 (int8, row-major, host
+ * memory).  Layout: bit rows out[k * words + w], bit b = 1 when signs[k][32 w + b] < 0,
+ * words = (kfac + 31) / 32; then, at the next 16-byte boundary, the same matrix as bfloat16 +-1.0
+ * padded with zeros to kp x kp, kp = kfac rounded up to a multiple of 16.
+ * out: flh_b200_sign_table_bytes(kfac) bytes of host memory. */
+size_t flh_b200_sign_table_bytes(int kfac);
 int flh_b200_pack_signs(const int8_t *signs, int kfac, uint32_t *out);
 
 /* ---- weights ---------------------------------------------------------------------------- */
@@ -137,7 +144,7 @@ size_t flh_b200_gemm_workspace_bytes(long M, long N, long K, long a_group, long 
 /* Which algorithm FLH_B200_GEMM_AUTO resolves to for this shape (one of FLH_B200_GEMM_*). */
 int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group);
 
-/* Decode GEMM (M <= 32) for callers that must not allocate.  Same arguments and results as
+/* Decode GEMM (M <= 64) for callers that must not allocate.  Same arguments and results as
  * flh_b200_gemm_i4_dequant with algo = FLH_B200_GEMM_STREAM_SPLITK, but the split-K scratch is not a
  * caller buffer: it is a 4 KiB + 2 MiB array built into the library's device image, so a serving loop
  * that runs inside a fixed memory budget, a plugin host that owns every cudaMalloc, or code running
@@ -163,6 +170,13 @@ int flh_b200_gemm_i4_dequant_decode_noalloc(const uint8_t *A, const uint8_t *B, 
  * out[1] = the CTA that reported it.  SYNCHRONISES the device; for tests and post-mortems only.
  * out: 4 ints in HOST memory.  No counterpart in FLH. */
 int flh_b200_gemm_status(int *out);
+
+/* Diagnostic: nanoseconds the roles of the tcgen05 GEMM spent waiting on each other since the last call
+ * (summed over CTAs; out[1] TMA producer on a free packed slot, out[2] MMA thread on a free accumulator,
+ * out[3] MMA thread on converted operands, out[4] converters on TMA data, out[5] converters on a free
+ * int8 slot, out[6] epilogue on a finished accumulator).  Reads and clears; SYNCHRONISES the device.
+ * out: 8 x unsigned long long in HOST memory.  No counterpart in FLH. */
+int flh_b200_gemm_wait_profile(unsigned long long *out);
 
 /* The reference's one true C symbol, same signature and meaning
  * (flh/kernels/gemm_and_dequant_i4.cu:471-480): group-128 symmetric scales, f16 output,

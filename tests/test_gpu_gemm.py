@@ -59,7 +59,7 @@ MODES = [  # (a_group, b_group, asym): 0 stands for "whole K"
 
 
 @pytest.mark.parametrize("mode", MODES)
-@pytest.mark.parametrize("m", [1, 8, 16, 17, 32])
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 32, 33, 64])
 def test_stream_kernel(cuda, mode, m):
     run_case(cuda, STREAM, make_case(10 * m, m, 256, 1024, *mode))
 
@@ -70,7 +70,7 @@ def test_stream_kernel_shapes(cuda, m, n, k):
     run_case(cuda, STREAM, make_case(m + n + k + 1, m, n, k, 0, 0, True, bias=True), bf16=True)
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 4096, 11008), (32, 1024, 2048), (7, 256, 4096)])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 4096, 11008), (32, 1024, 2048), (7, 256, 4096), (64, 1024, 8192)])
 def test_stream_splitk(cuda, m, n, k):
     """K cut across CTAs (decode shapes with few output columns).  Without group scales the partial sums
     are int32 and the result equals the oracle bit for bit; with group scales every split keeps its own

@@ -38,7 +38,7 @@ def test_argument_validation_without_a_device():
     assert lib.flh_b200_gemm_i4_dequant(one, one, one, None, one, None, None, one, 4, 100, 256, 128, 128, 0, 0, None, 0, None) == 1
     assert lib.flh_b200_gemm_i4_dequant(one, one, one, one, one, None, None, one, 4, 128, 256, 128, 128, 0, 0, None, 0, None) == 1
     assert b"b_rowsum" in lib.flh_b200_last_error()
-    assert lib.flh_b200_gemm_i4_dequant(one, one, one, None, one, None, None, one, 64, 128, 256, 128, 128, 0, 3, None, 0, None) == 1
+    assert lib.flh_b200_gemm_i4_dequant(one, one, one, None, one, None, None, one, 65, 128, 256, 128, 128, 0, 3, None, 0, None) == 1
     # empty problems succeed without touching the device
     assert lib.flh_b200_quant_group_sym_i4(None, 0, 128, 1, None, None, None) == 0
     assert lib.flh_b200_gemm_i4_dequant(None, None, None, None, None, None, None, None, 0, 128, 256, 128, 128, 0, 0, None, 0, None) == 0

@@ -63,4 +63,4 @@ def test_decode_noalloc_rejects_what_does_not_fit(cuda):
     msg = lib.flh_b200_last_error().decode()
     assert "scratch" in msg and "caller workspace" in msg
     # prefill-sized M is not this entry point's business
-    assert lib.flh_b200_gemm_i4_dequant_decode_noalloc(one, one, one, None, one, None, None, one, 64, 4096, 4096, 128, 128, 0, None) == 1
+    assert lib.flh_b200_gemm_i4_dequant_decode_noalloc(one, one, one, None, one, None, None, one, 65, 4096, 4096, 128, 128, 0, None) == 1
