@@ -340,10 +340,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             unsigned long long w4 = 0, w5 = 0;
             if (DIRECT) {
+                // Register pipeline, kDepth stages deep: slot d holds the packed chunks of stage it + d; a slot is
+                // refilled with stage it + kDepth as soon as it has been expanded, so kDepth - 1 stages of global
+                // loads are always in flight per thread.
                 constexpr int kPer = (kChunks + kConvThreads - 1) / kConvThreads;   // chunks per thread per stage
+                constexpr int kDepth = GROUPED ? 1 : 3;
                 const long ldk = p.K / 2;
-                uint4 w[kPer];
+                uint4 w[kDepth][kPer];
                 const uint8_t *src[kPer];
+                int ex_off[kPer];
+#pragma unroll
+                for (int j = 0; j < kPer; ++j) {
+                    const int ch = ct + j * kConvThreads, row = ch >> 2, c = ch & 3;
+                    ex_off[j] = ch < kChunks ? row * 128 + (((2 * c) ^ (row & 7)) << 4) : -1;
+                }
+                int f_tile = blockIdx.x, f_kb = 0;          // fetch cursor
                 auto set_tile = [&](int tile) {
                     const int m0 = (tile % p.m_blocks) * BM, n0 = (tile / p.m_blocks) * BN;
 #pragma unroll
@@ -355,26 +366,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         else src[j] = p.B + (long)(n0 + row - BM) * ldk + c * 16;
                     }
                 };
-                auto fetch = [&](int kb) {
+                auto fetch_next = [&](uint4 (&dst)[kPer]) {
+                    if (f_tile >= p.num_tiles) return;
 #pragma unroll
                     for (int j = 0; j < kPer; ++j)
-                        w[j] = src[j] ? ldg_nc_v4(src[j] + kb * 64) : make_uint4(0, 0, 0, 0);
+                        dst[j] = src[j] ? ldg_nc_v4(src[j] + f_kb * 64) : make_uint4(0, 0, 0, 0);
+                    if (++f_kb == KB) {
+                        f_kb = 0;
+                        f_tile += gridDim.x;
+                        if (f_tile < p.num_tiles) set_tile(f_tile);
+                    }
                 };
-                int tile = blockIdx.x;
-                if (tile < p.num_tiles) { set_tile(tile); fetch(0); }
-                for (; tile < p.num_tiles && ok; tile += gridDim.x) {
-                    for (int kb = 0; kb < KB; ++kb, ++it) {
+                if (f_tile < p.num_tiles) set_tile(f_tile);
+#pragma unroll
+                for (int d = 0; d < kDepth; ++d) fetch_next(w[d]);
+                int my_tiles = 0;
+                for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) ++my_tiles;
+                const int total = my_tiles * KB;
+                while (it < total && ok) {
+#pragma unroll
+                    for (int d = 0; d < kDepth; ++d) {
+                        if (it >= total || !ok) break;
                         const int s = it % S;
-                        if (!mbar_wait(ex_empty(s), ((it / S) & 1) ^ 1, abort_flag, 5)) { ok = false; break; }
+                        if (!mbar_wait(ex_empty(s), ((it / S) & 1) ^ 1, abort_flag, 5, &w5)) { ok = false; break; }
                         uint8_t *ex = sm + Plan::kExpOff + s * Plan::kExpStage;
 #pragma unroll
-                        for (int j = 0; j < kPer; ++j)
-                            if (ct + j * kConvThreads < kChunks) expand_store(ex, ct + j * kConvThreads, w[j]);
-                        // next stage's operands: issued now, consumed one stage later
-                        if (kb + 1 < KB) fetch(kb + 1);
-                        else if (tile + (int)gridDim.x < p.num_tiles) { set_tile(tile + gridDim.x); fetch(0); }
+                        for (int j = 0; j < kPer; ++j) {
+                            if (ex_off[j] >= 0) {
+                                const uint4 v = w[d][j];
+                                uint4 e, o;
+                                e.x = (v.x << 4) & 0xF0F0F0F0u; e.y = (v.y << 4) & 0xF0F0F0F0u;
+                                e.z = (v.z << 4) & 0xF0F0F0F0u; e.w = (v.w << 4) & 0xF0F0F0F0u;
+                                o.x = v.x & 0xF0F0F0F0u; o.y = v.y & 0xF0F0F0F0u; o.z = v.z & 0xF0F0F0F0u; o.w = v.w & 0xF0F0F0F0u;
+                                *reinterpret_cast<uint4 *>(ex + ex_off[j]) = e;
+                                *reinterpret_cast<uint4 *>(ex + (ex_off[j] ^ 16)) = o;
+                            }
+                        }
+                        fetch_next(w[d]);
                         fence_proxy_async();
                         mbar_arrive(ex_full(s));
+                        ++it;
                     }
                 }
             } else {

@@ -61,6 +61,13 @@ __device__ __forceinline__ int phys(int chunk, int e) {
     return 68 * chunk + e;
 }
 
+// 32-bit words of the transpose buffer of a row of T 64-chunks (see phys): 68 per chunk, plus the extra
+// padding of the small-B2 layouts, plus slack.
+template <int B2>
+__host__ __device__ inline size_t buf_words(int T) {
+    return (size_t)T * (B2 == 1 ? 70 : ((B2 > 1 && B2 < 5) ? 69 : 68)) + 64;
+}
+
 __device__ __forceinline__ float min3(float a, float b, float c) {
     float r;
     asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -103,14 +110,14 @@ struct TokenParams {
 };
 
 // B2/B3: bits handled by passes 2/3.  FACTOR: kfac > 1.  HAD: transform at all.
-// With the transform, K <= 4096 and no factor stage mean at most 64 working threads: ask for ten CTAs per SM.
+// With the transform, K <= 4096 and no factor stage mean at most 64 working threads: ask for ten CTAs per SM (twelve fit only with spills and measured slower).
 template <int B2, int B3, bool FACTOR, bool HAD>
 __global__ void __launch_bounds__((HAD && B3 == 0 && !FACTOR) ? 64 : 512, (HAD && B3 == 0 && !FACTOR) ? 10 : 1)
 quant_token_asym_kernel(const TokenParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     float *buf = reinterpret_cast<float *>(smem_raw);
     __shared__ float red[2][32];
-    __shared__ float bcast[2];
+    __shared__ float bcast[3];
 
     const int t = threadIdx.x;
     const int lane = t & 31, warp = t >> 5;
@@ -119,7 +126,7 @@ quant_token_asym_kernel(const TokenParams p) {
     // Tensor-core factor stage: the sign matrix lives in shared memory for the whole (persistent) CTA,
     // rows padded by 16 bytes so that ldmatrix reads are conflict-free.
     const int smat_ld = p.kp + 8;                                              // bf16 elements per row
-    __nv_bfloat16 *smat = reinterpret_cast<__nv_bfloat16 *>(smem_raw + ((((size_t)p.T * 70 + 64) * 4 + 15) & ~(size_t)15));
+    __nv_bfloat16 *smat = reinterpret_cast<__nv_bfloat16 *>(smem_raw + ((buf_words<B2>(p.T) * 4 + 15) & ~(size_t)15));
     if (HAD && FACTOR && !p.factor_exact) {
         const int cpr = p.kp >> 3;                                             // 16-byte chunks per row
         for (int i = t; i < p.kp * cpr; i += blockDim.x) {
@@ -138,11 +145,13 @@ quant_token_asym_kernel(const TokenParams p) {
     // lands at chunk c ^ (L & 7), so that a thread reading its own line is conflict-free), then every
     // thread picks up its 64 consecutive values.
     {
-        const uint16_t *xrow = static_cast<const uint16_t *>(p.x) + row * p.ld;
-        for (int ch = t; ch < (p.n >> 3); ch += blockDim.x) {
-            const int line = ch >> 3, c = ch & 7;
-            const uint32_t dst = smem_u32(smem_raw + ((line << 3) + (c ^ (line & 7))) * 16);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(xrow + ch * 8));
+        const uint16_t *src = static_cast<const uint16_t *>(p.x) + row * p.ld + t * 8;
+        const uint32_t sbase = smem_u32(smem_raw);
+        const int c = t & 7, dl = blockDim.x >> 3, nch = p.n >> 3;
+        int line = t >> 3;
+        for (int ch = t; ch < nch; ch += blockDim.x, line += dl, src += blockDim.x * 8) {
+            const uint32_t dst = sbase + (((line << 3) + (c ^ (line & 7))) << 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
         }
         asm volatile("cp.async.commit_group;" ::);
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -254,7 +263,7 @@ quant_token_asym_kernel(const TokenParams p) {
     int f_kb = 0, f_w = 0;
     if (HAD && FACTOR && p.factor_exact) {
         const int words = (p.kfac + 31) >> 5;
-        uint32_t *sgn = reinterpret_cast<uint32_t *>(buf + (p.T * 70 + 64));   // after the data area
+        uint32_t *sgn = reinterpret_cast<uint32_t *>(buf + buf_words<B2>(p.T));   // after the data area
         for (int i = t; i < p.kfac * words; i += blockDim.x) sgn[i] = p.sign_bits[i];
         __syncthreads();
         const int Wd = p.P >> 4;
@@ -402,11 +411,16 @@ quant_token_asym_kernel(const TokenParams p) {
             const float rd0 = __frcp_rn(d);
             const float zf0 = rintf(__fmul_rn(-zmin, rd0));
             bcast[0] = rd0; bcast[1] = zf0;
+            // Does any code need clamping?  Without clipping every element lies in [a, b], the product with rd
+            // and rint are monotonic, so the codes lie in [rint(a rd) + zero, rint(b rd) + zero].
+            const bool in_range = p.clip == 1.0f && rintf(__fmul_rn(b, rd0)) + zf0 <= 15.0f && rintf(__fmul_rn(a, rd0)) + zf0 >= 0.0f;
+            bcast[2] = in_range ? 0.0f : 1.0f;
             p.scale[row] = sh; p.zero[row] = __float2half_rn(zf0);
         }
     }
     __syncthreads();
     const float rd = bcast[0], zf = bcast[1];
+    const bool clamp_codes = bcast[2] != 0.0f;
 
     // codes: clamp(rint(z * rd), -zero, 15 - zero) + zero; adding 1.5 * 2^23 rounds to the
     // nearest integer (ties to even) and leaves it in the low mantissa bits.
@@ -416,15 +430,13 @@ quant_token_asym_kernel(const TokenParams p) {
         const float magic = 12582912.0f;
         const int zi = (int)zf;
         const uint64_t rd2 = pack2(rd, rd), magic2 = pack2(magic, magic);
-        // Without clipping no element lies below the row minimum, and rint(z * rd) >= -zero follows
-        // from the monotonicity of the product and of rint: only the upper clamp can ever act.
-        const bool need_lo = p.clip != 1.0f;
+        // The row leader has checked whether any code of this row can leave 0..15 (it cannot, for almost
+        // every row, when nothing is clipped); only then are the values clamped before rounding.
 #pragma unroll
         for (int idx = 0; idx < 64; idx += 2) {
             float v0, v1;
             unpack2(mul2(pack2(x[idx], x[idx + 1]), rd2), v0, v1);
-            v0 = fminf(v0, hi); v1 = fminf(v1, hi);
-            if (need_lo) { v0 = fmaxf(v0, lo); v1 = fmaxf(v1, lo); }
+            if (clamp_codes) { v0 = fmaxf(fminf(v0, hi), lo); v1 = fmaxf(fminf(v1, hi), lo); }
             float r0, r1;
             unpack2(add2(pack2(v0, v1), magic2), r0, r1);
             // low byte of (bits + zero) = rint(v) + zero, already in 0..15
@@ -475,7 +487,7 @@ int launch_one(const TokenParams &p, long M, cudaStream_t stream) {
     if (FACTOR && !p.factor_exact && threads < 256) threads = 256;     // eight warps for the tensor-core factor stage
     size_t smem = (size_t)p.n * 2;                               // staged input row (codes reuse it)
     if (HAD && (B2 > 0 || FACTOR)) {
-        smem = ((size_t)p.T * 70 + 64) * 4;
+        smem = buf_words<B2>(p.T) * 4;
         if (FACTOR && p.factor_exact) smem += (size_t)p.kfac * ((p.kfac + 31) / 32) * 4;
         if (FACTOR && !p.factor_exact) smem = ((smem + 15) & ~(size_t)15) + (size_t)p.kp * (p.kp + 8) * 2;
         if (smem < (size_t)p.n * 2) smem = (size_t)p.n * 2;
