@@ -13,7 +13,8 @@
 // All butterflies run on packed binary32 pairs (add.rn.f32x2 / fma.rn.f32x2), so every result is
 // the IEEE sum or difference of its two inputs, in ascending bit order: bit-exact with the oracle.
 // Shared memory is used only for the transposes between register passes.
-#include "common.cuh"
+#include "token_common.cuh"
+#include <stdlib.h>
 
 namespace flh {
 namespace {
@@ -66,27 +67,6 @@ __device__ __forceinline__ int phys(int chunk, int e) {
 template <int B2>
 __host__ __device__ inline size_t buf_words(int T) {
     return (size_t)T * (B2 == 1 ? 70 : ((B2 > 1 && B2 < 5) ? 69 : 68)) + 64;
-}
-
-__device__ __forceinline__ float min3(float a, float b, float c) {
-    float r;
-    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-    return r;
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float r;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-    return r;
-}
-__device__ __forceinline__ float warp_min(float v) {
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, s));
-    return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
-    return v;
 }
 
 struct TokenParams {
@@ -401,21 +381,9 @@ quant_token_asym_kernel(const TokenParams p) {
         float b = lane < nw ? red[1][lane] : 0.0f;
         a = warp_min(a); b = warp_max(b);
         if (lane == 0) {
-            float zmin = __fmul_rn(a, p.clip), zmax = __fmul_rn(b, p.clip);
-            if (zmin == 0.0f && zmax == 0.0f) { zmin = -1.0f; zmax = 1.0f; }
-            float scale32 = __fdiv_rn(__fsub_rn(zmax, zmin), 15.0f);
-            scale32 = __fdiv_rn(scale32, p.c);
-            __half sh = __float2half_rn(scale32);
-            if ((__half_as_ushort(sh) & 0x7fffu) == 0) sh = __ushort_as_half(0x0001u);
-            const float d = __fmul_rn(p.c, __half2float(sh));
-            const float rd0 = __frcp_rn(d);
-            const float zf0 = rintf(__fmul_rn(-zmin, rd0));
-            bcast[0] = rd0; bcast[1] = zf0;
-            // Does any code need clamping?  Without clipping every element lies in [a, b], the product with rd
-            // and rint are monotonic, so the codes lie in [rint(a rd) + zero, rint(b rd) + zero].
-            const bool in_range = p.clip == 1.0f && rintf(__fmul_rn(b, rd0)) + zf0 <= 15.0f && rintf(__fmul_rn(a, rd0)) + zf0 >= 0.0f;
-            bcast[2] = in_range ? 0.0f : 1.0f;
-            p.scale[row] = sh; p.zero[row] = __float2half_rn(zf0);
+            const TokenRowParams rp = token_row_params(a, b, p.clip, p.c);
+            bcast[0] = rp.rd; bcast[1] = rp.zero; bcast[2] = rp.clamp ? 1.0f : 0.0f;
+            p.scale[row] = rp.scale; p.zero[row] = __float2half_rn(rp.zero);
         }
     }
     __syncthreads();
@@ -511,9 +479,26 @@ int launch_one(const TokenParams &p, long M, cudaStream_t stream) {
 
 }  // namespace
 
+int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld, float clip, uint8_t *q,
+                            void *scale, void *zero, cudaStream_t stream);
+
+// Rows from which the warp-per-row kernel (K = 4096) is used; below it the 64-thread kernel spreads a
+// small batch over more SMs.  FLH_B200_TOKEN_WARP_MIN_M overrides it (tuning aid).
+static long token_warp_min_rows() {
+    static long v = -1;
+    if (v < 0) {
+        const char *e = getenv("FLH_B200_TOKEN_WARP_MIN_M");
+        v = e ? atol(e) : 1024;
+        if (v < 0) v = 0;
+    }
+    return v;
+}
+
 int launch_quant_token_asym(const void *x, int in_dtype, long M, long K, long ld, int hadamard,
                             int kfac, const uint32_t *sign_bits, float clip, uint8_t *q,
                             void *scale, void *zero, cudaStream_t stream) {
+    if (hadamard && kfac == 1 && K == 4096 && M >= token_warp_min_rows())
+        return launch_quant_token_warp(x, in_dtype, M, K, ld, clip, q, scale, zero, stream);
     TokenParams p;
     // factor table layout (flh_b200_pack_signs): bit rows, then (16-byte aligned) the bf16 matrix
     p.kp = (kfac + 15) / 16 * 16;

@@ -1,0 +1,214 @@
+// Per-token quantiser for K = 4096 with one WARP per token row (full-width binary32 Hadamard in
+// matmul_hadU's order + asymmetric int4 + nibble packing), the shape of a Llama-7B hidden state.
+//
+// Every lane owns 128 values in registers, as 64 packed binary32 pairs:
+//   pass 1  the row is staged in shared memory by coalesced 16-byte cp.async (the NEXT row of the
+//           persistent warp is already in flight while this one is computed); a lane picks up 128
+//           consecutive inputs and runs butterfly bits 0-6;
+//   pass 2  one transpose through padded shared memory, 128-bit accesses on both sides: a lane then
+//           owns elements m * 128 + 4 lane + i (m < 32, i < 4) and runs bits 7-11 over m, the two
+//           halves of a packed pair being neighbouring elements;
+//   quant   warp min/max by shuffles, scale and zero-point computed redundantly by every lane, four
+//           neighbouring codes packed into 16 bits with shift-adds and stored directly.
+// No block-level barrier, no byte staging of the codes.  Each butterfly is the IEEE sum or difference of
+// its two inputs in ascending bit order, so the result is bit-identical to the 64-thread kernel and to the
+// CPU restatement.
+#include "token_common.cuh"
+
+namespace flh {
+namespace {
+
+constexpr int kRowK = 4096;
+constexpr int kStageBytes = kRowK * 2;                 // one staged row of 16-bit inputs
+constexpr int kChunkWords = 132;                        // 128 values of a lane + 4 words of padding
+constexpr int kXposeBytes = 32 * kChunkWords * 4;
+constexpr int kWarpBytes = kStageBytes + kXposeBytes;   // 25,088 bytes per warp
+constexpr int kWarpsPerCta = 4;
+
+struct WarpParams {
+    const uint8_t *x;      // rows of 4096 16-bit values
+    long ld_bytes;
+    long M;
+    float clip;
+    uint8_t *q;
+    __half *scale;
+    __half *zero;
+};
+
+// butterflies over the pair index k (0..63): partner k ^ h for h = H0, 2 H0, ... < 64
+template <int H0>
+__device__ __forceinline__ void bfly_pairs(uint64_t (&p)[64]) {
+#pragma unroll
+    for (int h = H0; h < 64; h <<= 1) {
+#pragma unroll
+        for (int k = 0; k < 64; ++k) {
+            if ((k & h) == 0) {
+                const uint64_t a = p[k], b = p[k + h];
+                p[k] = add2(a, b);
+                p[k + h] = sub2(a, b);
+            }
+        }
+    }
+}
+
+// issue the sixteen 16-byte copies of this lane for one row; chunk c of 128-byte line L lands at
+// chunk c ^ ((L >> 1) & 7) of that line, which makes the reads of pass 1 conflict-free
+__device__ __forceinline__ void stage_row(const WarpParams &p, long row, uint32_t stage, int lane) {
+    const uint8_t *src = p.x + row * p.ld_bytes + lane * 16;
+    const int c0 = (lane & 7) ^ (lane >> 4);
+    const uint32_t base = stage + ((lane >> 3) << 7);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t dst = base + i * 512 + ((c0 ^ ((2 * i) & 7)) << 4);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + i * 512));
+    }
+    asm volatile("cp.async.commit_group;" ::);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 2) quant_token_warp_kernel(const WarpParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint8_t *my = smem_raw + warp * kWarpBytes;
+    const uint32_t stage = smem_u32(my);
+    float *xp = reinterpret_cast<float *>(my + kStageBytes);
+
+    const long nwarps = (long)gridDim.x * kWarpsPerCta;
+    long row = (long)blockIdx.x * kWarpsPerCta + warp;
+    if (row < p.M) stage_row(p, row, stage, lane);
+
+    for (; row < p.M; row += nwarps) {
+        uint64_t v[64];
+
+        // ---------------- pass 1: 128 consecutive inputs, bits 0-6 --------------------------------
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        {
+            const uint8_t *mine = my + lane * 256;
+            const int tx = lane & 7;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 w4 = *reinterpret_cast<const uint4 *>(mine + j * 128 + ((c ^ tx) << 4));
+                    const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        float a, b;
+                        if (BF16) {
+                            a = __uint_as_float(w[k] << 16);
+                            b = __uint_as_float(w[k] & 0xffff0000u);
+                        } else {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+                            a = f.x; b = f.y;
+                        }
+                        v[j * 32 + c * 4 + k] = pack2(__fadd_rn(a, b), __fsub_rn(a, b));      // bit 0
+                    }
+                }
+            }
+        }
+        __syncwarp();                                   // the staged row is in registers everywhere
+        if (row + nwarps < p.M) stage_row(p, row + nwarps, stage, lane);
+        bfly_pairs<1>(v);                               // bits 1-6
+
+        // ---------------- transpose: lane's chunk out, 4-wide columns in --------------------------
+        {
+            float *out = xp + lane * kChunkWords;
+#pragma unroll
+            for (int k = 0; k < 64; k += 2) {
+                float a, b, c, d;
+                unpack2(v[k], a, b);
+                unpack2(v[k + 1], c, d);
+                *reinterpret_cast<float4 *>(out + 2 * k) = make_float4(a, b, c, d);
+            }
+        }
+        __syncwarp();
+        // pair index k = 2 m + h: elements m * 128 + 4 lane + 2 h + {0, 1}
+#pragma unroll
+        for (int m = 0; m < 32; ++m) {
+            const float4 f = *reinterpret_cast<const float4 *>(xp + m * kChunkWords + lane * 4);
+            v[2 * m] = pack2(f.x, f.y);
+            v[2 * m + 1] = pack2(f.z, f.w);
+        }
+        bfly_pairs<2>(v);                               // bits 7-11 (over m)
+
+        // ---------------- row min / max, parameters ------------------------------------------------
+        float vmin = 0.0f, vmax = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 64; ++k) {
+            float a, b;
+            unpack2(v[k], a, b);
+            vmin = min3(vmin, a, b);
+            vmax = max3(vmax, a, b);
+        }
+        vmin = warp_min(vmin);
+        vmax = warp_max(vmax);
+        const TokenRowParams rp = token_row_params(vmin, vmax, p.clip, 64.0f);     // sqrt(4096)
+        if (lane == 0) { p.scale[row] = rp.scale; p.zero[row] = __float2half_rn(rp.zero); }
+
+        // ---------------- codes --------------------------------------------------------------------
+        // v * rd, (clamped only when the row needs it), + 1.5 * 2^23 leaves rint(v rd) = code - zero in
+        // the low mantissa bits.  With b_i the four bit patterns of one m, the low 16 bits of
+        // b0 + 16 b1 + 256 b2 + 4096 b3 + 0x1111 zero are the four packed codes: the constant upper
+        // part of the patterns is a multiple of 2^16, and the sum of the true codes fits 16 bits.
+        const uint64_t rd2 = pack2(rp.rd, rp.rd);
+#pragma unroll
+        for (int k = 0; k < 64; ++k) v[k] = mul2(v[k], rd2);
+        if (rp.clamp) {
+            const float lo = -rp.zero, hi = 15.0f - rp.zero;
+#pragma unroll
+            for (int k = 0; k < 64; ++k) {
+                float a, b;
+                unpack2(v[k], a, b);
+                v[k] = pack2(fmaxf(fminf(a, hi), lo), fmaxf(fminf(b, hi), lo));
+            }
+        }
+        const uint64_t magic2 = pack2(12582912.0f, 12582912.0f);
+        const uint32_t zsum = 0x1111u * (uint32_t)(int)rp.zero;
+        uint16_t *qrow = reinterpret_cast<uint16_t *>(p.q + row * (long)(kRowK / 2)) + lane;
+#pragma unroll
+        for (int m = 0; m < 32; ++m) {
+            float r0, r1, r2, r3;
+            unpack2(add2(v[2 * m], magic2), r0, r1);
+            unpack2(add2(v[2 * m + 1], magic2), r2, r3);
+            const uint32_t lo8 = (__float_as_uint(r1) << 4) + __float_as_uint(r0);
+            const uint32_t hi8 = (__float_as_uint(r3) << 4) + __float_as_uint(r2);
+            const uint32_t w = (hi8 << 8) + lo8 + zsum;
+            qrow[m * 32] = (uint16_t)w;
+        }
+    }
+}
+
+}  // namespace
+
+// K = 4096 with the transform and no factor stage.  Returns -1000 when the shape is not one this kernel
+// takes (the caller then uses the general kernel).
+int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld, float clip, uint8_t *q,
+                            void *scale, void *zero, cudaStream_t stream) {
+    if (K != kRowK) return -1000;
+    WarpParams p;
+    p.x = static_cast<const uint8_t *>(x);
+    p.ld_bytes = ld * 2;
+    p.M = M;
+    p.clip = clip;
+    p.q = q;
+    p.scale = static_cast<__half *>(scale);
+    p.zero = static_cast<__half *>(zero);
+    const size_t smem = (size_t)kWarpsPerCta * kWarpBytes;
+    auto kern = in_dtype == FLH_B200_BF16 ? quant_token_warp_kernel<true> : quant_token_warp_kernel<false>;
+    static bool attr_done[2][64] = {};
+    const int which = in_dtype == FLH_B200_BF16;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+    if (dev < 0 || !attr_done[which][dev]) {         // the attribute is per device
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_status(e, "quant_token_warp smem attribute");
+        if (dev >= 0) attr_done[which][dev] = true;
+    }
+    long grid = (M + kWarpsPerCta - 1) / kWarpsPerCta;
+    if (grid > 2L * kNumSMs) grid = 2L * kNumSMs;
+    kern<<<(unsigned)grid, kWarpsPerCta * 32, smem, stream>>>(p);
+    return cuda_status(cudaGetLastError(), "quant_token_warp launch");
+}
+
+}  // namespace flh

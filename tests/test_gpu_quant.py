@@ -136,6 +136,35 @@ def test_token_asym_bf16_strided_and_edges(cuda):
     assert np.array_equal(q.cpu().numpy(), qo)
 
 
+@pytest.mark.parametrize("m", [1024, 1189, 4100])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_token_asym_k4096_large_batches(cuda, m, bf16):
+    """K = 4096 with many rows runs the one-warp-per-row kernel (persistent warps, next row prefetched): every row
+    bit-equal to the oracle, with edge rows, a padded row stride, and a clip ratio that forces clamping."""
+    k = 4096
+    xf = activations(3700 + m, m, k).astype(np.float32)
+    xf[1] = 0.0
+    xf[2] = np.abs(xf[2])
+    xf[m - 1] = -np.abs(xf[m - 1])
+    xf[m // 2, 7] = 3000.0           # one large outlier
+    if bf16:
+        bits = O.f32_to_bf16_bits(xf)
+        wide = torch.zeros((m, k + 8), dtype=torch.bfloat16, device="cuda")
+        wide[:, :k] = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+        xin, xo = wide[:, :k], bits
+    else:
+        xo = xf.astype(np.float16)
+        wide = torch.zeros((m, k + 64), dtype=torch.float16, device="cuda")
+        wide[:, :k] = torch.from_numpy(xo).cuda()
+        xin = wide[:, :k]
+    for clip in (1.0, 0.9):
+        q, s, z = cuda.quant_token_asym_i4(xin, hadamard=True, clip=clip)
+        qo, so, zo = O.quant_token_asym(xo, True, clip=clip, bf16=bf16)
+        assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16))
+        assert np.array_equal(z.cpu().numpy().view(np.uint16), zo.view(np.uint16))
+        assert np.array_equal(q.cpu().numpy(), qo)
+
+
 def test_token_asym_full_size_property(cuda):
     # BASELINE sweep M=4096, K=4096: sampled rows against the oracle + a checksum of all codes
     x = activations(88, 4096, 4096)

@@ -55,11 +55,20 @@ def test_pack_signs_host_helper():
     s, k = get_hadK(11008)
     assert k == 172
     words = (k + 31) // 32
-    out = np.zeros((k, words), dtype=np.uint32)
-    assert _lib.load().flh_b200_pack_signs(np.ascontiguousarray(s).ctypes.data_as(ctypes.c_void_p), k,
-                                           out.ctypes.data_as(ctypes.c_void_p)) == 0
+    lib = _lib.load()
+    nbytes = lib.flh_b200_sign_table_bytes(k)        # bit rows, then the bf16 matrix padded to a multiple of 16
+    kp = (k + 15) // 16 * 16
+    bits_bytes = (k * words * 4 + 15) // 16 * 16
+    assert nbytes == bits_bytes + kp * kp * 2
+    buf = np.zeros(nbytes // 4, dtype=np.uint32)
+    assert lib.flh_b200_pack_signs(np.ascontiguousarray(s).ctypes.data_as(ctypes.c_void_p), k,
+                                   buf.ctypes.data_as(ctypes.c_void_p)) == 0
+    out = buf[:k * words].reshape(k, words)
     bits = ((out[:, :, None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(k, -1)[:, :k]
     assert np.array_equal(bits == 1, s < 0)
+    mat = buf.view(np.uint16)[bits_bytes // 2:].reshape(kp, kp)
+    assert np.array_equal(mat[:k, :k], np.where(s < 0, 0xBF80, 0x3F80).astype(np.uint16))
+    assert not mat[k:].any() and not mat[:, k:].any()
 
 
 def test_get_hadK_precedence():
