@@ -488,7 +488,7 @@ static long token_warp_min_rows() {
     static long v = -1;
     if (v < 0) {
         const char *e = getenv("FLH_B200_TOKEN_WARP_MIN_M");
-        v = e ? atol(e) : 1024;
+        v = e ? atol(e) : 512;
         if (v < 0) v = 0;
     }
     return v;

@@ -3,8 +3,8 @@
 //
 // Every lane owns 128 values in registers, as 64 packed binary32 pairs:
 //   pass 1  the row is staged in shared memory by coalesced 16-byte cp.async (the NEXT row of the
-//           persistent warp is already in flight while this one is computed); a lane picks up 128
-//           consecutive inputs and runs butterfly bits 0-6;
+//           persistent warp is prefetched into L2 at once and copied while the second half of this
+//           row is computed); a lane picks up 128 consecutive inputs and runs butterfly bits 0-6;
 //   pass 2  one transpose through padded shared memory, 128-bit accesses on both sides: a lane then
 //           owns elements m * 128 + 4 lane + i (m < 32, i < 4) and runs bits 7-11 over m, the two
 //           halves of a packed pair being neighbouring elements;
@@ -19,11 +19,12 @@ namespace flh {
 namespace {
 
 constexpr int kRowK = 4096;
-constexpr int kStageBytes = kRowK * 2;                 // one staged row of 16-bit inputs
+static_assert(kRowK * 2 <= 32 * 132 * 4, "the staged row must fit the transpose buffer");
 constexpr int kChunkWords = 132;                        // 128 values of a lane + 4 words of padding
 constexpr int kXposeBytes = 32 * kChunkWords * 4;
-constexpr int kWarpBytes = kStageBytes + kXposeBytes;   // 25,088 bytes per warp
+constexpr int kWarpBytes = kXposeBytes;                 // 16,896 bytes per warp: the staged row aliases the transpose buffer
 constexpr int kWarpsPerCta = 4;
+constexpr int kCtasPerSm = 3;                           // 12 warps per SM: 168 registers, 66 KB per CTA
 
 struct WarpParams {
     const uint8_t *x;      // rows of 4096 16-bit values
@@ -66,12 +67,12 @@ __device__ __forceinline__ void stage_row(const WarpParams &p, long row, uint32_
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, 2) quant_token_warp_kernel(const WarpParams p) {
+__global__ void __launch_bounds__(kWarpsPerCta * 32, kCtasPerSm) quant_token_warp_kernel(const WarpParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint8_t *my = smem_raw + warp * kWarpBytes;
     const uint32_t stage = smem_u32(my);
-    float *xp = reinterpret_cast<float *>(my + kStageBytes);
+    const uint32_t xp = stage;                              // transpose buffer (aliases the staged row)
 
     const long nwarps = (long)gridDim.x * kWarpsPerCta;
     long row = (long)blockIdx.x * kWarpsPerCta + warp;
@@ -94,42 +95,53 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 2) quant_token_warp_kernel(
                     const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        float a, b;
+                        float sum, dif;
                         if (BF16) {
-                            a = __uint_as_float(w[k] << 16);
-                            b = __uint_as_float(w[k] & 0xffff0000u);
+                            const float a = __uint_as_float(w[k] << 16);
+                            const float b = __uint_as_float(w[k] & 0xffff0000u);
+                            sum = __fadd_rn(a, b);
+                            dif = __fsub_rn(a, b);
                         } else {
-                            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
-                            a = f.x; b = f.y;
+                            // bit 0 straight from the binary16 pair: a + b and fma(b, -1, a) with b widened inside the
+                            // instruction are the same IEEE binary32 sum and difference as after two conversions
+                            uint16_t ha, hb;
+                            asm("mov.b32 {%0, %1}, %2;" : "=h"(ha), "=h"(hb) : "r"(w[k]));
+                            const float a = __half2float(__ushort_as_half(ha));
+                            const uint16_t neg1 = 0xBC00u;
+                            asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(sum) : "h"(hb), "f"(a));
+                            asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(dif) : "h"(hb), "h"(neg1), "f"(a));
                         }
-                        v[j * 32 + c * 4 + k] = pack2(__fadd_rn(a, b), __fsub_rn(a, b));      // bit 0
+                        v[j * 32 + c * 4 + k] = pack2(sum, dif);
                     }
                 }
             }
         }
         __syncwarp();                                   // the staged row is in registers everywhere
-        if (row + nwarps < p.M) stage_row(p, row + nwarps, stage, lane);
+        const bool more = row + nwarps < p.M;
+        if (more) {                                     // next row: towards L2 now, into shared memory below
+            const uint8_t *nx = p.x + (row + nwarps) * p.ld_bytes + lane * 128;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(nx));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + 4096));
+        }
         bfly_pairs<1>(v);                               // bits 1-6
 
         // ---------------- transpose: lane's chunk out, 4-wide columns in --------------------------
         {
-            float *out = xp + lane * kChunkWords;
+            const uint32_t out = xp + lane * (kChunkWords * 4);
 #pragma unroll
-            for (int k = 0; k < 64; k += 2) {
-                float a, b, c, d;
-                unpack2(v[k], a, b);
-                unpack2(v[k + 1], c, d);
-                *reinterpret_cast<float4 *>(out + 2 * k) = make_float4(a, b, c, d);
-            }
+            for (int k = 0; k < 64; k += 2)
+                asm volatile("st.shared.v2.u64 [%0], {%1, %2};" ::"r"(out + 8 * k), "l"(v[k]), "l"(v[k + 1]) : "memory");
         }
         __syncwarp();
         // pair index k = 2 m + h: elements m * 128 + 4 lane + 2 h + {0, 1}
+        {
+            const uint32_t in = xp + lane * 16;
 #pragma unroll
-        for (int m = 0; m < 32; ++m) {
-            const float4 f = *reinterpret_cast<const float4 *>(xp + m * kChunkWords + lane * 4);
-            v[2 * m] = pack2(f.x, f.y);
-            v[2 * m + 1] = pack2(f.z, f.w);
+            for (int m = 0; m < 32; ++m)
+                asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v[2 * m]), "=l"(v[2 * m + 1]) : "r"(in + m * (kChunkWords * 4)) : "memory");
         }
+        __syncwarp();                                   // the buffer is free again: stage the next row into it
+        if (more) stage_row(p, row + nwarps, stage, lane);
         bfly_pairs<2>(v);                               // bits 7-11 (over m)
 
         // ---------------- row min / max, parameters ------------------------------------------------
@@ -171,9 +183,11 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 2) quant_token_warp_kernel(
             float r0, r1, r2, r3;
             unpack2(add2(v[2 * m], magic2), r0, r1);
             unpack2(add2(v[2 * m + 1], magic2), r2, r3);
-            const uint32_t lo8 = (__float_as_uint(r1) << 4) + __float_as_uint(r0);
-            const uint32_t hi8 = (__float_as_uint(r3) << 4) + __float_as_uint(r2);
-            const uint32_t w = (hi8 << 8) + lo8 + zsum;
+            // Horner in 16: ((b3 16 + b2) 16 + b1) 16 + b0 + 0x1111 zero
+            uint32_t w = __float_as_uint(r3) * 16u + __float_as_uint(r2);
+            w = w * 16u + __float_as_uint(r1);
+            w = w * 16u + __float_as_uint(r0);
+            w += zsum;
             qrow[m * 32] = (uint16_t)w;
         }
     }
@@ -206,7 +220,7 @@ int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld
         if (dev >= 0) attr_done[which][dev] = true;
     }
     long grid = (M + kWarpsPerCta - 1) / kWarpsPerCta;
-    if (grid > 2L * kNumSMs) grid = 2L * kNumSMs;
+    if (grid > (long)kCtasPerSm * kNumSMs) grid = (long)kCtasPerSm * kNumSMs;
     kern<<<(unsigned)grid, kWarpsPerCta * 32, smem, stream>>>(p);
     return cuda_status(cudaGetLastError(), "quant_token_warp launch");
 }
