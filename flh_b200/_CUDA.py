@@ -21,6 +21,7 @@ from .hadamard import get_hadK
 
 F16, BF16 = 0, 1
 GEMM_AUTO, GEMM_TCGEN05, GEMM_MMA_SYNC, GEMM_STREAM, GEMM_STREAM_SPLITK, GEMM_TCGEN05_DIRECT = 0, 1, 2, 3, 4, 5
+GEMM_TCGEN05_I8, GEMM_TCGEN05_I8_PAIR = 6, 7
 
 
 def _check(cond: bool, msg: str) -> None:
@@ -197,6 +198,20 @@ def _workspace(device, stream: int, nbytes: int):
     return ws
 
 
+_SCRATCH: dict = {}
+
+
+def _scratch(device, stream: int, nbytes: int):
+    """Uninitialised scratch for the int8-operand GEMM (the expanded operands), one per (device, stream); kept
+    apart from the zeroed split-K workspace, whose counters it would overwrite."""
+    key = (str(device), stream)
+    ws = _SCRATCH.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _SCRATCH[key] = ws
+    return ws
+
+
 def gemm_i4_dequant(A, B, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=None,
                     out_dtype=torch.float16, algo: int = GEMM_AUTO, out=None):
     """General form of the GEMM (include/flh_b200.h: flh_b200_gemm_i4_dequant).  Scale granularity
@@ -213,8 +228,13 @@ def gemm_i4_dequant(A, B, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=Non
     lib = _lib.load()
     with torch.cuda.device(A.device):
         stream = _stream(A)
-        need = lib.flh_b200_gemm_workspace_bytes(M, N, K, ag, bg, algo) if M <= 64 else 0
-        ws = _workspace(A.device, stream, need) if need else None
+        need = lib.flh_b200_gemm_workspace_bytes(M, N, K, ag, bg, algo)
+        if not need:
+            ws = None
+        elif M <= 64:
+            ws = _workspace(A.device, stream, need)
+        else:
+            ws = _scratch(A.device, stream, need)
         _lib.check(lib.flh_b200_gemm_i4_dequant(
             _ptr(A), _ptr(B), _ptr(A_scale), _ptr(A_zero), _ptr(B_scale), _ptr(B_rowsum), _ptr(bias), _ptr(D),
             M, N, K, ag, bg, BF16 if D.dtype == torch.bfloat16 else F16, algo, _ptr(ws), ws.numel() if ws is not None else 0,

@@ -46,6 +46,12 @@ int launch_gemm_tcgen05(const uint8_t *, const uint8_t *, const void *, const vo
                         const int32_t *, const void *, void *, long, long, long, long, long, int, int,
                         cudaStream_t);
 
+size_t gemm_i8_workspace_bytes(long M, long N, long K);
+int launch_gemm_i8(const uint8_t *, const uint8_t *, const void *, const void *, const void *, const int32_t *,
+                   const void *, void *, long, long, long, int, int, void *, cudaStream_t);
+int gemm_i8_status(int *);
+int gemm_i8_status_clear();
+
 int gemm_tcgen05_status(int *);
 int gemm_tcgen05_wait_profile(unsigned long long *);
 int gemm_tcgen05_status_clear();
@@ -161,6 +167,7 @@ int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group) 
 
 size_t flh_b200_gemm_workspace_bytes(long M, long N, long K, long a_group, long b_group, int algo) {
     if (algo == FLH_B200_GEMM_AUTO) algo = flh_b200_gemm_pick_algo(M, N, K, a_group, b_group);
+    if (algo == FLH_B200_GEMM_TCGEN05_I8 || algo == FLH_B200_GEMM_TCGEN05_I8_PAIR) return gemm_i8_workspace_bytes(M, N, K);
     if (algo != FLH_B200_GEMM_STREAM_SPLITK || M > 64) return 0;
     return stream_scratch_bytes(M, N, stream_splits(M, N, K));
 }
@@ -207,6 +214,17 @@ int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_s
             return launch_gemm_mma_tile(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, s);
         case FLH_B200_GEMM_TCGEN05:
             return launch_gemm_tcgen05(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, 0, s);
+        case FLH_B200_GEMM_TCGEN05_I8:
+        case FLH_B200_GEMM_TCGEN05_I8_PAIR: {
+            FLH_REQUIRE(a_group == K && b_group == K, FLH_B200_EINVAL, "the int8-operand kernels take per-token / per-channel scales only");
+            const size_t need = gemm_i8_workspace_bytes(M, N, K);
+            FLH_REQUIRE(workspace && workspace_bytes >= need, FLH_B200_EINVAL,
+                        "the int8-operand kernels need %zu bytes of workspace (got %zu)", need, workspace_bytes);
+            FLH_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, FLH_B200_EALIGN, "workspace must be 256-byte aligned");
+            FLH_REQUIRE(algo == FLH_B200_GEMM_TCGEN05_I8 || N % 256 == 0, FLH_B200_EINVAL, "the two-CTA kernel needs N %% 256 == 0 (got %ld)", N);
+            return launch_gemm_i8(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, out_dtype,
+                                  algo == FLH_B200_GEMM_TCGEN05_I8_PAIR, workspace, s);
+        }
         case FLH_B200_GEMM_TCGEN05_DIRECT:
             return launch_gemm_tcgen05(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, 1, s);
         default:
@@ -237,7 +255,10 @@ int flh_b200_gemm_status(int *out) {
     FLH_REQUIRE(out, FLH_B200_EINVAL, "null pointer");
     int rc = gemm_tcgen05_status(out);
     if (rc) return rc;
-    return out[0] ? gemm_tcgen05_status_clear() : 0;
+    if (out[0]) return gemm_tcgen05_status_clear();
+    rc = gemm_i8_status(out);
+    if (rc) return rc;
+    return out[0] ? gemm_i8_status_clear() : 0;
 }
 
 int flh_b200_gemm_wait_profile(unsigned long long *out) {

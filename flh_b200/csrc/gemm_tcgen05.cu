@@ -21,8 +21,7 @@
 //
 // Every wait on an mbarrier is bounded (two seconds); a wait that runs out records where in a
 // device status word, and the CTA drains its copies, frees its TMEM and returns.
-#include "common.cuh"
-#include <cuda.h>
+#include "tc_common.cuh"
 
 namespace flh {
 namespace {
@@ -36,80 +35,9 @@ __device__ int g_status[4];             // [0] = first error code, [1] = block, 
 // [5] converter on ex_empty, [6]/[7] epilogue on acc_full.  Diagnostic only (flh_b200_gemm_wait_profile).
 __device__ unsigned long long g_wait_ns[8];
 
-// ---- PTX wrappers ---------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ uint64_t gtimer() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait: false when two seconds pass or another thread of the CTA already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code,
                                           unsigned long long *waited = nullptr) {
-    if (mbar_try(bar, parity)) return true;
-    const uint64_t t0 = gtimer();
-    for (int it = 0;; ++it) {
-        if (mbar_try(bar, parity)) {
-            if (waited) *waited += gtimer() - t0;
-            return true;
-        }
-        if ((it & 63) == 63) {
-            if (*abort_flag) return false;
-            if (gtimer() - t0 > 2000000000ull) {
-                *abort_flag = code;
-                if (atomicCAS(&g_status[0], 0, code) == 0) g_status[1] = blockIdx.x + 65536 * blockIdx.y;
-                return false;
-            }
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
-// K-major, 128-byte swizzle: 8-row groups 1024 B apart (SBO), LBO unused (1), descriptor version 1.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+    return mbar_wait_status(g_status, bar, parity, abort_flag, code, waited);
 }
 
 struct TcParams {
@@ -154,32 +82,6 @@ struct SmemPlan {
 static_assert(256 * SmemPlan<256>::kLowRegs(true) + 256 * SmemPlan<256>::kEpiRegs(true) <= 65536, "register budget");
 static_assert(256 * SmemPlan<256>::kLowRegs(false) + 256 * SmemPlan<256>::kEpiRegs(false) <= 65536, "register budget");
 static_assert(256 * SmemPlan<128>::kLowRegs(true) + 128 * SmemPlan<128>::kEpiRegs(true) <= 384 * 168, "register budget");
-
-__device__ __forceinline__ void store_row_chunk(void *D, bool bf16, long off, const float (&v)[32]) {
-    if (bf16) {
-        __nv_bfloat16 *d = static_cast<__nv_bfloat16 *>(D) + off;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            uint4 o;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-            o.x = *reinterpret_cast<uint32_t *>(&h0); o.y = *reinterpret_cast<uint32_t *>(&h1);
-            o.z = *reinterpret_cast<uint32_t *>(&h2); o.w = *reinterpret_cast<uint32_t *>(&h3);
-            *reinterpret_cast<uint4 *>(d + 8 * j) = o;
-        }
-    } else {
-        __half *d = static_cast<__half *>(D) + off;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            uint4 o;
-            __half2 h0 = __floats2half2_rn(v[8 * j], v[8 * j + 1]), h1 = __floats2half2_rn(v[8 * j + 2], v[8 * j + 3]);
-            __half2 h2 = __floats2half2_rn(v[8 * j + 4], v[8 * j + 5]), h3 = __floats2half2_rn(v[8 * j + 6], v[8 * j + 7]);
-            o.x = *reinterpret_cast<uint32_t *>(&h0); o.y = *reinterpret_cast<uint32_t *>(&h1);
-            o.z = *reinterpret_cast<uint32_t *>(&h2); o.w = *reinterpret_cast<uint32_t *>(&h3);
-            *reinterpret_cast<uint4 *>(d + 8 * j) = o;
-        }
-    }
-}
 
 // Persistent: CTA b works on output tiles b, b + gridDim.x, ... (row blocks fastest, so the CTAs that
 // run together share the same weight columns).  Barrier phases and the TMEM accumulator buffer are

@@ -47,6 +47,10 @@ extern "C" {
 #define FLH_B200_GEMM_TCGEN05_DIRECT 5 /* tcgen05 path whose converter warps load the packed operands from L2
                                          straight into registers (no TMA staging): less shared-memory traffic */
 #define FLH_B200_GEMM_STREAM_SPLITK 4 /* the same with K cut across CTAs; needs workspace (see below)           */
+#define FLH_B200_GEMM_TCGEN05_I8 6 /* large M without group scales: both operands expanded to int8 in the workspace
+                                     first, then TMA + tcgen05.mma on int8 tiles (no conversion inside the GEMM)  */
+#define FLH_B200_GEMM_TCGEN05_I8_PAIR 7 /* the same on two-CTA clusters (tcgen05 cta_group::2, 256 x 256 tiles);
+                                          N % 256 == 0                                                         */
 
 int flh_b200_version(void);
 const char *flh_b200_last_error(void);
@@ -130,6 +134,9 @@ int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t
  *   workspace the plain streaming kernel runs instead.  Split-K adds the per-split binary32 chains in
  *   split order, so with group scales its outputs can differ from the single chain in the last bit
  *   (<= 1e-3 relative); without group scales the partial sums are int32 and the result is identical.
+ *   The int8-operand kernels (TCGEN05_I8, TCGEN05_I8_PAIR; a_group = b_group = K only) write the expanded
+ *   operands, (M + N) * K bytes, into the workspace; it needs no initial contents, results are bit-identical
+ *   to the other kernels, and launches that share a workspace must not overlap on the GPU.
  * Replaces flhDenseLayerGEMM_i4_o16 (flh/kernels/gemm_and_dequant_i4.cu:471-508) and
  * flhDenseLayerGEMM_i4_o16_gs (flh/kernels/gemm_and_dequant_i4_gs.h); bound as
  * gemm_i4_dequant_o16(_gs) (flh/cuda/flh_cuda_bindings.cpp:75-113, 253-299). */
