@@ -50,6 +50,7 @@ size_t gemm_i8_workspace_bytes(long M, long N, long K);
 int launch_gemm_i8(const uint8_t *, const uint8_t *, const void *, const void *, const void *, const int32_t *,
                    const void *, void *, long, long, long, int, int, void *, cudaStream_t);
 int gemm_i8_status(int *);
+int gemm_i8_wait_profile(unsigned long long *);
 int gemm_i8_status_clear();
 
 int gemm_tcgen05_status(int *);
@@ -263,7 +264,11 @@ int flh_b200_gemm_status(int *out) {
 
 int flh_b200_gemm_wait_profile(unsigned long long *out) {
     FLH_REQUIRE(out, FLH_B200_EINVAL, "null pointer");
-    return gemm_tcgen05_wait_profile(out);
+    int rc = gemm_tcgen05_wait_profile(out);
+    if (rc) return rc;
+    bool any = false;
+    for (int i = 0; i < 8; ++i) any = any || out[i] != 0;
+    return any ? 0 : gemm_i8_wait_profile(out);        // nothing from the converting kernels: the int8-operand ones
 }
 
 void flhDenseLayerGEMM_i4_o16(const uint8_t *A, const uint8_t *B, const void *A_scale, const void *B_scale,

@@ -10,8 +10,9 @@
 //                      two TMEM buffers), warps 4-7 epilogue (tcgen05.ld, zero-point term, scales, bias,
 //                      f16/bf16 rows).  PAIR = true runs two CTAs of a cluster on one 256 x 256 tile
 //                      (tcgen05 cta_group::2): each CTA loads 128 rows of A and 128 rows of B, the leader
-//                      issues the MMAs for both, commits are multicast to both CTAs' barriers, and the
-//                      peer reports its loads and its drained accumulators with remote mbarrier arrives.
+//                      issues the MMAs for both, commits are multicast to both CTAs' barriers, the peer's TMA
+//                      loads complete on the leader's barrier, and the peer reports its drained accumulators
+//                      with remote mbarrier arrives.
 // The int32 dot product is 256 * sum(qa qw); the factor is folded back exactly in the epilogue.
 // Every wait is bounded (two seconds) and reports through the same status word as the other GEMM kernels.
 #include "tc_common.cuh"
@@ -24,9 +25,13 @@ constexpr int BM = 128;
 constexpr int BK = 128;
 
 __device__ int g_status_i8[4];
+// Nanoseconds inside bounded waits, summed over CTAs: [1] producer on empty, [2] MMA on acc_empty, [3] MMA on full,
+// [6] epilogue on acc_full, [7] MMA issuers (CTAs, or clusters).  Diagnostic only.
+__device__ unsigned long long g_wait_ns_i8[8];
 
-__device__ __forceinline__ bool wait_i8(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
-    return mbar_wait_status(g_status_i8, bar, parity, abort_flag, code, nullptr);
+__device__ __forceinline__ bool wait_i8(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code,
+                                        unsigned long long *waited = nullptr) {
+    return mbar_wait_status(g_status_i8, bar, parity, abort_flag, code, waited);
 }
 
 // ---- cluster helpers (PAIR) -------------------------------------------------------------------
@@ -44,6 +49,13 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t rank) 
     uint32_t raddr;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(bar), "r"(rank));
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(raddr) : "memory");
+}
+// TMA tile load of a CTA of a pair whose completion is counted on the barrier at the same offset in CTA 0
+__device__ __forceinline__ void tma_load_2d_to_leader(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+    uint32_t rbar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(rbar) : "r"(bar));
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(rbar) : "memory");
 }
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
     const uint16_t mask = 3;
@@ -109,8 +121,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint8_t *sm = smem_dyn + (base - raw);
 
     const uint32_t bars = base + Plan::kBarOff;
-    auto full = [&](int s) { return bars + 8u * s; };                 // this CTA's tiles of stage s have landed
-    auto peer_full = [&](int s) { return bars + 8u * (8 + s); };     // leader only: the peer's tiles have landed
+    auto full = [&](int s) { return bars + 8u * s; };                 // the tiles of stage s have landed (a pair: both CTAs', counted by the leader)
     auto empty = [&](int s) { return bars + 8u * (16 + s); };        // the tensor core has read stage s
     auto acc_full = [&](int b) { return bars + 8u * (24 + b); };
     auto acc_empty = [&](int b) { return bars + 8u * (26 + b); };    // leader only in a pair
@@ -126,7 +137,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(full(s), 1);
-            mbar_init(peer_full(s), 1);
             mbar_init(empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), PAIR ? 256 : 128); }
@@ -154,19 +164,28 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             int it = 0;
             bool ok = true;
+            unsigned long long w1 = 0;
             for (int tile = first; tile < p.num_tiles && ok; tile += step) {
                 const int m0 = (tile % p.m_blocks) * (PAIR ? 2 * BM : BM) + (int)rank * BM;
                 const int n0 = (tile / p.m_blocks) * BN + (int)rank * Plan::BNL;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % S;
-                    if (!wait_i8(empty(s), ((it / S) & 1) ^ 1, abort_flag, 11)) { ok = false; break; }
-                    mbar_expect_tx(full(s), Plan::kStageBytes);
+                    if (!wait_i8(empty(s), ((it / S) & 1) ^ 1, abort_flag, 11, &w1)) { ok = false; break; }
                     const uint32_t dst = base + s * Plan::kStageBytes;
-                    tma_load_2d(dst, &map_a, kb * BK, m0, full(s));
-                    tma_load_2d(dst + BM * BK, &map_b, kb * BK, n0, full(s));
+                    if (PAIR && rank == 1) {
+                        // the leader's barrier counts these bytes too (it has expected them, or will: a transaction
+                        // count may run negative for a while, and the phase cannot end before the leader's arrive)
+                        tma_load_2d_to_leader(dst, &map_a, kb * BK, m0, full(s));
+                        tma_load_2d_to_leader(dst + BM * BK, &map_b, kb * BK, n0, full(s));
+                    } else {
+                        mbar_expect_tx(full(s), (PAIR ? 2 : 1) * Plan::kStageBytes);
+                        tma_load_2d(dst, &map_a, kb * BK, m0, full(s));
+                        tma_load_2d(dst + BM * BK, &map_b, kb * BK, n0, full(s));
+                    }
                 }
             }
-            if (*abort_flag) {               // let the copies already issued land before the CTA leaves
+            if (rank == 0) atomicAdd(&g_wait_ns_i8[1], w1);
+            if (*abort_flag && rank == 0) {  // let the copies already issued land before the CTA leaves
                 for (int j = it > S ? it - S : 0; j < it; ++j) {
                     const uint64_t t0 = gtimer();
                     while (!mbar_try(full(j % S), (j / S) & 1) && gtimer() - t0 < 100000000ull) {}
@@ -180,13 +199,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                    ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((PAIR ? 2 * BM : BM) >> 4) << 24);
             int it = 0, u = 0;
             bool ok = true;
+            unsigned long long w2 = 0, w3 = 0, w4 = 0;
             for (int tile = first; tile < p.num_tiles && ok; tile += step, ++u) {
                 const int buf = u & 1;
-                if (u >= 2 && !wait_i8(acc_empty(buf), ((u >> 1) & 1) ^ 1, abort_flag, 12)) { ok = false; break; }
+                if (u >= 2 && !wait_i8(acc_empty(buf), ((u >> 1) & 1) ^ 1, abort_flag, 12, &w2)) { ok = false; break; }
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % S;
-                    if (!wait_i8(full(s), (it / S) & 1, abort_flag, 13)) { ok = false; break; }
-                    if (PAIR && !wait_i8(peer_full(s), (it / S) & 1, abort_flag, 14)) { ok = false; break; }
+                    if (!wait_i8(full(s), (it / S) & 1, abort_flag, 13, &w3)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = base + s * Plan::kStageBytes;
                     const uint64_t adesc = make_smem_desc(a_addr), bdesc = make_smem_desc(a_addr + BM * BK);
@@ -197,19 +216,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 if (ok) { if (PAIR) tc_commit_pair(acc_full(buf)); else tc_commit(acc_full(buf)); }
             }
-        }
-    } else if (warp == 2) {
-        // ------------------------------------------------------------ peer: report landed stages to the leader
-        if (PAIR && rank == 1 && lane == 0) {
-            int it = 0;
-            bool ok = true;
-            for (int tile = first; tile < p.num_tiles && ok; tile += step) {
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int s = it % S;
-                    if (!wait_i8(full(s), (it / S) & 1, abort_flag, 15)) { ok = false; break; }
-                    mbar_arrive_remote(peer_full(s), 0);
-                }
-            }
+            atomicAdd(&g_wait_ns_i8[2], w2); atomicAdd(&g_wait_ns_i8[3], w3); atomicAdd(&g_wait_ns_i8[4], w4);
+            atomicAdd(&g_wait_ns_i8[7], 1ull);
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------ epilogue
@@ -324,19 +332,27 @@ int launch_i8(const CUtensorMap &ma, const CUtensorMap &mb, const I8Params &p, c
     const int sms = device_sms();
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
-    if (PAIR) {
-        int pairs = sms / 2;
-        if (q.num_tiles < pairs) pairs = q.num_tiles;
-        cfg.gridDim = dim3(2 * pairs);
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr; cfg.numAttrs = 1;
-    } else {
-        cfg.gridDim = dim3(q.num_tiles < sms ? q.num_tiles : sms);
-    }
     cfg.blockDim = dim3(Plan::kThreads);
     cfg.dynamicSmemBytes = Plan::kBytes;
     cfg.stream = stream;
+    if (PAIR) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        // the kernel is persistent: launch no more clusters than can be resident at once
+        static int max_pairs = 0;
+        if (max_pairs == 0) {
+            cfg.gridDim = dim3(sms / 2 * 2);
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) n = sms / 2;
+            max_pairs = n;
+        }
+        int pairs = max_pairs;
+        if (q.num_tiles < pairs) pairs = q.num_tiles;
+        cfg.gridDim = dim3(2 * pairs);
+    } else {
+        cfg.gridDim = dim3(q.num_tiles < sms ? q.num_tiles : sms);
+    }
     e = cudaLaunchKernelEx(&cfg, kern, ma, mb, q);
     return cuda_status(e, "gemm_i8 launch");
 }
@@ -388,6 +404,13 @@ int launch_gemm_i8(const uint8_t *A, const uint8_t *B, const void *a_scale, cons
     if (rc) return rc;
     if (bn == 256) return u ? launch_i8<256, true, false>(ma, mb, p, stream) : launch_i8<256, false, false>(ma, mb, p, stream);
     return u ? launch_i8<128, true, false>(ma, mb, p, stream) : launch_i8<128, false, false>(ma, mb, p, stream);
+}
+
+int gemm_i8_wait_profile(unsigned long long *out8) {
+    cudaError_t e = cudaMemcpyFromSymbol(out8, g_wait_ns_i8, sizeof(unsigned long long) * 8);
+    if (e != cudaSuccess) return cuda_status(e, "wait profile read");
+    unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    return cuda_status(cudaMemcpyToSymbol(g_wait_ns_i8, z, sizeof(z)), "wait profile clear");
 }
 
 int gemm_i8_status(int *out4) {
