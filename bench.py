@@ -256,9 +256,15 @@ def run_ours(args, world, rank, local, dist):
         D = torch.empty((M, N), dtype=torch.float16, device=device)
         flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device) if prefill else None
 
+        prepack = bool(args.prepack and prefill and asym)
+        B8 = C.expand_i4(sets[0][1]) if prepack else None
+
         def fn(i):
             A, B, sa, sb, za, rs = sets[i % len(sets)]
-            C.gemm_i4_dequant(A, B, sa, sb, A_zero=za, B_rowsum=rs, out=D)
+            if prepack:
+                C.gemm_i8w_dequant(A, B8, sa, sb, A_zero=za, B_rowsum=rs, out=D)
+            else:
+                C.gemm_i4_dequant(A, B, sa, sb, A_zero=za, B_rowsum=rs, out=D)
 
         with ClockSampler(local) as cs:
             t = timed_loop(fn, steps, warmup, dist, device, graph=not prefill, sampler=cs)
@@ -278,7 +284,8 @@ def run_ours(args, world, rank, local, dist):
                                  "peak_src": peaks["src"], "unit": "GB/s", "frac": b * steps / t / 1e9 / peaks["hbm_gbs"], "traffic": None})
         out.update(ms_per_step=t / steps * 1e3, clocks=cs.summary(), gpu_launches=steps,
                    config={"workload": f"int4 GEMM + {'per-token asymmetric x per-channel' if asym else 'group-128'} dequant, M={M}, {K}->{N}, f16 out",
-                           "M": M, "N": N, "K": K,
+                           "M": M, "N": N, "K": K, "algo": int(_lib.load().flh_b200_gemm_pick_algo(M, N, K, K if asym else 128, K if asym else 128)),
+                           "weights_prepacked_int8": prepack,
                            "l2": "weights of three rotating problems (3 x 45 MB > L2); the K steps run as one CUDA graph" if not prefill else "operands re-used across steps (compute-bound)",
                            "parallelism": f"replicated x{world}, no collective"})
     elif args.workload in ("llama7b_prefill", "llama7b_decode", "llama70b_prefill", "llama70b_decode"):
@@ -290,6 +297,9 @@ def run_ours(args, world, rank, local, dist):
             shape["n_layers"] = args.layers
         cfg = DecoderConfig(**shape, vocab=32000, act_mode=args.act_mode, tp=world)
         model = Decoder(cfg, device, seed=0, group=None, with_head=True)
+        prepack = bool(args.prepack and prefill and args.act_mode == "token_asym")
+        if prepack:
+            model.prepack_int8()
         if prefill:
             B, S = (4, 2048) if big else (1, 2048)
             ids = torch.randint(100, 200, (B, S), device=device)
@@ -318,7 +328,8 @@ def run_ours(args, world, rank, local, dist):
                    steps=steps, warmup=max(warmup, 3), scaling="strong" if world > 1 else "weak", clocks=cs.summary(),
                    config={"workload": args.workload, **shape, "act_mode": args.act_mode, "batch": B,
                            "seq_or_ctx": 2048 if prefill else 1024, "parallelism": f"tp{world}" if world > 1 else "single GPU",
-                           "weights": "random int4 codes and scales (no checkpoint)", "cuda_graph": graphed})
+                           "weights": "random int4 codes and scales (no checkpoint)", "cuda_graph": graphed,
+                           "weights_prepacked_int8": prepack})
     else:
         raise SystemExit(f"unknown workload {args.workload}")
     st = C.gemm_status()
@@ -379,6 +390,11 @@ def extras(C, device, peaks):
             A, B, sa, sb, za, rs = gemm_inputs(C, m, n, k, grouped, asym, device)
             t = _time(lambda: C.gemm_i4_dequant(A, B, sa, sb, A_zero=za, B_rowsum=rs), iters=5, warm=2)
             ex[f"gemm_M{m}_{k}to{n}_{tag}_TOPS"] = 2.0 * m * n * k / t / 1e12
+            if asym:        # the same with the weights expanded to int8 ahead of time
+                B8 = C.expand_i4(B)
+                t = _time(lambda: C.gemm_i8w_dequant(A, B8, sa, sb, A_zero=za, B_rowsum=rs), iters=5, warm=2)
+                ex[f"gemm_M{m}_{k}to{n}_{tag}_prepacked_TOPS"] = 2.0 * m * n * k / t / 1e12
+                del B8
     for (m, k, n) in ((1, 4096, 22016), (16, 4096, 22016), (16, 11008, 4096), (16, 4096, 4096)):
         sets = [gemm_inputs(C, m, n, k, True, False, device, seed=s) for s in range(3)]
         it = [0]
@@ -456,6 +472,8 @@ def main():
     ap.add_argument("--workload", default="had_quant")
     ap.add_argument("--act-mode", default="group_sym", choices=["group_sym", "token_asym"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count of the llama workloads")
+    ap.add_argument("--prepack", action="store_true",
+                    help="gemm_prefill / llama*_prefill with token_asym: keep an int8 copy of the weights (expanded once, outside the timed region)")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline (profiling runs)")
     args = ap.parse_args()
     world, rank, local, dist = dist_setup(args)

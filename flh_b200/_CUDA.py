@@ -242,6 +242,31 @@ def gemm_i4_dequant(A, B, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=Non
     return D
 
 
+def expand_i4(B):
+    """Packed int4 weights u8[N, K/2] -> the int8 copy u8[N, K] (16 * q) that gemm_i8w_dequant multiplies."""
+    _check(B.is_cuda and B.dtype == torch.uint8 and B.dim() == 2 and B.is_contiguous(), "B must be a contiguous CUDA uint8 matrix")
+    N, Kp = B.shape
+    out = torch.empty((N, 2 * Kp), dtype=torch.uint8, device=B.device)
+    with torch.cuda.device(B.device):
+        _lib.check(_lib.load().flh_b200_expand_i4(_ptr(B), N, 2 * Kp, _ptr(out), _stream(B)), "expand_i4")
+    return out
+
+
+def gemm_i8w_dequant(A, B8, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=None, out_dtype=torch.float16, out=None):
+    """The GEMM with per-token / per-channel scales on weights expanded ahead of time by expand_i4 (prefill batches)."""
+    M, Kp = A.shape
+    N, K = B8.shape
+    _check(K == 2 * Kp, "B8 must be [N, K] for A [M, K/2]")
+    D = out if out is not None else torch.empty((M, N), dtype=out_dtype, device=A.device)
+    with torch.cuda.device(A.device):
+        stream = _stream(A)
+        ws = _scratch(A.device, stream, M * K)
+        _lib.check(_lib.load().flh_b200_gemm_i8w_dequant(
+            _ptr(A), _ptr(B8), _ptr(A_scale), _ptr(A_zero), _ptr(B_scale), _ptr(B_rowsum), _ptr(bias), _ptr(D),
+            M, N, K, BF16 if D.dtype == torch.bfloat16 else F16, _ptr(ws), ws.numel(), stream), "gemm_i8w_dequant")
+    return D
+
+
 def gemm_status():
     """[code, cta, 0, 0] of the tcgen05 GEMM's bounded waits; synchronises.  0 = clean."""
     out = (ctypes.c_int * 4)()

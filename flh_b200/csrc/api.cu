@@ -47,8 +47,9 @@ int launch_gemm_tcgen05(const uint8_t *, const uint8_t *, const void *, const vo
                         cudaStream_t);
 
 size_t gemm_i8_workspace_bytes(long M, long N, long K);
-int launch_gemm_i8(const uint8_t *, const uint8_t *, const void *, const void *, const void *, const int32_t *,
-                   const void *, void *, long, long, long, int, int, void *, cudaStream_t);
+int launch_gemm_i8(const uint8_t *, const uint8_t *, const uint8_t *, const void *, const void *, const void *,
+                   const int32_t *, const void *, void *, long, long, long, int, int, void *, cudaStream_t);
+int launch_expand_i4(const uint8_t *, long, long, uint8_t *, cudaStream_t);
 int gemm_i8_status(int *);
 int gemm_i8_wait_profile(unsigned long long *);
 int gemm_i8_status_clear();
@@ -161,8 +162,10 @@ int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t
 }
 
 int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group) {
-    (void)a_group; (void)b_group;
     if (M <= 64) return stream_splits(M, N, K) > 1 ? FLH_B200_GEMM_STREAM_SPLITK : FLH_B200_GEMM_STREAM;
+    // large batches without group scales: expanding both operands to int8 first pays for itself
+    if (a_group == K && b_group == K && M >= 1024)
+        return N % 256 == 0 ? FLH_B200_GEMM_TCGEN05_I8_PAIR : FLH_B200_GEMM_TCGEN05_I8;
     return FLH_B200_GEMM_TCGEN05;
 }
 
@@ -194,6 +197,10 @@ int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_s
         if (algo == FLH_B200_GEMM_STREAM_SPLITK &&
             (!workspace || workspace_bytes < stream_scratch_bytes(M, N, stream_splits(M, N, K))))
             algo = FLH_B200_GEMM_STREAM;
+        // likewise the int8-operand kernels give way to the converting kernel
+        if ((algo == FLH_B200_GEMM_TCGEN05_I8 || algo == FLH_B200_GEMM_TCGEN05_I8_PAIR) &&
+            (!workspace || workspace_bytes < gemm_i8_workspace_bytes(M, N, K) || (reinterpret_cast<uintptr_t>(workspace) & 255)))
+            algo = FLH_B200_GEMM_TCGEN05;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (algo) {
@@ -223,7 +230,7 @@ int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_s
                         "the int8-operand kernels need %zu bytes of workspace (got %zu)", need, workspace_bytes);
             FLH_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, FLH_B200_EALIGN, "workspace must be 256-byte aligned");
             FLH_REQUIRE(algo == FLH_B200_GEMM_TCGEN05_I8 || N % 256 == 0, FLH_B200_EINVAL, "the two-CTA kernel needs N %% 256 == 0 (got %ld)", N);
-            return launch_gemm_i8(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, out_dtype,
+            return launch_gemm_i8(A, B, nullptr, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, out_dtype,
                                   algo == FLH_B200_GEMM_TCGEN05_I8_PAIR, workspace, s);
         }
         case FLH_B200_GEMM_TCGEN05_DIRECT:
@@ -250,6 +257,35 @@ int flh_b200_gemm_i4_dequant_decode_noalloc(const uint8_t *A, const uint8_t *B, 
     FLH_REQUIRE(aligned16(A) && aligned16(B), FLH_B200_EALIGN, "A and B must be 16-byte aligned");
     return launch_gemm_stream_static(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group,
                                      out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int flh_b200_expand_i4(const uint8_t *packed, long rows, long K, uint8_t *out, void *stream) {
+    FLH_REQUIRE(rows >= 0 && K > 0 && K % 128 == 0, FLH_B200_EINVAL, "bad shape rows=%ld K=%ld (K must be a multiple of 128)", rows, K);
+    if (rows == 0) return 0;
+    FLH_REQUIRE(packed && out, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(aligned16(packed) && (reinterpret_cast<uintptr_t>(out) & 127) == 0, FLH_B200_EALIGN,
+                "packed must be 16-byte aligned and out 128-byte aligned");
+    return launch_expand_i4(packed, rows, K, out, static_cast<cudaStream_t>(stream));
+}
+
+int flh_b200_gemm_i8w_dequant(const uint8_t *A, const uint8_t *B8, const void *a_scale, const void *a_zero,
+                              const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D, long M, long N,
+                              long K, int out_dtype, void *workspace, size_t workspace_bytes, void *stream) {
+    FLH_REQUIRE(M >= 0 && N >= 0 && K > 0, FLH_B200_EINVAL, "bad shape M=%ld N=%ld K=%ld", M, N, K);
+    FLH_REQUIRE(K % 128 == 0 && K <= 65536, FLH_B200_EINVAL, "K must be a multiple of 128 and <= 65536 (got %ld)", K);
+    FLH_REQUIRE(N % 128 == 0, FLH_B200_EINVAL, "N must be a multiple of 128 (got %ld)", N);
+    FLH_REQUIRE(out_dtype == FLH_B200_F16 || out_dtype == FLH_B200_BF16, FLH_B200_EINVAL, "out_dtype must be F16 or BF16");
+    if (M == 0 || N == 0) return 0;
+    FLH_REQUIRE(A && B8 && a_scale && b_scale && D, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(!a_zero || b_rowsum, FLH_B200_EINVAL, "a_zero needs b_rowsum");
+    FLH_REQUIRE(aligned16(A) && (reinterpret_cast<uintptr_t>(B8) & 127) == 0, FLH_B200_EALIGN,
+                "A must be 16-byte aligned and the expanded weights 128-byte aligned");
+    FLH_REQUIRE((reinterpret_cast<uintptr_t>(D) & 15) == 0, FLH_B200_EALIGN, "D must be 16-byte aligned");
+    FLH_REQUIRE(workspace && workspace_bytes >= (size_t)M * K, FLH_B200_EINVAL,
+                "needs M * K = %zu bytes of workspace for the expanded activations (got %zu)", (size_t)M * K, workspace_bytes);
+    FLH_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, FLH_B200_EALIGN, "workspace must be 256-byte aligned");
+    return launch_gemm_i8(A, nullptr, B8, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, out_dtype,
+                          N % 256 == 0, workspace, static_cast<cudaStream_t>(stream));
 }
 
 int flh_b200_gemm_status(int *out) {

@@ -364,22 +364,30 @@ size_t gemm_i8_workspace_bytes(long M, long N, long K) {
     return a + (size_t)N * K;
 }
 
+int launch_expand_i4(const uint8_t *packed, long rows, long K, uint8_t *out, cudaStream_t stream) {
+    const long n16 = rows * K / 32;                            // 16-byte packed chunks
+    if (n16 == 0) return 0;
+    long grid = (n16 + 255) / 256;
+    const long cap = 8L * device_sms();
+    if (grid > cap) grid = cap;
+    expand_i4_kernel<<<(unsigned)grid, 256, 0, stream>>>(reinterpret_cast<const uint4 *>(packed), reinterpret_cast<uint4 *>(out), n16);
+    return cuda_status(cudaGetLastError(), "expand_i4 launch");
+}
+
 // pair = 0: one CTA per 128 x BN tile; pair = 1: two-CTA clusters on 256 x 256 tiles (needs N % 256 == 0).
-int launch_gemm_i8(const uint8_t *A, const uint8_t *B, const void *a_scale, const void *a_zero, const void *b_scale,
-                   const int32_t *b_rowsum, const void *bias, void *D, long M, long N, long K, int out_dtype, int pair,
-                   void *workspace, cudaStream_t stream) {
+// B8 != nullptr: the weights are already expanded (launch_expand_i4), only A goes through the workspace.
+int launch_gemm_i8(const uint8_t *A, const uint8_t *B, const uint8_t *B8, const void *a_scale, const void *a_zero,
+                   const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D, long M, long N, long K,
+                   int out_dtype, int pair, void *workspace, cudaStream_t stream) {
     uint8_t *ea = static_cast<uint8_t *>(workspace);
-    uint8_t *eb = ea + (((size_t)M * K + 255) & ~(size_t)255);
-    {
-        const long na = M * K / 32, nb = N * K / 32;           // 16-byte packed chunks
-        const int sms = device_sms();
-        long ga = (na + 255) / 256, gb = (nb + 255) / 256;
-        if (ga > 8L * sms) ga = 8L * sms;
-        if (gb > 8L * sms) gb = 8L * sms;
-        expand_i4_kernel<<<(unsigned)ga, 256, 0, stream>>>(reinterpret_cast<const uint4 *>(A), reinterpret_cast<uint4 *>(ea), na);
-        expand_i4_kernel<<<(unsigned)gb, 256, 0, stream>>>(reinterpret_cast<const uint4 *>(B), reinterpret_cast<uint4 *>(eb), nb);
-        int rc = cuda_status(cudaGetLastError(), "expand_i4 launch");
+    const uint8_t *eb = B8;
+    int rc = launch_expand_i4(A, M, K, ea, stream);
+    if (rc) return rc;
+    if (!eb) {
+        uint8_t *dst = ea + (((size_t)M * K + 255) & ~(size_t)255);
+        rc = launch_expand_i4(B, N, K, dst, stream);
         if (rc) return rc;
+        eb = dst;
     }
     I8Params p;
     p.a_scale = static_cast<const __half *>(a_scale);
@@ -391,7 +399,7 @@ int launch_gemm_i8(const uint8_t *A, const uint8_t *B, const void *a_scale, cons
     p.out_bf16 = out_dtype == FLH_B200_BF16;
     const bool u = a_zero != nullptr;
     CUtensorMap ma, mb;
-    int rc = make_map_i8(&ma, ea, M, K, BM);
+    rc = make_map_i8(&ma, ea, M, K, BM);
     if (rc) return rc;
     if (pair) {
         if (N % 256 != 0) return fail(FLH_B200_EINVAL, "the two-CTA kernel needs N %% 256 == 0 (got %ld)", N);

@@ -141,6 +141,13 @@ class Decoder(torch.nn.Module):
         self.norm = RMSNorm(cfg.hidden, cfg.eps).to(device)
         self.head = torch.nn.Linear(cfg.hidden, cfg.vocab, bias=False, device=device, dtype=torch.float16) if with_head else None
 
+    def prepack_int8(self):
+        """Prefill-heavy serving: every W4 linear with per-channel scales keeps an int8 copy of its weights too."""
+        for m in self.modules():
+            if isinstance(m, LinearFLH):
+                m.prepack_int8()
+        return self
+
     def new_cache(self, batch, max_len):
         c = self.cfg
         nkv = max(c.n_kv_heads // c.tp, 1)

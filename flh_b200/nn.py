@@ -186,6 +186,7 @@ class LinearFLH(torch.nn.Module):
         else:
             self.bias = None
         self._rowsum = None
+        self._w_i8 = None          # optional int8 copy of the weights for large-batch GEMMs (prepack_int8)
 
     # -- offline side ---------------------------------------------------------------------------
     def _pack_weights(self, w_int, scale, zero):
@@ -193,6 +194,7 @@ class LinearFLH(torch.nn.Module):
         self.w_zero.copy_(zero.reshape(self.w_zero.shape).clamp(0, 15).to(torch.uint8))
         self.w_packed.copy_(pack_i4(w_int.to(torch.int32).clamp(-8, 7)).reshape(-1))
         self._rowsum = None
+        self._w_i8 = None
 
     def _unpack_weights(self):
         w = unpack_i4(self.w_packed.view(self.out_features, self.in_features // 2)).to(self.w_scale.dtype)
@@ -237,6 +239,16 @@ class LinearFLH(torch.nn.Module):
             self._rowsum = _CUDA.weight_rowsum(self.w_packed.view(self.out_features, self.in_features // 2), group)
         return self._rowsum
 
+    PREPACK_MIN_ROWS = 256      # batches from which the int8 copy is used
+
+    def prepack_int8(self):
+        """Keep an int8 copy of the weights (1 byte per weight on top of the packed half byte) for large-batch
+        GEMMs with per-channel weight scales: the tensor cores then read int8 tiles straight from TMA.  Decode-size
+        batches keep streaming the packed weights.  No counterpart in the reference (int4 weights only)."""
+        if self.w_scale.shape[1] == 1 and self._w_i8 is None:
+            self._w_i8 = _CUDA.expand_i4(self.w_packed.view(self.out_features, self.in_features // 2))
+        return self
+
     def forward(self, x, a_scale=None, a_zero=None, x_is_packed=True, is_symmetric=None, out_dtype=None):
         """x: packed activations [.., K/2]; a_scale [.., K/gs] (group mode) or [.., 1] (per token);
         a_zero None or like a_scale.  Returns [.., N] in the dtype of w_scale (flh/nn/linear.py:125-133)."""
@@ -248,9 +260,13 @@ class LinearFLH(torch.nn.Module):
         if a_zero is not None:
             a_zero = a_zero.reshape(M, -1)
             rs = self.w_rowsum(min(ga, gb))
-        y = _CUDA.gemm_i4_dequant(x.reshape(M, -1), self.w_packed.view(self.out_features, self.in_features // 2),
-                                  a_scale, self.w_scale, A_zero=a_zero, B_rowsum=rs, bias=self.bias,
-                                  out_dtype=out_dtype or self.w_scale.dtype)
+        if self._w_i8 is not None and a_scale.shape[1] == 1 and M >= self.PREPACK_MIN_ROWS:
+            y = _CUDA.gemm_i8w_dequant(x.reshape(M, -1), self._w_i8, a_scale, self.w_scale, A_zero=a_zero, B_rowsum=rs,
+                                       bias=self.bias, out_dtype=out_dtype or self.w_scale.dtype)
+        else:
+            y = _CUDA.gemm_i4_dequant(x.reshape(M, -1), self.w_packed.view(self.out_features, self.in_features // 2),
+                                      a_scale, self.w_scale, A_zero=a_zero, B_rowsum=rs, bias=self.bias,
+                                      out_dtype=out_dtype or self.w_scale.dtype)
         return y.view(lead + (self.out_features,))
 
     def forward_torch(self, x, a_scale=None, a_zero=None, x_is_packed=True, is_symmetric=None):

@@ -131,7 +131,7 @@ int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t
  *   split-K streaming kernel uses it (decode shapes whose N alone cannot fill the GPU): its first 4 KB
  *   are arrival counters that must be ZERO before the first launch and are left zero by every launch;
  *   launches that share a workspace must not overlap on the GPU.  With AUTO and no (or too small a)
- *   workspace the plain streaming kernel runs instead.  Split-K adds the per-split binary32 chains in
+ *   workspace the plain streaming kernel (or, for large batches, the converting tcgen05 kernel) runs instead.  Split-K adds the per-split binary32 chains in
  *   split order, so with group scales its outputs can differ from the single chain in the last bit
  *   (<= 1e-3 relative); without group scales the partial sums are int32 and the result is identical.
  *   The int8-operand kernels (TCGEN05_I8, TCGEN05_I8_PAIR; a_group = b_group = K only) write the expanded
@@ -147,6 +147,21 @@ int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_s
                              size_t workspace_bytes, void *stream);
 
 size_t flh_b200_gemm_workspace_bytes(long M, long N, long K, long a_group, long b_group, int algo);
+
+/* Weights expanded once, ahead of time, for large-batch (prefill) GEMMs with per-token / per-channel scales.
+ * flh_b200_expand_i4 turns packed int4 [rows, K/2] into int8 [rows, K] holding 16 * q (for unsigned codes:
+ * 16 * code as uint8), in the element order the int8-operand kernels use (per 32 elements: the 16 even ones,
+ * then the 16 odd ones); out is 128-byte aligned.  flh_b200_gemm_i8w_dequant is flh_b200_gemm_i4_dequant with
+ * a_group = b_group = K whose weight operand is that expanded copy: only the activations are expanded per call,
+ * into `workspace` (>= M * K bytes, 256-byte aligned, no initial contents; launches sharing it must not overlap).
+ * Results are bit-identical to flh_b200_gemm_i4_dequant.  Neither has a counterpart in the reference, which
+ * keeps int4 weights only: an engine with HBM to spare keeps both copies, the packed one for decode (where the
+ * weight bytes are the cost) and this one for prefill (where the tensor cores are). */
+int flh_b200_expand_i4(const uint8_t *packed, long rows, long K, uint8_t *out, void *stream);
+int flh_b200_gemm_i8w_dequant(const uint8_t *A, const uint8_t *B8, const void *a_scale, const void *a_zero,
+                              const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D,
+                              long M, long N, long K, int out_dtype, void *workspace,
+                              size_t workspace_bytes, void *stream);
 
 /* Which algorithm FLH_B200_GEMM_AUTO resolves to for this shape (one of FLH_B200_GEMM_*). */
 int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group);

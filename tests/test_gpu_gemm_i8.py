@@ -75,3 +75,43 @@ def test_i8_prefill_size_against_converting_kernel(cuda, algo):
     rows = [0, 127, 128, 255, 256, 1000, 2047]
     ref = O.gemm_i4_dequant(ap[rows], bp, sa[rows], sb, a_zero=za[rows], bias=bi)
     assert np.array_equal(d1[rows].cpu().numpy().view(np.uint16), ref.view(np.uint16))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 256, 128), (300, 512, 1024), (515, 384, 2048), (2048, 4096, 4096)])
+def test_i8_prepacked_weights(cuda, m, n, k):
+    """Weights expanded once (expand_i4), activations per call: same bits as the general entry point."""
+    for asym in (True, False):
+        ap, bp, sa, sb, za, bi = make_case(300 + m, m, n, k, 0, 0, asym, bias=True)
+        A, B, SA, SB, BI = _dev(ap), _dev(bp), _dev(sa), _dev(sb), _dev(bi)
+        ZA = _dev(za) if asym else None
+        rsum = cuda.weight_rowsum(B, k) if asym else None
+        B8 = cuda.expand_i4(B)
+        # the expansion itself: every 32 elements, the 16 even ones then the 16 odd ones, each 16 * q as a byte
+        q = (O.unpack_i4(bp, True).astype(np.int32) * 16).astype(np.uint8).reshape(n, k // 32, 16, 2)
+        want = np.concatenate([q[..., 0], q[..., 1]], axis=-1).reshape(n, k)
+        assert np.array_equal(B8.cpu().numpy(), want)
+        d1 = cuda.gemm_i8w_dequant(A, B8, SA, SB, A_zero=ZA, B_rowsum=rsum, bias=BI)
+        d2 = cuda.gemm_i4_dequant(A, B, SA, SB, A_zero=ZA, B_rowsum=rsum, bias=BI, algo=TC)
+        assert torch.equal(d1.view(torch.int16), d2.view(torch.int16))
+        if m <= 515:
+            ref = O.gemm_i4_dequant(ap, bp, sa, sb, a_zero=za, bias=bi)
+            assert np.array_equal(d1.cpu().numpy().view(np.uint16), ref.view(np.uint16))
+
+
+def test_i8_auto_selection_and_module(cuda):
+    from flh_b200 import _lib
+    from flh_b200.nn import LinearFLH
+    lib = _lib.load()
+    assert lib.flh_b200_gemm_pick_algo(2048, 4096, 4096, 4096, 4096) == I8_PAIR
+    assert lib.flh_b200_gemm_pick_algo(2048, 384, 4096, 4096, 4096) == I8
+    assert lib.flh_b200_gemm_pick_algo(512, 4096, 4096, 4096, 4096) == TC
+    assert lib.flh_b200_gemm_pick_algo(2048, 4096, 4096, 128, 128) == TC
+    assert lib.flh_b200_gemm_workspace_bytes(2048, 4096, 4096, 4096, 4096, 0) == (2048 + 4096) * 4096
+    # a module with and without the int8 copy gives the same output
+    m, k, n = 1100, 1024, 768
+    ap, bp, sa, sb, za, _ = make_case(400, m, n, k, 0, 0, True)
+    lin = LinearFLH(k, n, device="cuda", group_size=-1)
+    lin.w_packed.copy_(_dev(bp).reshape(-1)); lin.w_scale.copy_(_dev(sb))
+    y0 = lin(_dev(ap), _dev(sa), _dev(za))
+    y1 = lin.prepack_int8()(_dev(ap), _dev(sa), _dev(za))
+    assert lin._w_i8 is not None and torch.equal(y0.view(torch.int16), y1.view(torch.int16))
