@@ -8,6 +8,7 @@
 // order so that every binary16 rounding happens where the reference kernel has it
 // (flh/kernels/had_and_quant.cu:13-56).  Each thread keeps U independent 16-byte loads in flight.
 #include "common.cuh"
+#include <stdlib.h>
 
 namespace flh {
 
@@ -55,6 +56,42 @@ __device__ __forceinline__ void fht_regs(__half2 (&h)[4], int lane_in_group) {
     }
 }
 
+// scale = __hdiv(max, 7) with a correctly rounded reciprocal (cuda_fp16.hpp __hdiv, device branch:
+// reciprocal, multiply, round, one correction for tiny results); at most half(1e-6) -> 1.
+__device__ __forceinline__ __half group_scale(__half m) {
+    const float fm = __half2float(m);
+    const float rcp7 = 1.0f / 7.0f;
+    float fv = __fmul_rn(rcp7, fm);
+    __half sh = __float2half_rn(fv);
+    const unsigned short a = __half_as_ushort(sh) & 0x7fffu;
+    if (a != 0 && a < 0x008Fu) {
+        const float err = __fmaf_rn(-7.0f, fv, fm);
+        fv = __fmaf_rn(rcp7, err, fv);
+        sh = __float2half_rn(fv);
+    }
+    if (__half2float(sh) <= __half2float(__float2half_rn(1e-6f))) sh = __float2half_rn(1.0f);
+    return sh;
+}
+
+// q = rint(half(x * rcp)) for the four half2 of eight consecutive elements -> eight packed nibbles.
+// |x| <= max and scale = half(max / 7) keep |q| <= 7 for finite input, so the reference's clamp never acts.
+// Adding 1032 (= 1024 + 8) in binary16 rounds to the nearest integer, ties to even, and leaves q + 8 in the
+// low four bits of each half.
+__device__ __forceinline__ uint32_t quant_pack8(const __half2 (&h)[4], float rcp) {
+    const __half2 magic = __float2half2_rn(1032.0f);
+    uint32_t nib[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        const __half2 t = __floats2half2_rn(__fmul_rn(f.x, rcp), __fmul_rn(f.y, rcp));
+        nib[j] = (h22u(__hadd2(t, magic)) & 0x000F000Fu) ^ 0x00080008u;   // two's-complement nibbles at bits 0-3, 16-19
+    }
+    // nib[j] = [even code, 0, odd code, 0] as bytes; gather evens and odds, then byte j = even | odd << 4
+    const uint32_t a01 = nib[1] * 256u + nib[0], a23 = nib[3] * 256u + nib[2];
+    const uint32_t ev = __byte_perm(a01, a23, 0x5410), od = __byte_perm(a01, a23, 0x7632);
+    return od * 16u + ev;
+}
+
 template <int LOG_GS, bool HADAMARD>
 __global__ void __launch_bounds__(kThreads)
 quant_group_sym_kernel(const uint4 *__restrict__ x, uint32_t *__restrict__ q,
@@ -88,42 +125,109 @@ quant_group_sym_kernel(const uint4 *__restrict__ x, uint32_t *__restrict__ q,
                 const unsigned short o = __shfl_xor_sync(0xffffffffu, __half_as_ushort(m), s);
                 m = __hmax(m, __ushort_as_half(o));
             }
-            // scale = __hdiv(max, 7) with a correctly rounded reciprocal (cuda_fp16.hpp __hdiv,
-            // device branch: reciprocal, multiply, round, one correction for tiny results)
-            const float fm = __half2float(m);
-            const float rcp7 = 1.0f / 7.0f;
-            float fv = __fmul_rn(rcp7, fm);
-            __half sh = __float2half_rn(fv);
-            {
-                const unsigned short a = __half_as_ushort(sh) & 0x7fffu;
-                if (a != 0 && a < 0x008Fu) {
-                    const float err = __fmaf_rn(-7.0f, fv, fm);
-                    fv = __fmaf_rn(rcp7, err, fv);
-                    sh = __float2half_rn(fv);
-                }
-            }
-            if (__half2float(sh) <= __half2float(__float2half_rn(1e-6f))) sh = __float2half_rn(1.0f);
+            const __half sh = group_scale(m);
             const float rcp = __frcp_rn(__half2float(sh));
 
-            // q = rint(half(x * rcp)): |x| <= max and scale = half(max / 7) keep |q| <= 7 for finite input, so
-            // the reference's clamp never acts.  Adding 1032 (= 1024 + 8) in binary16 rounds to the nearest
-            // integer, ties to even, and leaves q + 8 in the low four bits of each half.
-            const __half2 magic = __float2half2_rn(1032.0f);
-            uint32_t nib[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __half22float2(h[j]);
-                const __half2 t = __floats2half2_rn(__fmul_rn(f.x, rcp), __fmul_rn(f.y, rcp));
-                nib[j] = (h22u(__hadd2(t, magic)) & 0x000F000Fu) ^ 0x00080008u;   // two's-complement nibbles at bits 0-3, 16-19
-            }
-            // nib[j] = [even code, 0, odd code, 0] as bytes; gather evens and odds, then byte j = even | odd << 4
-            const uint32_t a01 = nib[1] * 256u + nib[0], a23 = nib[3] * 256u + nib[2];
-            const uint32_t ev = __byte_perm(a01, a23, 0x5410), od = __byte_perm(a01, a23, 0x7632);
-            const uint32_t packed = od * 16u + ev;
+            const uint32_t packed = quant_pack8(h, rcp);
             if (c < total_chunks) {
                 q[c] = packed;
                 if (lig == 0) scales[c / L] = sh;
             }
+        }
+    }
+}
+
+
+// ---- one thread per group of 128 -------------------------------------------------------------------
+// For large inputs: a lane owns a whole group (64 half2 registers), so all seven butterfly bits run in
+// registers with no shuffle, and the scale is derived once per group instead of once per 8 elements.  A warp
+// works on 32 consecutive groups (8 KB): they are staged in shared memory by coalesced 16-byte cp.async
+// (chunk c of 128-byte line L lands at chunk c ^ ((L >> 1) & 7), so that a lane reading its own two lines is
+// conflict-free) and the next tile of the persistent warp is in flight while this one is computed.
+constexpr int kTWarps = 4;             // warps per CTA
+constexpr int kTTile = 32 * 256;       // bytes of one warp tile
+
+__device__ __forceinline__ void stage_groups(const uint8_t *x, long tile, long total_chunks, uint32_t stage, int lane) {
+    const long c0 = tile * 512 + lane;                      // 16-byte chunk index of this lane's first copy
+    const int cx = (lane & 7) ^ (lane >> 4);
+    const uint32_t base = stage + ((lane >> 3) << 7);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const long c = c0 + i * 32;
+        const uint32_t dst = base + i * 512 + ((cx ^ ((2 * i) & 7)) << 4);
+        const int n = c < total_chunks ? 16 : 0;            // past the end: zero fill, nothing is read
+        const uint8_t *src = x + (c < total_chunks ? c : 0) * 16;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n));
+    }
+    asm volatile("cp.async.commit_group;" ::);
+}
+
+template <bool HADAMARD>
+__global__ void __launch_bounds__(kTWarps * 32, 4)
+quant_group128_thread_kernel(const uint8_t *__restrict__ x, uint4 *__restrict__ q, __half *__restrict__ scales, long groups) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint8_t *my = smem_raw + warp * kTTile;
+    const uint32_t stage = smem_u32(my);
+    const long tiles = (groups + 31) >> 5, total_chunks = groups * 16;
+    const long nwarps = (long)gridDim.x * kTWarps;
+    long tile = (long)blockIdx.x * kTWarps + warp;
+    if (tile < tiles) stage_groups(x, tile, total_chunks, stage, lane);
+
+    for (; tile < tiles; tile += nwarps) {
+        __half2 h[64];
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        {
+            const uint8_t *mine = my + lane * 256;
+            const int tx = lane & 7;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 w = *reinterpret_cast<const uint4 *>(mine + j * 128 + ((c ^ tx) << 4));
+                    h[j * 32 + c * 4 + 0] = u2h2(w.x); h[j * 32 + c * 4 + 1] = u2h2(w.y);
+                    h[j * 32 + c * 4 + 2] = u2h2(w.z); h[j * 32 + c * 4 + 3] = u2h2(w.w);
+                }
+            }
+        }
+        __syncwarp();                                   // the tile is in registers everywhere: refill the buffer
+        if (tile + nwarps < tiles) stage_groups(x, tile + nwarps, total_chunks, stage, lane);
+
+        if (HADAMARD) {
+#pragma unroll
+            for (int r = 0; r < 64; ++r) h[r] = bfly_inner(h[r]);                 // bit 0
+#pragma unroll
+            for (int d = 1; d < 64; d <<= 1) {                                    // bits 1-6
+#pragma unroll
+                for (int r = 0; r < 64; ++r) {
+                    if ((r & d) == 0) {
+                        const __half2 a = h[r], b = h[r + d];
+                        h[r] = __hadd2(a, b);
+                        h[r + d] = __hsub2(a, b);
+                    }
+                }
+            }
+        }
+        __half2 m2 = __habs2(h[0]);
+#pragma unroll
+        for (int r = 1; r < 64; ++r) m2 = __hmax2(m2, __habs2(h[r]));
+        const __half m = __hmax(__low2half(m2), __high2half(m2));
+        const __half sh = group_scale(m);
+        const float rcp = __frcp_rn(__half2float(sh));
+        const long g = tile * 32 + lane;
+        if (g < groups) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                uint32_t o[4];
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const __half2 hh[4] = {h[16 * v + 4 * w], h[16 * v + 4 * w + 1], h[16 * v + 4 * w + 2], h[16 * v + 4 * w + 3]};
+                    o[w] = quant_pack8(hh, rcp);
+                }
+                q[g * 4 + v] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            scales[g] = sh;
         }
     }
 }
@@ -178,9 +282,32 @@ int grid_for(K kernel, long total_chunks) {
 
 }  // namespace
 
+// Groups from which the thread-per-group kernel is used (it measured faster from a few thousand groups on; below
+// that the 16-lanes-per-group kernel spreads a small input over more warps).  FLH_B200_GROUP_THREAD_MIN_ROWS
+// overrides it (tuning aid).
+static long group_thread_min_rows() {
+    static long v = -1;
+    if (v < 0) {
+        const char *e = getenv("FLH_B200_GROUP_THREAD_MIN_ROWS");
+        v = e ? atol(e) : 4096;
+        if (v < 0) v = 0;
+    }
+    return v;
+}
+
 int launch_quant_group_sym(const void *x, long rows, int gs, int hadamard, uint8_t *q,
                            void *scales, cudaStream_t stream) {
     const long chunks = rows * (gs / 8);
+    // many groups of 128: the thread-per-group kernel (a full wave of its persistent warps has 32 groups each)
+    if (gs == 128 && rows >= group_thread_min_rows()) {
+        auto kern = hadamard ? quant_group128_thread_kernel<true> : quant_group128_thread_kernel<false>;
+        const long tiles = (rows + 31) / 32;
+        long grid = (tiles + kTWarps - 1) / kTWarps;
+        if (grid > 4L * kNumSMs) grid = 4L * kNumSMs;
+        kern<<<(unsigned)grid, kTWarps * 32, kTWarps * kTTile, stream>>>(static_cast<const uint8_t *>(x), reinterpret_cast<uint4 *>(q),
+                                                                       static_cast<__half *>(scales), rows);
+        return cuda_status(cudaGetLastError(), "quant_group128_thread launch");
+    }
     const uint4 *xi = static_cast<const uint4 *>(x);
     uint32_t *qo = reinterpret_cast<uint32_t *>(q);
     __half *so = static_cast<__half *>(scales);

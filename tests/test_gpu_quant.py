@@ -25,6 +25,19 @@ def test_group_sym_bit_exact(cuda, gs, had, rows):
     assert np.array_equal(q.cpu().numpy(), qo)
 
 
+@pytest.mark.parametrize("had", [True, False])
+@pytest.mark.parametrize("rows", [4096, 20001, 200003])
+def test_group_sym_many_groups(cuda, had, rows):
+    """Large inputs run the thread-per-group kernel (persistent warps, 32 groups per tile, ragged last tile)."""
+    x = activations(900 + rows % 97, rows // 32 + 1, 128 * 32).reshape(-1, 128)[:rows]
+    x = np.ascontiguousarray(x)
+    f = cuda.hadamard_and_quantize_i4 if had else cuda.quant_and_pack_i4
+    q, s = f(_dev(x))
+    qo, so = O.quant_group_sym(x, had)
+    assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16))
+    assert np.array_equal(q.cpu().numpy(), qo)
+
+
 def test_group_sym_edge_values(cuda):
     # all-zero groups (scale -> 1), tiny groups (scale in the subnormal correction range),
     # a saturating group, negative zero
