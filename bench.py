@@ -184,7 +184,7 @@ def run_ours(args, world, rank, local, dist):
            "vs_baseline": None, "data": "synthetic", "impl": "ours"}
 
     if args.workload == "had_quant":
-        M, K = 16384, 4096
+        M, K = args.rows, args.k
         xs = [synth_activations(M, K, 100 + i + 10 * rank, device) for i in range(3)]   # 3 x 134 MB > L2
         step_bytes = M * (2 * K + K // 2 + 4)
 
@@ -196,18 +196,19 @@ def run_ours(args, world, rank, local, dist):
         value = world * step_bytes * steps / t / 1e9
         out.update(metric="had_quant_GBps", unit="GB/s", value=value, ms_per_step=t / steps * 1e3, dtype="f32",
                    config={"workload": "fused full-width Hadamard (binary32) + per-token asymmetric int4 quant + pack, "
-                                       "f16 X[16384,4096] per GPU, 0.1% outlier channels x20",
+                                       f"f16 X[{M},{K}] per GPU, 0.1% outlier channels x20",
                            "M_per_gpu": M, "K": K, "bytes_per_step_per_gpu": step_bytes,
-                           "l2": "three rotating 134 MB inputs, each larger than the 126 MB L2",
+                           "l2": f"three rotating {M * K * 2 // 1000000} MB inputs" + (", each larger than the 126 MB L2" if M * K * 2 > L2_BYTES else ""),
                            "parallelism": f"token-sharded x{world}, no collective"},
                    clocks=cs.summary(), gpu_launches=steps)
         ach = step_bytes * steps / t / 1e9
-        out["roofline"] = {"kernel": "quant_token_asym_kernel<6,0,false,true>", "bound": "hbm", "achieved": ach,
+        headline = (M, K) == (16384, 4096)
+        out["roofline"] = {"kernel": "quant_token_warp_kernel<false>" if K == 4096 and M >= 512 else "quant_token_asym_kernel", "bound": "hbm", "achieved": ach,
                            "peak": peaks["hbm_gbs"], "peak_src": peaks["src"], "unit": "GB/s",
                            "frac": ach / peaks["hbm_gbs"],
                            # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
-                           # summarised in profiles/quant_token_asym_M16384_K4096.md (134.3 MB + 17.9 MB)
-                           "traffic": 152.2e6, "traffic_unit": "bytes/launch (ncu)", "algorithmic_bytes": step_bytes}
+                           # summarised in profiles/quant_token_asym_M16384_K4096.md (134.3 MB + 17.4 MB)
+                           "traffic": 151.8e6 if headline else None, "traffic_unit": "bytes/launch (ncu)", "algorithmic_bytes": step_bytes}
         # ---- end to end through the public API with host buffers ----
         xh = [x.cpu().pin_memory() for x in xs[:2]]
         qh = torch.empty((M, K // 2), dtype=torch.uint8).pin_memory()
@@ -472,6 +473,8 @@ def main():
     ap.add_argument("--workload", default="had_quant")
     ap.add_argument("--act-mode", default="group_sym", choices=["group_sym", "token_asym"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count of the llama workloads")
+    ap.add_argument("--rows", type=int, default=16384, help="had_quant: token rows per GPU (default: the headline 16384)")
+    ap.add_argument("--k", type=int, default=4096, help="had_quant: hidden size K (default: the headline 4096)")
     ap.add_argument("--prepack", action="store_true",
                     help="gemm_prefill / llama*_prefill with token_asym: keep an int8 copy of the weights (expanded once, outside the timed region)")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline (profiling runs)")

@@ -229,12 +229,13 @@ def gemm_i4_dequant(A, B, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=Non
     with torch.cuda.device(A.device):
         stream = _stream(A)
         need = lib.flh_b200_gemm_workspace_bytes(M, N, K, ag, bg, algo)
+        resolved = algo if algo != GEMM_AUTO else lib.flh_b200_gemm_pick_algo(M, N, K, ag, bg)
         if not need:
             ws = None
-        elif M <= 64:
-            ws = _workspace(A.device, stream, need)
+        elif resolved in (GEMM_TCGEN05_I8, GEMM_TCGEN05_I8_PAIR):
+            ws = _scratch(A.device, stream, need)          # expanded operands: any contents
         else:
-            ws = _scratch(A.device, stream, need)
+            ws = _workspace(A.device, stream, need)        # split-K: zeroed counters, left zeroed
         _lib.check(lib.flh_b200_gemm_i4_dequant(
             _ptr(A), _ptr(B), _ptr(A_scale), _ptr(A_zero), _ptr(B_scale), _ptr(B_rowsum), _ptr(bias), _ptr(D),
             M, N, K, ag, bg, BF16 if D.dtype == torch.bfloat16 else F16, algo, _ptr(ws), ws.numel() if ws is not None else 0,

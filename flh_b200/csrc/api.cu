@@ -51,6 +51,8 @@ int launch_gemm_i8(const uint8_t *, const uint8_t *, const uint8_t *, const void
                    const int32_t *, const void *, void *, long, long, long, int, int, void *, cudaStream_t);
 int launch_expand_i4(const uint8_t *, long, long, uint8_t *, cudaStream_t);
 int gemm_i8_status(int *);
+int quant_token_factor_status(int *);
+int quant_token_factor_status_clear();
 int gemm_i8_wait_profile(unsigned long long *);
 int gemm_i8_status_clear();
 
@@ -295,7 +297,10 @@ int flh_b200_gemm_status(int *out) {
     if (out[0]) return gemm_tcgen05_status_clear();
     rc = gemm_i8_status(out);
     if (rc) return rc;
-    return out[0] ? gemm_i8_status_clear() : 0;
+    if (out[0]) return gemm_i8_status_clear();
+    rc = quant_token_factor_status(out);
+    if (rc) return rc;
+    return out[0] ? quant_token_factor_status_clear() : 0;
 }
 
 int flh_b200_gemm_wait_profile(unsigned long long *out) {

@@ -482,6 +482,9 @@ int launch_one(const TokenParams &p, long M, cudaStream_t stream) {
 int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld, float clip, uint8_t *q,
                             void *scale, void *zero, cudaStream_t stream);
 
+int launch_quant_token_factor(const void *x, int in_dtype, long M, long K, long ld, int kfac, const void *sign_mat_bf16,
+                              float clip, uint8_t *q, void *scale, void *zero, cudaStream_t stream);
+
 // Rows from which the warp-per-row kernel (K = 4096) is used; below it the 64-thread kernel spreads a
 // small batch over more SMs.  FLH_B200_TOKEN_WARP_MIN_M overrides it (tuning aid).
 static long token_warp_min_rows() {
@@ -499,6 +502,14 @@ int launch_quant_token_asym(const void *x, int in_dtype, long M, long K, long ld
                             void *scale, void *zero, cudaStream_t stream) {
     if (hadamard && kfac == 1 && K == 4096 && M >= token_warp_min_rows())
         return launch_quant_token_warp(x, in_dtype, M, K, ld, clip, q, scale, zero, stream);
+    if (hadamard == 1 && kfac >= 64 && K == (long)kfac * 64 && M >= 256) {
+        // K = kfac * 64 with a large factor (11008 = 172 * 64), prefill-size batches: butterflies + the factor on
+        // tcgen05, two rows per step of a persistent CTA (its set-up costs more than a decode-size batch)
+        const size_t bits_bytes = ((size_t)kfac * ((kfac + 31) / 32) * 4 + 15) / 16 * 16;
+        const int rc = launch_quant_token_factor(x, in_dtype, M, K, ld, kfac, reinterpret_cast<const uint8_t *>(sign_bits) + bits_bytes,
+                                                 clip, q, scale, zero, stream);
+        if (rc != -1000) return rc;
+    }
     TokenParams p;
     // factor table layout (flh_b200_pack_signs): bit rows, then (16-byte aligned) the bf16 matrix
     p.kp = (kfac + 15) / 16 * 16;

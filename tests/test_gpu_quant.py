@@ -103,7 +103,7 @@ def test_token_asym_hadamard_bit_exact(cuda, m, k):
     assert np.array_equal(q.cpu().numpy(), qo)
 
 
-@pytest.mark.parametrize("m,k", [(mk) for mk in TOKEN_SHAPES if mk[1] in FACTORED] + [(64, 11008), (33, 14336)])
+@pytest.mark.parametrize("m,k", [(mk) for mk in TOKEN_SHAPES if mk[1] in FACTORED] + [(64, 11008), (33, 14336), (1, 11008), (7, 11008), (301, 11008), (1001, 11008)])
 def test_token_asym_tensor_core_factor(cuda, m, k):
     """Default path for K = kfac * 2^m: the kfac x kfac factor on the tensor cores (exact bf16x3 split, binary32
     accumulation in another order than the oracle's).  Not the reference's order, so the bound is the stated
