@@ -214,12 +214,35 @@ def run_ours(args, world, rank, local, dist):
         qh = torch.empty((M, K // 2), dtype=torch.uint8).pin_memory()
         sh = torch.empty((M,), dtype=torch.float16).pin_memory()
         zh = torch.empty((M,), dtype=torch.float16).pin_memory()
-        xd = torch.empty((M, K), dtype=torch.float16, device=device)
+        # Three streams, two buffer sets: the upload of step i + 1 and the download of step i - 1 run beside the kernel of
+        # step i (PCIe is full duplex).  Every step still uploads its own input and downloads its own codes, scales and
+        # zero-points; the timed region ends when the last download has landed (the main stream waits for it).
+        main = torch.cuda.current_stream()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        xd = [torch.empty((M, K), dtype=torch.float16, device=device) for _ in range(2)]
+        qd = [torch.empty((M, K // 2), dtype=torch.uint8, device=device) for _ in range(2)]
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_used = [torch.cuda.Event() for _ in range(2)]       # the kernel has consumed xd[b]
+        ev_out = [torch.cuda.Event() for _ in range(2)]        # the results of buffer set b are on the host
+        outs = [None, None]
 
         def e2e(i):
-            xd.copy_(xh[i % 2], non_blocking=True)
-            q, s, z = C.quant_token_asym_i4(xd, hadamard=True)
-            qh.copy_(q, non_blocking=True); sh.copy_(s, non_blocking=True); zh.copy_(z, non_blocking=True)
+            b = i % 2
+            s_in.wait_event(ev_used[b])                        # (first use: an unrecorded event does not block)
+            with torch.cuda.stream(s_in):
+                xd[b].copy_(xh[b], non_blocking=True)
+                ev_in[b].record(s_in)
+            main.wait_event(ev_in[b])
+            main.wait_event(ev_out[b])                         # the previous results of this set have left the device
+            q, s_, z = C.quant_token_asym_i4(xd[b], hadamard=True)
+            outs[b] = (q, s_, z)                               # keep the device tensors alive until they are copied
+            ev_used[b].record(main)
+            s_out.wait_event(ev_used[b])
+            with torch.cuda.stream(s_out):
+                qh.copy_(q, non_blocking=True); sh.copy_(s_, non_blocking=True); zh.copy_(z, non_blocking=True)
+                ev_out[b].record(s_out)
+            if i == steps - 1 or i < 3:                        # last timed step (and the warm-up): join the downloads
+                main.wait_event(ev_out[b])
 
         te = timed_loop(e2e, steps, 3, dist, device)
         out["e2e"] = {"value": world * step_bytes * steps / te / 1e9, "unit": "GB/s",
