@@ -500,7 +500,7 @@ static long token_warp_min_rows() {
 int launch_quant_token_asym(const void *x, int in_dtype, long M, long K, long ld, int hadamard,
                             int kfac, const uint32_t *sign_bits, float clip, uint8_t *q,
                             void *scale, void *zero, cudaStream_t stream) {
-    if (hadamard && kfac == 1 && K == 4096 && M >= token_warp_min_rows())
+    if (hadamard && kfac == 1 && (K == 4096 || K == 8192) && M >= token_warp_min_rows())
         return launch_quant_token_warp(x, in_dtype, M, K, ld, clip, q, scale, zero, stream);
     if (hadamard == 1 && kfac >= 64 && K == (long)kfac * 64 && M >= 256) {
         // K = kfac * 64 with a large factor (11008 = 172 * 64), prefill-size batches: butterflies + the factor on
@@ -515,7 +515,11 @@ int launch_quant_token_asym(const void *x, int in_dtype, long M, long K, long ld
     p.kp = (kfac + 15) / 16 * 16;
     // the tensor-core factor stage pays off for the large orders (108 ... 172); the small ones (12 ... 60) are
     // cheaper summed directly, which is also the oracle's order
-    p.factor_exact = hadamard == 2 || kfac < 64;
+    {
+        static int min_kfac = -1;
+        if (min_kfac < 0) { const char *e = getenv("FLH_B200_FACTOR_TC_MIN_KFAC"); min_kfac = e ? atoi(e) : 64; }
+        p.factor_exact = hadamard == 2 || kfac < min_kfac;
+    }
     {
         const size_t bits_bytes = ((size_t)kfac * ((kfac + 31) / 32) * 4 + 15) / 16 * 16;
         p.sign_mat = reinterpret_cast<const __nv_bfloat16 *>(reinterpret_cast<const uint8_t *>(sign_bits) + bits_bytes);

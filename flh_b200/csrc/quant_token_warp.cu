@@ -1,5 +1,8 @@
-// Per-token quantiser for K = 4096 with one WARP per token row (full-width binary32 Hadamard in
-// matmul_hadU's order + asymmetric int4 + nibble packing), the shape of a Llama-7B hidden state.
+// Per-token quantiser for K = 4096 with one WARP per token row, and K = 8192 with two (full-width binary32
+// Hadamard in matmul_hadU's order + asymmetric int4 + nibble packing): the hidden states of Llama-7B / 70B.
+// Described for K = 4096; with two warps a lane still owns 128 values, the second pass runs bits 7-12 over
+// 2-wide columns (64-bit shared loads), the warps of a row meet at named barriers, and a lane stores one
+// byte (two codes) per m.
 //
 // Every lane owns 128 values in registers, as 64 packed binary32 pairs:
 //   pass 1  the row is staged in shared memory by coalesced 16-byte cp.async (the NEXT row of the
@@ -18,7 +21,7 @@
 namespace flh {
 namespace {
 
-constexpr int kRowK = 4096;
+constexpr int kRowK = 4096;                             // values per warp of a row
 static_assert(kRowK * 2 <= 32 * 132 * 4, "the staged row must fit the transpose buffer");
 constexpr int kChunkWords = 132;                        // 128 values of a lane + 4 words of padding
 constexpr int kXposeBytes = 32 * kChunkWords * 4;
@@ -52,41 +55,50 @@ __device__ __forceinline__ void bfly_pairs(uint64_t (&p)[64]) {
     }
 }
 
-// issue the sixteen 16-byte copies of this lane for one row; chunk c of 128-byte line L lands at
-// chunk c ^ ((L >> 1) & 7) of that line, which makes the reads of pass 1 conflict-free
-__device__ __forceinline__ void stage_row(const WarpParams &p, long row, uint32_t stage, int lane) {
-    const uint8_t *src = p.x + row * p.ld_bytes + lane * 16;
-    const int c0 = (lane & 7) ^ (lane >> 4);
-    const uint32_t base = stage + ((lane >> 3) << 7);
+// issue the sixteen 16-byte copies of this lane for one row of W warps (t = lane index inside the row, 0 .. 32 W - 1);
+// chunk c of 128-byte line L lands at chunk c ^ ((L >> 1) & 7) of that line, which makes the reads of pass 1 conflict-free
+template <int W>
+__device__ __forceinline__ void stage_row(const WarpParams &p, long row, uint32_t stage, int t) {
+    const uint8_t *src = p.x + row * p.ld_bytes + t * 16;
+    // copy i covers chunks i * 32 W + t: line = i * 4 W + (t >> 3), (line >> 1) & 7 = (i * 2 W + (t >> 4)) & 7
+    const int c0 = (t & 7) ^ (t >> 4);
+    const uint32_t base = stage + ((t >> 3) << 7);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        const uint32_t dst = base + i * 512 + ((c0 ^ ((2 * i) & 7)) << 4);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + i * 512));
+        const uint32_t dst = base + i * 512 * W + ((c0 ^ ((2 * W * i) & 7)) << 4);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + i * 512 * W));
     }
     asm volatile("cp.async.commit_group;" ::);
 }
 
-template <bool BF16>
+template <bool BF16, int W>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, kCtasPerSm) quant_token_warp_kernel(const WarpParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    __shared__ float red[kWarpsPerCta][2];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    uint8_t *my = smem_raw + warp * kWarpBytes;
+    const int grp = warp / W;                               // row slot of this warp inside the CTA
+    const int t = (warp % W) * 32 + lane;                   // lane index inside the row: 0 .. 32 W - 1
+    uint8_t *my = smem_raw + grp * (W * kWarpBytes);        // the row's buffer: 32 W chunks of 132 words
     const uint32_t stage = smem_u32(my);
     const uint32_t xp = stage;                              // transpose buffer (aliases the staged row)
+    auto row_sync = [&]() {                                 // the warps of this row
+        if (W == 1) __syncwarp();
+        else asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(32 * W) : "memory");
+    };
 
-    const long nwarps = (long)gridDim.x * kWarpsPerCta;
-    long row = (long)blockIdx.x * kWarpsPerCta + warp;
-    if (row < p.M) stage_row(p, row, stage, lane);
+    const long nwarps = (long)gridDim.x * (kWarpsPerCta / W);    // rows in flight
+    long row = (long)blockIdx.x * (kWarpsPerCta / W) + grp;
+    if (row < p.M) stage_row<W>(p, row, stage, t);
 
     for (; row < p.M; row += nwarps) {
         uint64_t v[64];
 
         // ---------------- pass 1: 128 consecutive inputs, bits 0-6 --------------------------------
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncwarp();
+        row_sync();
         {
-            const uint8_t *mine = my + lane * 256;
-            const int tx = lane & 7;
+            const uint8_t *mine = my + t * 256;
+            const int tx = t & 7;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
 #pragma unroll
@@ -116,33 +128,40 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kCtasPerSm) quant_token_war
                 }
             }
         }
-        __syncwarp();                                   // the staged row is in registers everywhere
+        row_sync();                                     // the staged row is in registers everywhere
         const bool more = row + nwarps < p.M;
         if (more) {                                     // next row: towards L2 now, into shared memory below
-            const uint8_t *nx = p.x + (row + nwarps) * p.ld_bytes + lane * 128;
+            const uint8_t *nx = p.x + (row + nwarps) * p.ld_bytes + t * 128;
             asm volatile("prefetch.global.L2 [%0];" ::"l"(nx));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + 4096));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + 4096 * W));
         }
         bfly_pairs<1>(v);                               // bits 1-6
 
-        // ---------------- transpose: lane's chunk out, 4-wide columns in --------------------------
+        // ---------------- transpose: lane's chunk out, 4-wide (W = 2: 2-wide) columns in ---------------
         {
-            const uint32_t out = xp + lane * (kChunkWords * 4);
+            const uint32_t out = xp + t * (kChunkWords * 4);
 #pragma unroll
             for (int k = 0; k < 64; k += 2)
                 asm volatile("st.shared.v2.u64 [%0], {%1, %2};" ::"r"(out + 8 * k), "l"(v[k]), "l"(v[k + 1]) : "memory");
         }
-        __syncwarp();
-        // pair index k = 2 m + h: elements m * 128 + 4 lane + 2 h + {0, 1}
-        {
-            const uint32_t in = xp + lane * 16;
+        row_sync();
+        if (W == 1) {
+            // pair index k = 2 m + h: elements m * 128 + 4 lane + 2 h + {0, 1}
+            const uint32_t in = xp + t * 16;
 #pragma unroll
             for (int m = 0; m < 32; ++m)
                 asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v[2 * m]), "=l"(v[2 * m + 1]) : "r"(in + m * (kChunkWords * 4)) : "memory");
+        } else {
+            // pair index k = m (0..63): elements m * 128 + 2 t + {0, 1}
+            const uint32_t in = xp + t * 8;
+#pragma unroll
+            for (int m = 0; m < 64; ++m)
+                asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v[m]) : "r"(in + m * (kChunkWords * 4)) : "memory");
         }
-        __syncwarp();                                   // the buffer is free again: stage the next row into it
-        if (more) stage_row(p, row + nwarps, stage, lane);
-        bfly_pairs<2>(v);                               // bits 7-11 (over m)
+        row_sync();                                     // the buffer is free again: stage the next row into it
+        if (more) stage_row<W>(p, row + nwarps, stage, t);
+        if (W == 1) bfly_pairs<2>(v);                   // bits 7-11 (over m, two pairs per m)
+        else bfly_pairs<1>(v);                          // bits 7-12 (over m, one pair per m)
 
         // ---------------- row min / max, parameters ------------------------------------------------
         float vmin = 0.0f, vmax = 0.0f;
@@ -155,8 +174,15 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kCtasPerSm) quant_token_war
         }
         vmin = warp_min(vmin);
         vmax = warp_max(vmax);
-        const TokenRowParams rp = token_row_params(vmin, vmax, p.clip, 64.0f);     // sqrt(4096)
-        if (lane == 0) { p.scale[row] = rp.scale; p.zero[row] = __float2half_rn(rp.zero); }
+        if (W > 1) {                                    // join the warps of the row
+            if (lane == 0) { red[warp][0] = vmin; red[warp][1] = vmax; }
+            row_sync();
+#pragma unroll
+            for (int o = 0; o < W; ++o) { vmin = fminf(vmin, red[grp * W + o][0]); vmax = fmaxf(vmax, red[grp * W + o][1]); }
+            // (the next write of red comes after three more row barriers)
+        }
+        const TokenRowParams rp = token_row_params(vmin, vmax, p.clip, W == 1 ? 64.0f : 90.50966799187809f);   // sqrt(4096 W)
+        if (t == 0) { p.scale[row] = rp.scale; p.zero[row] = __float2half_rn(rp.zero); }
 
         // ---------------- codes --------------------------------------------------------------------
         // v * rd, (clamped only when the row needs it), + 1.5 * 2^23 leaves rint(v rd) = code - zero in
@@ -176,30 +202,43 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kCtasPerSm) quant_token_war
             }
         }
         const uint64_t magic2 = pack2(12582912.0f, 12582912.0f);
-        const uint32_t zsum = 0x1111u * (uint32_t)(int)rp.zero;
-        uint16_t *qrow = reinterpret_cast<uint16_t *>(p.q + row * (long)(kRowK / 2)) + lane;
+        if (W == 1) {
+            const uint32_t zsum = 0x1111u * (uint32_t)(int)rp.zero;
+            uint16_t *qrow = reinterpret_cast<uint16_t *>(p.q + row * (long)(kRowK / 2)) + t;
 #pragma unroll
-        for (int m = 0; m < 32; ++m) {
-            float r0, r1, r2, r3;
-            unpack2(add2(v[2 * m], magic2), r0, r1);
-            unpack2(add2(v[2 * m + 1], magic2), r2, r3);
-            // Horner in 16: ((b3 16 + b2) 16 + b1) 16 + b0 + 0x1111 zero
-            uint32_t w = __float_as_uint(r3) * 16u + __float_as_uint(r2);
-            w = w * 16u + __float_as_uint(r1);
-            w = w * 16u + __float_as_uint(r0);
-            w += zsum;
-            qrow[m * 32] = (uint16_t)w;
+            for (int m = 0; m < 32; ++m) {
+                float r0, r1, r2, r3;
+                unpack2(add2(v[2 * m], magic2), r0, r1);
+                unpack2(add2(v[2 * m + 1], magic2), r2, r3);
+                // Horner in 16: ((b3 16 + b2) 16 + b1) 16 + b0 + 0x1111 zero
+                uint32_t w = __float_as_uint(r3) * 16u + __float_as_uint(r2);
+                w = w * 16u + __float_as_uint(r1);
+                w = w * 16u + __float_as_uint(r0);
+                w += zsum;
+                qrow[m * 32] = (uint16_t)w;
+            }
+        } else {
+            // two neighbouring codes per m: the low byte of b0 + 16 b1 + 0x11 zero
+            const uint32_t zsum = 0x11u * (uint32_t)(int)rp.zero;
+            uint8_t *qrow = p.q + row * (long)(kRowK * W / 2) + t;
+#pragma unroll
+            for (int m = 0; m < 64; ++m) {
+                float r0, r1;
+                unpack2(add2(v[m], magic2), r0, r1);
+                qrow[m * 64] = (uint8_t)(__float_as_uint(r1) * 16u + __float_as_uint(r0) + zsum);
+            }
         }
     }
 }
 
 }  // namespace
 
-// K = 4096 with the transform and no factor stage.  Returns -1000 when the shape is not one this kernel
+// K = 4096 or 8192 with the transform and no factor stage.  Returns -1000 when the shape is not one this kernel
 // takes (the caller then uses the general kernel).
 int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld, float clip, uint8_t *q,
                             void *scale, void *zero, cudaStream_t stream) {
-    if (K != kRowK) return -1000;
+    if (K != kRowK && K != 2 * kRowK) return -1000;
+    const int W = (int)(K / kRowK);
     WarpParams p;
     p.x = static_cast<const uint8_t *>(x);
     p.ld_bytes = ld * 2;
@@ -209,9 +248,10 @@ int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld
     p.scale = static_cast<__half *>(scale);
     p.zero = static_cast<__half *>(zero);
     const size_t smem = (size_t)kWarpsPerCta * kWarpBytes;
-    auto kern = in_dtype == FLH_B200_BF16 ? quant_token_warp_kernel<true> : quant_token_warp_kernel<false>;
-    static bool attr_done[2][64] = {};
-    const int which = in_dtype == FLH_B200_BF16;
+    auto kern = W == 1 ? (in_dtype == FLH_B200_BF16 ? quant_token_warp_kernel<true, 1> : quant_token_warp_kernel<false, 1>)
+                       : (in_dtype == FLH_B200_BF16 ? quant_token_warp_kernel<true, 2> : quant_token_warp_kernel<false, 2>);
+    static bool attr_done[4][64] = {};
+    const int which = (in_dtype == FLH_B200_BF16) + 2 * (W - 1);
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
     if (dev < 0 || !attr_done[which][dev]) {         // the attribute is per device
@@ -219,7 +259,8 @@ int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld
         if (e != cudaSuccess) return cuda_status(e, "quant_token_warp smem attribute");
         if (dev >= 0) attr_done[which][dev] = true;
     }
-    long grid = (M + kWarpsPerCta - 1) / kWarpsPerCta;
+    const int rows_per_cta = kWarpsPerCta / W;
+    long grid = (M + rows_per_cta - 1) / rows_per_cta;
     if (grid > (long)kCtasPerSm * kNumSMs) grid = (long)kCtasPerSm * kNumSMs;
     kern<<<(unsigned)grid, kWarpsPerCta * 32, smem, stream>>>(p);
     return cuda_status(cudaGetLastError(), "quant_token_warp launch");

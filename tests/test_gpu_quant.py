@@ -149,12 +149,12 @@ def test_token_asym_bf16_strided_and_edges(cuda):
     assert np.array_equal(q.cpu().numpy(), qo)
 
 
-@pytest.mark.parametrize("m", [1024, 1189, 4100])
+@pytest.mark.parametrize("m,k", [(1024, 4096), (1189, 4096), (4100, 4096), (512, 8192), (1777, 8192)])
 @pytest.mark.parametrize("bf16", [False, True])
-def test_token_asym_k4096_large_batches(cuda, m, bf16):
-    """K = 4096 with many rows runs the one-warp-per-row kernel (persistent warps, next row prefetched): every row
-    bit-equal to the oracle, with edge rows, a padded row stride, and a clip ratio that forces clamping."""
-    k = 4096
+def test_token_asym_k4096_large_batches(cuda, m, k, bf16):
+    """K = 4096 / 8192 with many rows run the warp-per-row kernel (one / two warps per row, persistent, next row
+    prefetched): every row bit-equal to the oracle, with edge rows, a padded row stride, and a clip ratio that forces
+    clamping."""
     xf = activations(3700 + m, m, k).astype(np.float32)
     xf[1] = 0.0
     xf[2] = np.abs(xf[2])
