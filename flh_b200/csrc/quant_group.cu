@@ -138,23 +138,31 @@ quant_group_sym_kernel(const uint4 *__restrict__ x, uint32_t *__restrict__ q,
 }
 
 
-// ---- one thread per group of 128 -------------------------------------------------------------------
-// For large inputs: a lane owns a whole group (64 half2 registers), so all seven butterfly bits run in
-// registers with no shuffle, and the scale is derived once per group instead of once per 8 elements.  A warp
-// works on 32 consecutive groups (8 KB): they are staged in shared memory by coalesced 16-byte cp.async
-// (chunk c of 128-byte line L lands at chunk c ^ ((L >> 1) & 7), so that a lane reading its own two lines is
-// conflict-free) and the next tile of the persistent warp is in flight while this one is computed.
+// ---- one thread per group ------------------------------------------------------------------------------
+// For large inputs: a lane owns a whole group (GS / 2 half2 registers), so all butterfly bits run in registers with
+// no shuffle, and the scale is derived once per group instead of once per 8 elements.  A warp works on 32
+// consecutive groups (64 GS bytes): they are staged in shared memory by coalesced 16-byte cp.async — chunk c of
+// 128-byte line L lands at chunk c ^ key(L), key chosen per group size so that eight neighbouring lanes reading
+// their own 16-byte chunks hit eight different bank groups — and the next tile of the persistent warp is in flight
+// while this one is computed.
 constexpr int kTWarps = 4;             // warps per CTA
-constexpr int kTTile = 32 * 256;       // bytes of one warp tile
 
+// GS = 128: a lane reads lines 2 t and 2 t + 1, key (L >> 1) & 7.  GS = 64: line t, key L & 7.  GS = 32: half of
+// line t >> 1, key L & 3 (bit 2 of the chunk index tells the two lanes of a line apart).
+template <int GS>
+__device__ __forceinline__ int swizzle_key(int line) {
+    return GS == 128 ? (line >> 1) & 7 : GS == 64 ? line & 7 : line & 3;
+}
+
+template <int GS>
 __device__ __forceinline__ void stage_groups(const uint8_t *x, long tile, long total_chunks, uint32_t stage, int lane) {
-    const long c0 = tile * 512 + lane;                      // 16-byte chunk index of this lane's first copy
-    const int cx = (lane & 7) ^ (lane >> 4);
-    const uint32_t base = stage + ((lane >> 3) << 7);
+    constexpr int kCopies = GS / 8;                         // 16-byte copies per lane: 32 groups x 2 GS bytes / (32 lanes x 16)
+    const long c0 = tile * (4 * GS) + lane;                 // 16-byte chunk index of this lane's first copy
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < kCopies; ++i) {
         const long c = c0 + i * 32;
-        const uint32_t dst = base + i * 512 + ((cx ^ ((2 * i) & 7)) << 4);
+        const int line = 4 * i + (lane >> 3);
+        const uint32_t dst = stage + line * 128 + (((lane & 7) ^ swizzle_key<GS>(line)) << 4);
         const int n = c < total_chunks ? 16 : 0;            // past the end: zero fill, nothing is read
         const uint8_t *src = x + (c < total_chunks ? c : 0) * 16;
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n));
@@ -162,45 +170,42 @@ __device__ __forceinline__ void stage_groups(const uint8_t *x, long tile, long t
     asm volatile("cp.async.commit_group;" ::);
 }
 
-template <bool HADAMARD>
+template <int GS, bool HADAMARD>
 __global__ void __launch_bounds__(kTWarps * 32, 4)
-quant_group128_thread_kernel(const uint8_t *__restrict__ x, uint4 *__restrict__ q, __half *__restrict__ scales, long groups) {
+quant_group_thread_kernel(const uint8_t *__restrict__ x, uint4 *__restrict__ q, __half *__restrict__ scales, long groups) {
+    constexpr int NH = GS / 2;                              // half2 registers of a group
+    constexpr int kTile = 64 * GS;                          // bytes of one warp tile
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    uint8_t *my = smem_raw + warp * kTTile;
+    uint8_t *my = smem_raw + warp * kTile;
     const uint32_t stage = smem_u32(my);
-    const long tiles = (groups + 31) >> 5, total_chunks = groups * 16;
+    const long tiles = (groups + 31) >> 5, total_chunks = groups * (GS / 8);
     const long nwarps = (long)gridDim.x * kTWarps;
     long tile = (long)blockIdx.x * kTWarps + warp;
-    if (tile < tiles) stage_groups(x, tile, total_chunks, stage, lane);
+    if (tile < tiles) stage_groups<GS>(x, tile, total_chunks, stage, lane);
 
     for (; tile < tiles; tile += nwarps) {
-        __half2 h[64];
+        __half2 h[NH];
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncwarp();
-        {
-            const uint8_t *mine = my + lane * 256;
-            const int tx = lane & 7;
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 w = *reinterpret_cast<const uint4 *>(mine + j * 128 + ((c ^ tx) << 4));
-                    h[j * 32 + c * 4 + 0] = u2h2(w.x); h[j * 32 + c * 4 + 1] = u2h2(w.y);
-                    h[j * 32 + c * 4 + 2] = u2h2(w.z); h[j * 32 + c * 4 + 3] = u2h2(w.w);
-                }
-            }
+        for (int cc = 0; cc < GS / 8; ++cc) {               // this lane's chunks, in element order
+            const int byte = lane * (2 * GS) + cc * 16;     // unswizzled position inside the tile
+            const int line = byte >> 7, c = (byte >> 4) & 7;
+            const uint4 w = *reinterpret_cast<const uint4 *>(my + line * 128 + ((c ^ swizzle_key<GS>(line)) << 4));
+            h[cc * 4 + 0] = u2h2(w.x); h[cc * 4 + 1] = u2h2(w.y);
+            h[cc * 4 + 2] = u2h2(w.z); h[cc * 4 + 3] = u2h2(w.w);
         }
-        __syncwarp();                                   // the tile is in registers everywhere: refill the buffer
-        if (tile + nwarps < tiles) stage_groups(x, tile + nwarps, total_chunks, stage, lane);
+        __syncwarp();                                       // the tile is in registers everywhere: refill the buffer
+        if (tile + nwarps < tiles) stage_groups<GS>(x, tile + nwarps, total_chunks, stage, lane);
 
         if (HADAMARD) {
 #pragma unroll
-            for (int r = 0; r < 64; ++r) h[r] = bfly_inner(h[r]);                 // bit 0
+            for (int r = 0; r < NH; ++r) h[r] = bfly_inner(h[r]);                 // bit 0
 #pragma unroll
-            for (int d = 1; d < 64; d <<= 1) {                                    // bits 1-6
+            for (int d = 1; d < NH; d <<= 1) {                                    // the remaining bits
 #pragma unroll
-                for (int r = 0; r < 64; ++r) {
+                for (int r = 0; r < NH; ++r) {
                     if ((r & d) == 0) {
                         const __half2 a = h[r], b = h[r + d];
                         h[r] = __hadd2(a, b);
@@ -211,21 +216,21 @@ quant_group128_thread_kernel(const uint8_t *__restrict__ x, uint4 *__restrict__ 
         }
         __half2 m2 = __habs2(h[0]);
 #pragma unroll
-        for (int r = 1; r < 64; ++r) m2 = __hmax2(m2, __habs2(h[r]));
+        for (int r = 1; r < NH; ++r) m2 = __hmax2(m2, __habs2(h[r]));
         const __half m = __hmax(__low2half(m2), __high2half(m2));
         const __half sh = group_scale(m);
         const float rcp = __frcp_rn(__half2float(sh));
         const long g = tile * 32 + lane;
         if (g < groups) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
+            for (int v = 0; v < GS / 32; ++v) {
                 uint32_t o[4];
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                     const __half2 hh[4] = {h[16 * v + 4 * w], h[16 * v + 4 * w + 1], h[16 * v + 4 * w + 2], h[16 * v + 4 * w + 3]};
                     o[w] = quant_pack8(hh, rcp);
                 }
-                q[g * 4 + v] = make_uint4(o[0], o[1], o[2], o[3]);
+                q[g * (GS / 32) + v] = make_uint4(o[0], o[1], o[2], o[3]);
             }
             scales[g] = sh;
         }
@@ -283,7 +288,7 @@ int grid_for(K kernel, long total_chunks) {
 }  // namespace
 
 // Groups from which the thread-per-group kernel is used (it measured faster from a few thousand groups on; below
-// that the 16-lanes-per-group kernel spreads a small input over more warps).  FLH_B200_GROUP_THREAD_MIN_ROWS
+// that the several-lanes-per-group kernel spreads a small input over more warps).  FLH_B200_GROUP_THREAD_MIN_ROWS
 // overrides it (tuning aid).
 static long group_thread_min_rows() {
     static long v = -1;
@@ -299,14 +304,19 @@ int launch_quant_group_sym(const void *x, long rows, int gs, int hadamard, uint8
                            void *scales, cudaStream_t stream) {
     const long chunks = rows * (gs / 8);
     // many groups of 128: the thread-per-group kernel (a full wave of its persistent warps has 32 groups each)
-    if (gs == 128 && rows >= group_thread_min_rows()) {
-        auto kern = hadamard ? quant_group128_thread_kernel<true> : quant_group128_thread_kernel<false>;
+    if (rows >= group_thread_min_rows()) {
         const long tiles = (rows + 31) / 32;
         long grid = (tiles + kTWarps - 1) / kTWarps;
         if (grid > 4L * kNumSMs) grid = 4L * kNumSMs;
-        kern<<<(unsigned)grid, kTWarps * 32, kTWarps * kTTile, stream>>>(static_cast<const uint8_t *>(x), reinterpret_cast<uint4 *>(q),
-                                                                       static_cast<__half *>(scales), rows);
-        return cuda_status(cudaGetLastError(), "quant_group128_thread launch");
+        const uint8_t *xb = static_cast<const uint8_t *>(x);
+        uint4 *qo4 = reinterpret_cast<uint4 *>(q);
+        __half *so4 = static_cast<__half *>(scales);
+#define FLH_TLAUNCH(GS_, H_) quant_group_thread_kernel<GS_, H_><<<(unsigned)grid, kTWarps * 32, kTWarps * 64 * GS_, stream>>>(xb, qo4, so4, rows)
+        if (gs == 128) { if (hadamard) FLH_TLAUNCH(128, true); else FLH_TLAUNCH(128, false); }
+        else if (gs == 64) { if (hadamard) FLH_TLAUNCH(64, true); else FLH_TLAUNCH(64, false); }
+        else { if (hadamard) FLH_TLAUNCH(32, true); else FLH_TLAUNCH(32, false); }
+#undef FLH_TLAUNCH
+        return cuda_status(cudaGetLastError(), "quant_group_thread launch");
     }
     const uint4 *xi = static_cast<const uint4 *>(x);
     uint32_t *qo = reinterpret_cast<uint32_t *>(q);

@@ -25,14 +25,15 @@ def test_group_sym_bit_exact(cuda, gs, had, rows):
     assert np.array_equal(q.cpu().numpy(), qo)
 
 
+@pytest.mark.parametrize("gs", [128, 64, 32])
 @pytest.mark.parametrize("had", [True, False])
 @pytest.mark.parametrize("rows", [4096, 20001, 200003])
-def test_group_sym_many_groups(cuda, had, rows):
+def test_group_sym_many_groups(cuda, gs, had, rows):
     """Large inputs run the thread-per-group kernel (persistent warps, 32 groups per tile, ragged last tile)."""
-    x = activations(900 + rows % 97, rows // 32 + 1, 128 * 32).reshape(-1, 128)[:rows]
+    x = activations(900 + rows % 97 + gs, rows // 32 + 1, gs * 32).reshape(-1, gs)[:rows]
     x = np.ascontiguousarray(x)
-    f = cuda.hadamard_and_quantize_i4 if had else cuda.quant_and_pack_i4
-    q, s = f(_dev(x))
+    f = cuda.hadamard_and_quantize_i4_gs if had else cuda.quant_and_pack_i4_gs
+    q, s = f(_dev(x), gs)
     qo, so = O.quant_group_sym(x, had)
     assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16))
     assert np.array_equal(q.cpu().numpy(), qo)
