@@ -404,9 +404,9 @@ def extras(C, device, peaks):
             it[0] += 1
             C.hadamard_and_quantize_i4(xs[it[0] % 2].view(-1, 128))
 
-        t = _time(f)
+        t = _time(f, iters=20, warm=20)      # the end-to-end leg before this left the GPU mostly idle: let the clocks come back
         ex[f"had_quant_token_asym_M{m}_K{k}_GBps"] = m * (2 * k + k // 2 + 4) / t / 1e9
-        t = _time(g)
+        t = _time(g, iters=20, warm=10)
         ex[f"had_quant_group128_sym_M{m}_K{k}_GBps"] = m * (2 * k + k // 2 + 2 * k // 128) / t / 1e9
         del xs
     for (m, k, n) in ((2048, 4096, 12288), (8192, 4096, 22016), (2048, 11008, 4096)):
