@@ -174,6 +174,23 @@ def quant_token_asym_i4(x, hadamard: bool = True, clip: float = 1.0, exact_facto
     return q, s, z
 
 
+def rmsnorm_quant_token_asym_i4(x, eps: float, hadamard: bool = False, clip: float = 1.0):
+    """RMS-norm (weight 1) + per-token asymmetric int4 in one pass, K = 4096 or 8192 (include/flh_b200.h).
+    x [M, K] f16/bf16 (row stride allowed) -> (q u8[M,K/2], scale f16[M], zero f16[M])."""
+    _check(x.is_cuda, "Input tensor must be on CUDA")
+    _check(x.dtype in (torch.float16, torch.bfloat16), "Input tensor must be float16 or bfloat16")
+    _check(x.dim() == 2 and x.stride(1) == 1, "Input tensor must be 2D with unit inner stride")
+    M, K = x.shape
+    q = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float16, device=x.device)
+    z = torch.empty((M,), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().flh_b200_rmsnorm_quant_token_asym_i4(
+            _ptr(x), BF16 if x.dtype == torch.bfloat16 else F16, M, K, x.stride(0), float(eps), int(hadamard), float(clip),
+            _ptr(q), _ptr(s), _ptr(z), _stream(x)), "rmsnorm_quant_token_asym_i4")
+    return q, s, z
+
+
 def weight_rowsum(B, group: int):
     """int32 [N, K/group] sums of the signed weight codes (needed with zero-points)."""
     _check(B.is_cuda and B.dtype == torch.uint8 and B.dim() == 2 and B.is_contiguous(), "B must be a contiguous CUDA uint8 matrix")

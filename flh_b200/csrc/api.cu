@@ -31,6 +31,7 @@ int launch_quant_group_sym(const void *, long, int, int, uint8_t *, void *, cuda
 int launch_fht_inplace(void *, long, int, cudaStream_t);
 int launch_quant_token_asym(const void *, int, long, long, long, int, int, const uint32_t *, float,
                             uint8_t *, void *, void *, cudaStream_t);
+int launch_quant_token_warp(const void *, int, long, long, long, int, float, float, uint8_t *, void *, void *, cudaStream_t);
 int launch_weight_rowsum(const uint8_t *, long, long, long, int32_t *, cudaStream_t);
 int launch_gemm_mma_tile(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
                          const int32_t *, const void *, void *, long, long, long, long, long, int,
@@ -129,6 +130,22 @@ int flh_b200_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, lo
     FLH_REQUIRE(kfac == 1 || aligned16(sign_bits), FLH_B200_EALIGN, "the factor table must be 16-byte aligned");
     return launch_quant_token_asym(x, in_dtype, M, K, ld, hadamard, kfac, sign_bits, clip, q, scale,
                                    zero, static_cast<cudaStream_t>(stream));
+}
+
+int flh_b200_rmsnorm_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, long ld, float eps, int hadamard,
+                                         float clip, uint8_t *q, void *scale, void *zero, void *stream) {
+    FLH_REQUIRE(M >= 0 && K > 0, FLH_B200_EINVAL, "bad shape M=%ld K=%ld", M, K);
+    FLH_REQUIRE(in_dtype == FLH_B200_F16 || in_dtype == FLH_B200_BF16, FLH_B200_EINVAL, "in_dtype must be F16 or BF16");
+    FLH_REQUIRE(K == 4096 || K == 8192, FLH_B200_EUNSUPPORTED, "the fused RMS-norm quantiser serves K = 4096 and 8192 (got %ld)", K);
+    FLH_REQUIRE(eps >= 0.0f, FLH_B200_EINVAL, "eps must be >= 0");
+    FLH_REQUIRE(hadamard == 0 || hadamard == 1, FLH_B200_EINVAL, "hadamard must be 0 or 1 (got %d)", hadamard);
+    FLH_REQUIRE(ld >= K && ld % 8 == 0, FLH_B200_EALIGN, "row stride must be >= K and a multiple of 8 elements (got %ld)", ld);
+    FLH_REQUIRE(clip > 0.0f && clip <= 1.0f, FLH_B200_EINVAL, "clip ratio must be in (0, 1]");
+    if (M == 0) return 0;
+    FLH_REQUIRE(x && q && scale && zero, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(aligned16(x), FLH_B200_EALIGN, "x must be 16-byte aligned");
+    FLH_REQUIRE(aligned16(q), FLH_B200_EALIGN, "q must be 16-byte aligned");
+    return launch_quant_token_warp(x, in_dtype, M, K, ld, hadamard, eps, clip, q, scale, zero, static_cast<cudaStream_t>(stream));
 }
 
 size_t flh_b200_sign_table_bytes(int kfac) {

@@ -479,8 +479,8 @@ int launch_one(const TokenParams &p, long M, cudaStream_t stream) {
 
 }  // namespace
 
-int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld, float clip, uint8_t *q,
-                            void *scale, void *zero, cudaStream_t stream);
+int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld, int hadamard, float norm_eps, float clip,
+                            uint8_t *q, void *scale, void *zero, cudaStream_t stream);
 
 int launch_quant_token_factor(const void *x, int in_dtype, long M, long K, long ld, int kfac, const void *sign_mat_bf16,
                               float clip, uint8_t *q, void *scale, void *zero, cudaStream_t stream);
@@ -500,8 +500,9 @@ static long token_warp_min_rows() {
 int launch_quant_token_asym(const void *x, int in_dtype, long M, long K, long ld, int hadamard,
                             int kfac, const uint32_t *sign_bits, float clip, uint8_t *q,
                             void *scale, void *zero, cudaStream_t stream) {
-    if (hadamard && kfac == 1 && (K == 4096 || K == 8192) && M >= token_warp_min_rows())
-        return launch_quant_token_warp(x, in_dtype, M, K, ld, clip, q, scale, zero, stream);
+    if ((!hadamard || kfac == 1) && (K == 4096 || K == 8192) && M >= token_warp_min_rows() &&
+        (hadamard || (reinterpret_cast<uintptr_t>(q) & 15) == 0))          // its untransformed form stores 16 bytes at a time
+        return launch_quant_token_warp(x, in_dtype, M, K, ld, hadamard, -1.0f, clip, q, scale, zero, stream);
     if (hadamard == 1 && kfac >= 64 && K == (long)kfac * 64 && M >= 256) {
         // K = kfac * 64 with a large factor (11008 = 172 * 64), prefill-size batches: butterflies + the factor on
         // tcgen05, two rows per step of a persistent CTA (its set-up costs more than a decode-size batch)

@@ -34,6 +34,7 @@ struct WarpParams {
     long ld_bytes;
     long M;
     float clip;
+    float eps;             // RMS-norm epsilon (NORM kernels)
     uint8_t *q;
     __half *scale;
     __half *zero;
@@ -71,10 +72,15 @@ __device__ __forceinline__ void stage_row(const WarpParams &p, long row, uint32_
     asm volatile("cp.async.commit_group;" ::);
 }
 
-template <bool BF16, int W>
+// HAD: apply the transform.  NORM: first RMS-normalise the row (weight 1) exactly as a separate kernel writing the
+// input's 16-bit type would: s = sum of squares (each lane adds its 128 values in order with fma, lanes are joined
+// by xor-shuffles 16, 8, 4, 2, 1, the two warps of a row last), c = 1 / sqrt(s / K + eps) correctly rounded,
+// y = round16(x * c) — the quantiser then sees y.
+template <bool BF16, int W, bool HAD, bool NORM>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, kCtasPerSm) quant_token_warp_kernel(const WarpParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __shared__ float red[kWarpsPerCta][2];
+    __shared__ float red_sq[kWarpsPerCta];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int grp = warp / W;                               // row slot of this warp inside the CTA
     const int t = (warp % W) * 32 + lane;                   // lane index inside the row: 0 .. 32 W - 1
@@ -99,32 +105,76 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kCtasPerSm) quant_token_war
         {
             const uint8_t *mine = my + t * 256;
             const int tx = t & 7;
+            // one 32-bit word = two neighbouring inputs -> one packed pair: with the transform (a + b, a - b), i.e. bit 0
+            auto consume = [&](uint32_t word, int idx) {
+                float lo, hi;
+                if (BF16) {
+                    const float a = __uint_as_float(word << 16);
+                    const float b = __uint_as_float(word & 0xffff0000u);
+                    lo = HAD ? __fadd_rn(a, b) : a;
+                    hi = HAD ? __fsub_rn(a, b) : b;
+                } else if (HAD) {
+                    // bit 0 straight from the binary16 pair: a + b and fma(b, -1, a) with b widened inside the
+                    // instruction are the same IEEE binary32 sum and difference as after two conversions
+                    uint16_t ha, hb;
+                    asm("mov.b32 {%0, %1}, %2;" : "=h"(ha), "=h"(hb) : "r"(word));
+                    const float a = __half2float(__ushort_as_half(ha));
+                    const uint16_t neg1 = 0xBC00u;
+                    asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(lo) : "h"(hb), "f"(a));
+                    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(hi) : "h"(hb), "h"(neg1), "f"(a));
+                } else {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&word));
+                    lo = f.x; hi = f.y;
+                }
+                v[idx] = pack2(lo, hi);
+            };
+            if (NORM) {
+                uint4 raw[16];
+                float ssq = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 w4 = *reinterpret_cast<const uint4 *>(mine + j * 128 + ((c ^ tx) << 4));
-                    const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+                for (int cc = 0; cc < 16; ++cc) {
+                    raw[cc] = *reinterpret_cast<const uint4 *>(mine + (cc >> 3) * 128 + (((cc & 7) ^ tx) << 4));
+                    const uint32_t w[4] = {raw[cc].x, raw[cc].y, raw[cc].z, raw[cc].w};
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        float sum, dif;
-                        if (BF16) {
-                            const float a = __uint_as_float(w[k] << 16);
-                            const float b = __uint_as_float(w[k] & 0xffff0000u);
-                            sum = __fadd_rn(a, b);
-                            dif = __fsub_rn(a, b);
-                        } else {
-                            // bit 0 straight from the binary16 pair: a + b and fma(b, -1, a) with b widened inside the
-                            // instruction are the same IEEE binary32 sum and difference as after two conversions
-                            uint16_t ha, hb;
-                            asm("mov.b32 {%0, %1}, %2;" : "=h"(ha), "=h"(hb) : "r"(w[k]));
-                            const float a = __half2float(__ushort_as_half(ha));
-                            const uint16_t neg1 = 0xBC00u;
-                            asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(sum) : "h"(hb), "f"(a));
-                            asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(dif) : "h"(hb), "h"(neg1), "f"(a));
-                        }
-                        v[j * 32 + c * 4 + k] = pack2(sum, dif);
+                        float a, b;
+                        if (BF16) { a = __uint_as_float(w[k] << 16); b = __uint_as_float(w[k] & 0xffff0000u); }
+                        else { const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k])); a = f.x; b = f.y; }
+                        ssq = __fmaf_rn(a, a, ssq);
+                        ssq = __fmaf_rn(b, b, ssq);
                     }
+                }
+#pragma unroll
+                for (int sft = 16; sft > 0; sft >>= 1) ssq = __fadd_rn(ssq, __shfl_xor_sync(0xffffffffu, ssq, sft));
+                if (W > 1) {
+                    if (lane == 0) red_sq[warp] = ssq;
+                    row_sync();
+                    ssq = __fadd_rn(red_sq[grp * W], red_sq[grp * W + 1]);
+                }
+                const float c = __frcp_rn(__fsqrt_rn(__fadd_rn(__fmul_rn(ssq, 1.0f / (float)(kRowK * W)), p.eps)));
+#pragma unroll
+                for (int cc = 0; cc < 16; ++cc) {
+                    const uint32_t w[4] = {raw[cc].x, raw[cc].y, raw[cc].z, raw[cc].w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint32_t word;
+                        if (BF16) {
+                            const __nv_bfloat162 y = __floats2bfloat162_rn(__fmul_rn(__uint_as_float(w[k] << 16), c),
+                                                                           __fmul_rn(__uint_as_float(w[k] & 0xffff0000u), c));
+                            word = *reinterpret_cast<const uint32_t *>(&y);
+                        } else {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+                            const __half2 y = __floats2half2_rn(__fmul_rn(f.x, c), __fmul_rn(f.y, c));
+                            word = *reinterpret_cast<const uint32_t *>(&y);
+                        }
+                        consume(word, cc * 4 + k);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int cc = 0; cc < 16; ++cc) {
+                    const uint4 w4 = *reinterpret_cast<const uint4 *>(mine + (cc >> 3) * 128 + (((cc & 7) ^ tx) << 4));
+                    consume(w4.x, cc * 4 + 0); consume(w4.y, cc * 4 + 1); consume(w4.z, cc * 4 + 2); consume(w4.w, cc * 4 + 3);
                 }
             }
         }
@@ -135,33 +185,37 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kCtasPerSm) quant_token_war
             asm volatile("prefetch.global.L2 [%0];" ::"l"(nx));
             asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + 4096 * W));
         }
-        bfly_pairs<1>(v);                               // bits 1-6
-
-        // ---------------- transpose: lane's chunk out, 4-wide (W = 2: 2-wide) columns in ---------------
-        {
-            const uint32_t out = xp + t * (kChunkWords * 4);
-#pragma unroll
-            for (int k = 0; k < 64; k += 2)
-                asm volatile("st.shared.v2.u64 [%0], {%1, %2};" ::"r"(out + 8 * k), "l"(v[k]), "l"(v[k + 1]) : "memory");
-        }
-        row_sync();
-        if (W == 1) {
-            // pair index k = 2 m + h: elements m * 128 + 4 lane + 2 h + {0, 1}
-            const uint32_t in = xp + t * 16;
-#pragma unroll
-            for (int m = 0; m < 32; ++m)
-                asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v[2 * m]), "=l"(v[2 * m + 1]) : "r"(in + m * (kChunkWords * 4)) : "memory");
+        if (!HAD) {
+            if (more) stage_row<W>(p, row + nwarps, stage, t);       // no transpose: the buffer is free at once
         } else {
-            // pair index k = m (0..63): elements m * 128 + 2 t + {0, 1}
-            const uint32_t in = xp + t * 8;
+            bfly_pairs<1>(v);                               // bits 1-6
+
+            // ---------------- transpose: lane's chunk out, 4-wide (W = 2: 2-wide) columns in ---------------
+            {
+                const uint32_t out = xp + t * (kChunkWords * 4);
 #pragma unroll
-            for (int m = 0; m < 64; ++m)
-                asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v[m]) : "r"(in + m * (kChunkWords * 4)) : "memory");
+                for (int k = 0; k < 64; k += 2)
+                    asm volatile("st.shared.v2.u64 [%0], {%1, %2};" ::"r"(out + 8 * k), "l"(v[k]), "l"(v[k + 1]) : "memory");
+            }
+            row_sync();
+            if (W == 1) {
+                // pair index k = 2 m + h: elements m * 128 + 4 lane + 2 h + {0, 1}
+                const uint32_t in = xp + t * 16;
+#pragma unroll
+                for (int m = 0; m < 32; ++m)
+                    asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v[2 * m]), "=l"(v[2 * m + 1]) : "r"(in + m * (kChunkWords * 4)) : "memory");
+            } else {
+                // pair index k = m (0..63): elements m * 128 + 2 t + {0, 1}
+                const uint32_t in = xp + t * 8;
+#pragma unroll
+                for (int m = 0; m < 64; ++m)
+                    asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v[m]) : "r"(in + m * (kChunkWords * 4)) : "memory");
+            }
+            row_sync();                                     // the buffer is free again: stage the next row into it
+            if (more) stage_row<W>(p, row + nwarps, stage, t);
+            if (W == 1) bfly_pairs<2>(v);                   // bits 7-11 (over m, two pairs per m)
+            else bfly_pairs<1>(v);                          // bits 7-12 (over m, one pair per m)
         }
-        row_sync();                                     // the buffer is free again: stage the next row into it
-        if (more) stage_row<W>(p, row + nwarps, stage, t);
-        if (W == 1) bfly_pairs<2>(v);                   // bits 7-11 (over m, two pairs per m)
-        else bfly_pairs<1>(v);                          // bits 7-12 (over m, one pair per m)
 
         // ---------------- row min / max, parameters ------------------------------------------------
         float vmin = 0.0f, vmax = 0.0f;
@@ -181,7 +235,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kCtasPerSm) quant_token_war
             for (int o = 0; o < W; ++o) { vmin = fminf(vmin, red[grp * W + o][0]); vmax = fmaxf(vmax, red[grp * W + o][1]); }
             // (the next write of red comes after three more row barriers)
         }
-        const TokenRowParams rp = token_row_params(vmin, vmax, p.clip, W == 1 ? 64.0f : 90.50966799187809f);   // sqrt(4096 W)
+        const TokenRowParams rp = token_row_params(vmin, vmax, p.clip, !HAD ? 1.0f : W == 1 ? 64.0f : 90.50966799187809f);   // sqrt(4096 W) with the transform
         if (t == 0) { p.scale[row] = rp.scale; p.zero[row] = __float2half_rn(rp.zero); }
 
         // ---------------- codes --------------------------------------------------------------------
@@ -202,7 +256,28 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kCtasPerSm) quant_token_war
             }
         }
         const uint64_t magic2 = pack2(12582912.0f, 12582912.0f);
-        if (W == 1) {
+        if (!HAD) {
+            // the lane holds 128 consecutive elements: eight codes per 32-bit word by Horner in 16; the constant upper
+            // part J of the eight bit patterns contributes J * 0x11111111, which is taken off again (all mod 2^32)
+            const uint32_t fix = 0x11111111u * (uint32_t)(int)rp.zero - 0x4B400000u * 0x11111111u;
+            uint4 *qrow = reinterpret_cast<uint4 *>(p.q + row * (long)(kRowK * W / 2) + t * 64);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint32_t o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t w = 0;
+#pragma unroll
+                    for (int i = 3; i >= 0; --i) {
+                        float r0, r1;
+                        unpack2(add2(v[g * 16 + j * 4 + i], magic2), r0, r1);
+                        w = (w * 16u + __float_as_uint(r1)) * 16u + __float_as_uint(r0);
+                    }
+                    o[j] = w + fix;
+                }
+                qrow[g] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        } else if (W == 1) {
             const uint32_t zsum = 0x1111u * (uint32_t)(int)rp.zero;
             uint16_t *qrow = reinterpret_cast<uint16_t *>(p.q + row * (long)(kRowK / 2)) + t;
 #pragma unroll
@@ -233,10 +308,10 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kCtasPerSm) quant_token_war
 
 }  // namespace
 
-// K = 4096 or 8192 with the transform and no factor stage.  Returns -1000 when the shape is not one this kernel
-// takes (the caller then uses the general kernel).
-int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld, float clip, uint8_t *q,
-                            void *scale, void *zero, cudaStream_t stream) {
+// K = 4096 or 8192 (no factor stage), with or without the transform, optionally RMS-normalised first (norm_eps >= 0).
+// Returns -1000 when the shape is not one this kernel takes (the caller then uses the general kernel).
+int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld, int hadamard, float norm_eps, float clip,
+                            uint8_t *q, void *scale, void *zero, cudaStream_t stream) {
     if (K != kRowK && K != 2 * kRowK) return -1000;
     const int W = (int)(K / kRowK);
     WarpParams p;
@@ -244,14 +319,26 @@ int launch_quant_token_warp(const void *x, int in_dtype, long M, long K, long ld
     p.ld_bytes = ld * 2;
     p.M = M;
     p.clip = clip;
+    p.eps = norm_eps;
     p.q = q;
     p.scale = static_cast<__half *>(scale);
     p.zero = static_cast<__half *>(zero);
     const size_t smem = (size_t)kWarpsPerCta * kWarpBytes;
-    auto kern = W == 1 ? (in_dtype == FLH_B200_BF16 ? quant_token_warp_kernel<true, 1> : quant_token_warp_kernel<false, 1>)
-                       : (in_dtype == FLH_B200_BF16 ? quant_token_warp_kernel<true, 2> : quant_token_warp_kernel<false, 2>);
-    static bool attr_done[4][64] = {};
-    const int which = (in_dtype == FLH_B200_BF16) + 2 * (W - 1);
+    const bool bf = in_dtype == FLH_B200_BF16, had = hadamard != 0, norm = norm_eps >= 0.0f;
+    using Kern = void (*)(const WarpParams);
+    // [bf16][W - 1][HAD][NORM]
+    static const Kern table[2][2][2][2] = {
+        {{{quant_token_warp_kernel<false, 1, false, false>, quant_token_warp_kernel<false, 1, false, true>},
+          {quant_token_warp_kernel<false, 1, true, false>, quant_token_warp_kernel<false, 1, true, true>}},
+         {{quant_token_warp_kernel<false, 2, false, false>, quant_token_warp_kernel<false, 2, false, true>},
+          {quant_token_warp_kernel<false, 2, true, false>, quant_token_warp_kernel<false, 2, true, true>}}},
+        {{{quant_token_warp_kernel<true, 1, false, false>, quant_token_warp_kernel<true, 1, false, true>},
+          {quant_token_warp_kernel<true, 1, true, false>, quant_token_warp_kernel<true, 1, true, true>}},
+         {{quant_token_warp_kernel<true, 2, false, false>, quant_token_warp_kernel<true, 2, false, true>},
+          {quant_token_warp_kernel<true, 2, true, false>, quant_token_warp_kernel<true, 2, true, true>}}}};
+    const Kern kern = table[bf][W - 1][had][norm];
+    static bool attr_done[16][64] = {};
+    const int which = (int)bf * 8 + (W - 1) * 4 + (int)had * 2 + (int)norm;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
     if (dev < 0 || !attr_done[which][dev]) {         // the attribute is per device

@@ -40,6 +40,7 @@ class DecoderConfig:
     eps: float = 1e-5
     act_mode: str = "group_sym"          # or "token_asym"
     tp: int = 1
+    fuse_norm: bool = True               # RMS-norm fused into the per-token quantiser where the kernel exists
 
     @property
     def head_dim(self):
@@ -100,13 +101,23 @@ class DecoderLayer(torch.nn.Module):
             self.gate_up = ColumnParallelLinearFLH(_random_linear(cfg.hidden, 2 * cfg.ffn // tp, cfg, device, gen), group)
             self.down = RowParallelLinearFLH(_random_linear(cfg.ffn // tp, cfg.hidden, cfg, device, gen), group)
 
+    def _norm_quant(self, norm, quant, x):
+        """RMS-norm then quantise.  Per-token mode at hidden sizes 4096 / 8192: one fused kernel (the norm weight is 1,
+        as FLH leaves it after folding it into the next linear); otherwise the two steps."""
+        cfg = self.cfg
+        if cfg.fuse_norm and cfg.act_mode == "token_asym" and cfg.hidden in (4096, 8192) and not quant.use_hadamard:
+            lead = x.shape[:-1]
+            q, s, z = _CUDA.rmsnorm_quant_token_asym_i4(x.reshape(-1, cfg.hidden), norm.eps, hadamard=False)
+            return s.view(lead + (1,)), z.view(lead + (1,)), q.view(lead + (cfg.hidden // 2,))
+        return quant(norm(x))
+
     def forward(self, x, pos, cache=None):
         """x [B, S, hidden] f16; pos [S] absolute positions; cache = (k, v) [B, nkv, T, D] with a write
         cursor `cache[2]`, or None for a cache-less prefill."""
         cfg = self.cfg
         B, S, _ = x.shape
         hd = cfg.head_dim
-        s, z, q = self.q_in(self.norm1(x))
+        s, z, q = self._norm_quant(self.norm1, self.q_in, x)
         qkv = self.qkv(q, s, z)
         qh, kh, vh = qkv.split((self.nh * hd, self.nkv * hd, self.nkv * hd), dim=-1)
         qh = rope(qh.view(B, S, self.nh, hd), pos, cfg.rope_theta).transpose(1, 2)
@@ -121,7 +132,7 @@ class DecoderLayer(torch.nn.Module):
         att = att.transpose(1, 2).reshape(B, S, self.nh * hd)
         s, z, q = self.q_attn(att)
         x = x + self.o(q, s, z)
-        s, z, q = self.q_mlp(self.norm2(x))
+        s, z, q = self._norm_quant(self.norm2, self.q_mlp, x)
         gu = self.gate_up(q, s, z)
         g, u = gu.chunk(2, dim=-1)
         a = F.silu(g) * u

@@ -95,6 +95,19 @@ int flh_b200_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, lo
                                  int hadamard, int kfac, const uint32_t *sign_bits, float clip,
                                  uint8_t *q, void *scale, void *zero, void *stream);
 
+/* RMS-norm (weight 1, as FLH leaves it after folding the norm weight into the next linear) fused in front of the
+ * per-token asymmetric quantiser, K = 4096 or 8192: the decoder's "norm -> quantise" pair as one pass over the row.
+ * Equal to normalising into the input's 16-bit type and then calling flh_b200_quant_token_asym_i4(hadamard) on
+ * the result, with the normalisation defined as: s = sum x^2 in binary32 (each of the 32 K / 4096 lanes of a row
+ * adds its 128 consecutive values in order with fma; lanes are joined by xor-shuffles 16, 8, 4, 2, 1, then the
+ * two halves of a K = 8192 row), c = 1 / sqrt(s / K + eps) with correctly rounded sqrt and reciprocal,
+ * y = round_to_input_type(x * c).  q must be 16-byte aligned.  FLH_B200_EUNSUPPORTED for other K (normalise
+ * separately).  The reference has no fused form: `flh/nn/normalization.py` + `flh/nn/quantization.py:143-291`
+ * run back to back in `flh/quantized_model/modeling_llama.py:389-393, 522-526`. */
+int flh_b200_rmsnorm_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, long ld, float eps,
+                                         int hadamard, float clip, uint8_t *q, void *scale, void *zero,
+                                         void *stream);
+
 /* HOST helpers: build the factor table of a kfac x kfac matrix of +1/-1 (int8, row-major, host
  * memory).  Layout: bit rows out[k * words + w], bit b = 1 when signs[k][32 w + b] < 0,
  * words = (kfac + 31) / 32; then, at the next 16-byte boundary, the same matrix as bfloat16 +-1.0

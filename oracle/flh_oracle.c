@@ -355,5 +355,37 @@ void flh_oracle_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const uint16
 }
 
 /* Conversions exported for the Python side of the tests. */
+/* RMS-normalisation (weight 1) into the input's 16-bit type, with the summation order the fused B200 kernel
+ * defines (include/flh_b200.h, flh_b200_rmsnorm_quant_token_asym_i4): lanes of 128 consecutive values added in order
+ * with fma, 32 lanes joined by an xor tree (16, 8, 4, 2, 1), the warps of a row added last; then
+ * c = 1 / sqrt(s / K + eps) with correctly rounded sqrt and division, y = round16(x * c).
+ * Restates flh/nn/normalization.py (x * rsqrt(mean(x^2) + eps), weight folded to 1) up to that order. */
+void flh_oracle_rmsnorm16(const uint16_t *x, int bf16, long M, long K, long ld, float eps, uint16_t *y) {
+    const long lanes = K / 128, warps = lanes / 32;
+    for (long r = 0; r < M; ++r) {
+        const uint16_t *row = x + r * ld;
+        float total = 0.0f;
+        for (long w = 0; w < warps; ++w) {
+            float s[32], t[32];
+            for (int l = 0; l < 32; ++l) {
+                float acc = 0.0f;
+                const uint16_t *v = row + (w * 32 + l) * 128;
+                for (int i = 0; i < 128; ++i) { const float f = bf16 ? bf2f(v[i]) : h2f(v[i]); acc = fmaf(f, f, acc); }
+                s[l] = acc;
+            }
+            for (int sft = 16; sft > 0; sft >>= 1) {
+                for (int l = 0; l < 32; ++l) t[l] = s[l] + s[l ^ sft];
+                memcpy(s, t, sizeof(s));
+            }
+            total = w == 0 ? s[0] : total + s[0];
+        }
+        const float c = 1.0f / sqrtf(total * (1.0f / (float)K) + eps);
+        for (long i = 0; i < K; ++i) {
+            const float f = bf16 ? bf2f(row[i]) : h2f(row[i]);
+            y[r * K + i] = bf16 ? f2bf(f * c) : f2h(f * c);
+        }
+    }
+}
+
 void flh_oracle_f32_to_f16(const float *in, uint16_t *out, long n) { for (long i = 0; i < n; ++i) out[i] = f2h(in[i]); }
 void flh_oracle_f16_to_f32(const uint16_t *in, float *out, long n) { for (long i = 0; i < n; ++i) out[i] = h2f(in[i]); }

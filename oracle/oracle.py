@@ -149,6 +149,18 @@ def quant_token_asym(x: np.ndarray, hadamard: bool, clip: float = 1.0, exact_nor
     return q, s, z
 
 
+def rmsnorm16(x: np.ndarray, eps: float, bf16: bool = False) -> np.ndarray:
+    """RMS-norm (weight 1) of x [M, K] (float16, or uint16 bfloat16 bits) into the same 16-bit type, K = 4096 or
+    8192, in the summation order of the fused B200 kernel.  Restates flh/nn/normalization.py up to that order."""
+    xx = np.ascontiguousarray(x).view(np.uint16)
+    m, k = xx.shape
+    assert k % 4096 == 0
+    y = np.empty((m, k), dtype=np.uint16)
+    lib().flh_oracle_rmsnorm16(_p(xx, _u16p), ctypes.c_int(int(bf16)), ctypes.c_long(m), ctypes.c_long(k), ctypes.c_long(k),
+                               ctypes.c_float(eps), _p(y, _u16p))
+    return y if bf16 else y.view(np.float16)
+
+
 # ----------------------------------------------------------------------------- weights (offline side)
 def rtn_group_sym(w: np.ndarray, group: int = 128):
     """Symmetric RTN int4 with one scale per (row, group).

@@ -179,6 +179,64 @@ def test_token_asym_k4096_large_batches(cuda, m, k, bf16):
         assert np.array_equal(q.cpu().numpy(), qo)
 
 
+@pytest.mark.parametrize("m,k", [(600, 4096), (777, 8192)])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_token_asym_plain_large_batches(cuda, m, k, bf16):
+    """Without the transform, K = 4096 / 8192 and many rows also run the warp-per-row kernel."""
+    xf = activations(3800 + m, m, k).astype(np.float32)
+    xf[3] = 0.0
+    if bf16:
+        xo = O.f32_to_bf16_bits(xf)
+        xin = torch.from_numpy(xo.view(np.int16)).cuda().view(torch.bfloat16)
+    else:
+        xo = xf.astype(np.float16)
+        xin = torch.from_numpy(xo).cuda()
+    for clip in (1.0, 0.9):
+        q, s, z = cuda.quant_token_asym_i4(xin, hadamard=False, clip=clip)
+        qo, so, zo = O.quant_token_asym(xo, False, clip=clip, bf16=bf16)
+        assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16))
+        assert np.array_equal(z.cpu().numpy().view(np.uint16), zo.view(np.uint16))
+        assert np.array_equal(q.cpu().numpy(), qo)
+
+
+@pytest.mark.parametrize("m,k", [(1, 4096), (130, 4096), (1500, 4096), (3, 8192), (700, 8192)])
+@pytest.mark.parametrize("had", [False, True])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_rmsnorm_quant_token_fused(cuda, m, k, had, bf16):
+    """RMS-norm fused in front of the token quantiser: bit-equal to the oracle's normalisation (same summation order)
+    followed by the oracle's quantiser; and within rounding of torch's own RMS-norm."""
+    eps = 1e-5
+    xf = (activations(3900 + m + k % 13, m, k).astype(np.float32) * 3.0)
+    if m > 2:
+        xf[1] = 0.0                                    # all-zero row: c = 1 / sqrt(eps), everything stays 0
+    if bf16:
+        xo = O.f32_to_bf16_bits(xf)
+        xin = torch.zeros((m, k + 8), dtype=torch.bfloat16, device="cuda")
+        xin[:, :k] = torch.from_numpy(xo.view(np.int16)).cuda().view(torch.bfloat16)
+    else:
+        xo = xf.astype(np.float16)
+        xin = torch.zeros((m, k + 8), dtype=torch.float16, device="cuda")
+        xin[:, :k] = torch.from_numpy(xo).cuda()
+    q, s, z = cuda.rmsnorm_quant_token_asym_i4(xin[:, :k], eps, hadamard=had)
+    yo = O.rmsnorm16(xo, eps, bf16=bf16)
+    qo, so, zo = O.quant_token_asym(yo, had, bf16=bf16)
+    assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16))
+    assert np.array_equal(z.cpu().numpy().view(np.uint16), zo.view(np.uint16))
+    assert np.array_equal(q.cpu().numpy(), qo)
+    # the oracle's normalisation against torch's (another summation order, approximate rsqrt): one 16-bit ulp
+    v = xin[:, :k].float()
+    yt = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(xin.dtype).float().cpu().numpy()
+    yof = O.bf16_bits_to_f32(yo) if bf16 else yo.astype(np.float32)
+    ulp = np.maximum(np.abs(yt), 1e-3) * (2.0 ** -7 if bf16 else 2.0 ** -10)
+    assert np.all(np.abs(yof - yt) <= ulp)
+
+
+def test_rmsnorm_quant_rejects_other_widths(cuda):
+    x = torch.zeros((4, 2048), dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="4096"):
+        cuda.rmsnorm_quant_token_asym_i4(x, 1e-5)
+
+
 def test_token_asym_full_size_property(cuda):
     # BASELINE sweep M=4096, K=4096: sampled rows against the oracle + a checksum of all codes
     x = activations(88, 4096, 4096)

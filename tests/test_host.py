@@ -124,3 +124,18 @@ def test_pack_unpack_roundtrip():
     assert p.dtype == torch.uint8 and p.shape == (5, 32)
     assert torch.equal(unpack_i4(p), q)
     assert int(p[0, 0]) == (int(q[0, 0]) & 15) | ((int(q[0, 1]) & 15) << 4)
+
+
+def test_oracle_rmsnorm_matches_torch():
+    """The oracle's RMS-norm (fixed summation order, correctly rounded 1 / sqrt) against torch's on the CPU:
+    at most one unit in the last place of the 16-bit result."""
+    import torch
+    from helpers import activations
+    from oracle import oracle as O
+    for k in (4096, 8192):
+        x = (activations(77 + k, 9, k).astype(np.float32) * 2.5).astype(np.float16)
+        y = O.rmsnorm16(x, 1e-5).astype(np.float32)
+        v = torch.from_numpy(x).float()
+        yt = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-5)).half().float().numpy()
+        assert np.all(np.abs(y - yt) <= np.maximum(np.abs(yt), 1e-3) * 2.0 ** -10)
+        assert (y != yt).mean() < 1e-2
