@@ -191,6 +191,18 @@ def rmsnorm_quant_token_asym_i4(x, eps: float, hadamard: bool = False, clip: flo
     return q, s, z
 
 
+def rmsnorm_quant_group_sym_i4(x, eps: float, hadamard: bool = False):
+    """RMS-norm (weight 1) + group-128 symmetric int4 in one pass: x f16 [M, 4096] -> [q u8[M*32, 64], scale f16[M*32]]."""
+    _check(x.is_cuda and x.dtype == torch.float16 and x.dim() == 2 and x.is_contiguous(), "x must be a contiguous CUDA float16 matrix")
+    M, K = x.shape
+    q = torch.empty((M * (K // 128), 64), dtype=torch.uint8, device=x.device)
+    s = torch.empty((M * (K // 128),), dtype=torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().flh_b200_rmsnorm_quant_group_sym_i4(_ptr(x), M, K, float(eps), int(hadamard), _ptr(q), _ptr(s), _stream(x)),
+                   "rmsnorm_quant_group_sym_i4")
+    return [q, s]
+
+
 def weight_rowsum(B, group: int):
     """int32 [N, K/group] sums of the signed weight codes (needed with zero-points)."""
     _check(B.is_cuda and B.dtype == torch.uint8 and B.dim() == 2 and B.is_contiguous(), "B must be a contiguous CUDA uint8 matrix")

@@ -31,6 +31,7 @@ SIGNATURES = {
                                                         c_void_p, c_long, c_long, c_long, c_long, c_long, c_int, c_void_p]),
     "flh_b200_rmsnorm_quant_token_asym_i4": (c_int, [c_void_p, c_int, c_long, c_long, c_long, c_float, c_int, c_float, c_void_p,
                                                      c_void_p, c_void_p, c_void_p]),
+    "flh_b200_rmsnorm_quant_group_sym_i4": (c_int, [c_void_p, c_long, c_long, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "flh_b200_expand_i4": (c_int, [c_void_p, c_long, c_long, c_void_p, c_void_p]),
     "flh_b200_gemm_i8w_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_long, c_long, c_long, c_int, c_void_p, c_size_t, c_void_p]),

@@ -32,6 +32,7 @@ int launch_fht_inplace(void *, long, int, cudaStream_t);
 int launch_quant_token_asym(const void *, int, long, long, long, int, int, const uint32_t *, float,
                             uint8_t *, void *, void *, cudaStream_t);
 int launch_quant_token_warp(const void *, int, long, long, long, int, float, float, uint8_t *, void *, void *, cudaStream_t);
+int launch_rmsnorm_quant_group(const void *, long, int, float, uint8_t *, void *, cudaStream_t);
 int launch_weight_rowsum(const uint8_t *, long, long, long, int32_t *, cudaStream_t);
 int launch_gemm_mma_tile(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
                          const int32_t *, const void *, void *, long, long, long, long, long, int,
@@ -130,6 +131,18 @@ int flh_b200_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, lo
     FLH_REQUIRE(kfac == 1 || aligned16(sign_bits), FLH_B200_EALIGN, "the factor table must be 16-byte aligned");
     return launch_quant_token_asym(x, in_dtype, M, K, ld, hadamard, kfac, sign_bits, clip, q, scale,
                                    zero, static_cast<cudaStream_t>(stream));
+}
+
+int flh_b200_rmsnorm_quant_group_sym_i4(const void *x, long M, long K, float eps, int hadamard, uint8_t *q, void *scales,
+                                        void *stream) {
+    FLH_REQUIRE(M >= 0, FLH_B200_EINVAL, "bad row count %ld", M);
+    FLH_REQUIRE(K == 4096, FLH_B200_EUNSUPPORTED, "the fused RMS-norm group quantiser serves K = 4096 (got %ld)", K);
+    FLH_REQUIRE(eps >= 0.0f, FLH_B200_EINVAL, "eps must be >= 0");
+    FLH_REQUIRE(hadamard == 0 || hadamard == 1, FLH_B200_EINVAL, "hadamard must be 0 or 1 (got %d)", hadamard);
+    if (M == 0) return 0;
+    FLH_REQUIRE(x && q && scales, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(aligned16(x) && aligned16(q), FLH_B200_EALIGN, "x and q must be 16-byte aligned");
+    return launch_rmsnorm_quant_group(x, M, hadamard, eps, q, scales, static_cast<cudaStream_t>(stream));
 }
 
 int flh_b200_rmsnorm_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, long ld, float eps, int hadamard,

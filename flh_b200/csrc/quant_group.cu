@@ -170,9 +170,13 @@ __device__ __forceinline__ void stage_groups(const uint8_t *x, long tile, long t
     asm volatile("cp.async.commit_group;" ::);
 }
 
-template <int GS, bool HADAMARD>
+// NORM (GS = 128 only, rows of 4096 = one warp tile): RMS-normalise the row first, exactly as the per-token kernels do
+// (each lane adds its 128 squares in order with fma, xor-shuffle tree 16 .. 1, c = 1 / sqrt(s / 4096 + eps) correctly
+// rounded, y = half(x * c)).
+template <int GS, bool HADAMARD, bool NORM = false>
 __global__ void __launch_bounds__(kTWarps * 32, 4)
-quant_group_thread_kernel(const uint8_t *__restrict__ x, uint4 *__restrict__ q, __half *__restrict__ scales, long groups) {
+quant_group_thread_kernel(const uint8_t *__restrict__ x, uint4 *__restrict__ q, __half *__restrict__ scales, long groups, float eps = 0.0f) {
+    static_assert(!NORM || GS == 128, "the fused norm is written for rows of 4096 = 32 groups of 128");
     constexpr int NH = GS / 2;                              // half2 registers of a group
     constexpr int kTile = 64 * GS;                          // bytes of one warp tile
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -199,6 +203,23 @@ quant_group_thread_kernel(const uint8_t *__restrict__ x, uint4 *__restrict__ q, 
         __syncwarp();                                       // the tile is in registers everywhere: refill the buffer
         if (tile + nwarps < tiles) stage_groups<GS>(x, tile + nwarps, total_chunks, stage, lane);
 
+        if (NORM) {
+            float ssq = 0.0f;
+#pragma unroll
+            for (int r = 0; r < NH; ++r) {
+                const float2 f = __half22float2(h[r]);
+                ssq = __fmaf_rn(f.x, f.x, ssq);
+                ssq = __fmaf_rn(f.y, f.y, ssq);
+            }
+#pragma unroll
+            for (int sft = 16; sft > 0; sft >>= 1) ssq = __fadd_rn(ssq, __shfl_xor_sync(0xffffffffu, ssq, sft));
+            const float c = __frcp_rn(__fsqrt_rn(__fadd_rn(__fmul_rn(ssq, 1.0f / 4096.0f), eps)));
+#pragma unroll
+            for (int r = 0; r < NH; ++r) {
+                const float2 f = __half22float2(h[r]);
+                h[r] = __floats2half2_rn(__fmul_rn(f.x, c), __fmul_rn(f.y, c));
+            }
+        }
         if (HADAMARD) {
 #pragma unroll
             for (int r = 0; r < NH; ++r) h[r] = bfly_inner(h[r]);                 // bit 0
@@ -327,6 +348,20 @@ int launch_quant_group_sym(const void *x, long rows, int gs, int hadamard, uint8
     else { if (hadamard) FLH_LAUNCH(5, true); else FLH_LAUNCH(5, false); }
 #undef FLH_LAUNCH
     return cuda_status(cudaGetLastError(), "quant_group_sym launch");
+}
+
+// rows of 4096 halves: RMS-norm + group-128 (transform +) symmetric int4 + pack
+int launch_rmsnorm_quant_group(const void *x, long M, int hadamard, float eps, uint8_t *q, void *scales, cudaStream_t stream) {
+    const long groups = M * 32;
+    const long tiles = M;
+    long grid = (tiles + kTWarps - 1) / kTWarps;
+    if (grid > 4L * kNumSMs) grid = 4L * kNumSMs;
+    const uint8_t *xb = static_cast<const uint8_t *>(x);
+    uint4 *qo4 = reinterpret_cast<uint4 *>(q);
+    __half *so4 = static_cast<__half *>(scales);
+    if (hadamard) quant_group_thread_kernel<128, true, true><<<(unsigned)grid, kTWarps * 32, kTWarps * 64 * 128, stream>>>(xb, qo4, so4, groups, eps);
+    else quant_group_thread_kernel<128, false, true><<<(unsigned)grid, kTWarps * 32, kTWarps * 64 * 128, stream>>>(xb, qo4, so4, groups, eps);
+    return cuda_status(cudaGetLastError(), "rmsnorm_quant_group launch");
 }
 
 int launch_fht_inplace(void *x, long rows, int n, cudaStream_t stream) {

@@ -109,6 +109,12 @@ class DecoderLayer(torch.nn.Module):
             lead = x.shape[:-1]
             q, s, z = _CUDA.rmsnorm_quant_token_asym_i4(x.reshape(-1, cfg.hidden), norm.eps, hadamard=False)
             return s.view(lead + (1,)), z.view(lead + (1,)), q.view(lead + (cfg.hidden // 2,))
+        if cfg.fuse_norm and cfg.act_mode == "group_sym" and cfg.hidden == 4096 and quant.group_size == 128 and x.dtype == torch.float16:
+            lead = x.shape[:-1]
+            q, s = _CUDA.rmsnorm_quant_group_sym_i4(x.reshape(-1, cfg.hidden), norm.eps, hadamard=quant.use_hadamard)
+            if quant.use_hadamard:
+                s = s / math.sqrt(128)                   # the kernel's transform is un-normalised (as in ActQuantizer.forward)
+            return s.view(lead + (cfg.hidden // 128,)), None, q.view(lead + (cfg.hidden // 2,))
         return quant(norm(x))
 
     def forward(self, x, pos, cache=None):

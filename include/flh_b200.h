@@ -108,6 +108,12 @@ int flh_b200_rmsnorm_quant_token_asym_i4(const void *x, int in_dtype, long M, lo
                                          int hadamard, float clip, uint8_t *q, void *scale, void *zero,
                                          void *stream);
 
+/* The same fusion for the group-128 symmetric mode (the flh._CUDA contract): x f16 [M, 4096] contiguous ->
+ * q [M * 32, 64], scales [M * 32], equal to normalising into f16 (same definition as above) and then calling
+ * flh_b200_quant_group_sym_i4(gs = 128, hadamard).  K = 4096 only (a warp owns a whole row). */
+int flh_b200_rmsnorm_quant_group_sym_i4(const void *x, long M, long K, float eps, int hadamard, uint8_t *q,
+                                        void *scales, void *stream);
+
 /* HOST helpers: build the factor table of a kfac x kfac matrix of +1/-1 (int8, row-major, host
  * memory).  Layout: bit rows out[k * words + w], bit b = 1 when signs[k][32 w + b] < 0,
  * words = (kfac + 31) / 32; then, at the next 16-byte boundary, the same matrix as bfloat16 +-1.0

@@ -231,6 +231,20 @@ def test_rmsnorm_quant_token_fused(cuda, m, k, had, bf16):
     assert np.all(np.abs(yof - yt) <= ulp)
 
 
+@pytest.mark.parametrize("m", [1, 33, 1000])
+@pytest.mark.parametrize("had", [False, True])
+def test_rmsnorm_quant_group_fused(cuda, m, had):
+    """RMS-norm fused in front of the group-128 quantiser (rows of 4096): bit-equal to oracle norm + oracle quantiser."""
+    x = (activations(4100 + m, m, 4096).astype(np.float32) * 3.0).astype(np.float16)
+    if m > 2:
+        x[2] = 0.0
+    q, s = cuda.rmsnorm_quant_group_sym_i4(_dev(x), 1e-5, hadamard=had)
+    yo = O.rmsnorm16(x, 1e-5)
+    qo, so = O.quant_group_sym(yo.reshape(-1, 128), had)
+    assert np.array_equal(s.cpu().numpy().view(np.uint16), so.view(np.uint16))
+    assert np.array_equal(q.cpu().numpy(), qo)
+
+
 def test_rmsnorm_quant_rejects_other_widths(cuda):
     x = torch.zeros((4, 2048), dtype=torch.float16, device="cuda")
     with pytest.raises(RuntimeError, match="4096"):
