@@ -113,7 +113,7 @@ def main(ref_root):
     out["lin_fwd_torch"] = y.numpy()
     out["lin_x_packed"] = xqp.numpy()
 
-    # --- (6) BASELINE config 1: CPU fake-quant linear, seed 0 ---------------------------
+    # --- (6) the CPU-runnable benchmark configuration: CPU fake-quant linear, seed 0 ---------------------------
     torch.manual_seed(0)
     X = torch.randn(16, 4096)
     ch = torch.randperm(4096)[:8]

@@ -61,7 +61,7 @@ def test_group_sym_edge_values(cuda):
 
 
 def test_group_sym_full_size(cuda):
-    # BASELINE sweep size M=4096, K=4096: round trip property + sampled oracle rows
+    # the benchmark sweep size M=4096, K=4096: round trip property + sampled oracle rows
     x = activations(77, 4096, 4096)
     q, s = cuda.hadamard_and_quantize_i4(_dev(x).view(-1, 128))
     q, s = q.cpu().numpy(), s.cpu().numpy()
@@ -252,7 +252,7 @@ def test_rmsnorm_quant_rejects_other_widths(cuda):
 
 
 def test_token_asym_full_size_property(cuda):
-    # BASELINE sweep M=4096, K=4096: sampled rows against the oracle + a checksum of all codes
+    # the benchmark sweep size M=4096, K=4096: sampled rows against the oracle + a checksum of all codes
     x = activations(88, 4096, 4096)
     q, s, z = cuda.quant_token_asym_i4(_dev(x), hadamard=True)
     q, s, z = q.cpu().numpy(), s.cpu().numpy(), z.cpu().numpy()

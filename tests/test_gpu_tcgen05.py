@@ -56,7 +56,7 @@ def test_tcgen05_n_multiple_of_128_only(cuda):
 
 
 def test_tcgen05_prefill_size_against_mma_path(cuda):
-    # BASELINE shape 4096 -> 12288 at M = 2048: too big for the CPU oracle in seconds, so the two
+    # the benchmark shape 4096 -> 12288 at M = 2048: too big for the CPU oracle in seconds, so the two
     # independent GPU paths must agree bit for bit, and sampled rows are checked against the oracle.
     ap, bp, sa, sb, za, _ = make_case(99, 2048, 12288, 4096, 128, 128, False)
     A, B, SA, SB = _dev(ap), _dev(bp), _dev(sa), _dev(sb)

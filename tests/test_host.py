@@ -104,7 +104,7 @@ def rs_scales():
 
 
 def test_weight_quantizer_channel_wise_matches_fake_quant(golden):
-    # BASELINE config 1 weights: W ~ N(0, 0.02) rotated by the 4096-point transform, per-channel symmetric RTN
+    # weights of the CPU-runnable benchmark configuration: W ~ N(0, 0.02) rotated by the 4096-point transform, per-channel symmetric RTN
     from flh_b200.nn import WeightQuantizer
     from flh_b200.hadamard import matmul_hadU
     torch.manual_seed(0)
