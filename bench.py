@@ -203,7 +203,7 @@ def run_ours(args, world, rank, local, dist):
                    clocks=cs.summary(), gpu_launches=steps)
         ach = step_bytes * steps / t / 1e9
         headline = (M, K) == (16384, 4096)
-        out["roofline"] = {"kernel": "quant_token_warp_kernel<false>" if K == 4096 and M >= 512 else "quant_token_asym_kernel", "bound": "hbm", "achieved": ach,
+        out["roofline"] = {"kernel": "quant_token_warp_kernel<f16, warps per row = %d, transform, no norm>" % (K // 4096) if K in (4096, 8192) and M >= 512 else "quant_token_factor_kernel" if K == 11008 and M >= 256 else "quant_token_asym_kernel", "bound": "hbm", "achieved": ach,
                            "peak": peaks["hbm_gbs"], "peak_src": peaks["src"], "unit": "GB/s",
                            "frac": ach / peaks["hbm_gbs"],
                            # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
