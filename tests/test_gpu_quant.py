@@ -123,6 +123,27 @@ def test_token_asym_tensor_core_factor(cuda, m, k):
     assert d.size == 0 or (d.max() <= 1 and (d != 0).mean() <= 1e-3), (d.max(), (d != 0).mean())
 
 
+def test_token_asym_tensor_core_factor_bf16_strided(cuda):
+    """The tcgen05 factor kernel (K = 11008, prefill-size batch) on bfloat16 input with a padded row stride and a
+    clip ratio: same stated tolerance as the binary16 case."""
+    m, k = 515, 11008
+    xf = activations(4200, m, k).astype(np.float32)
+    xf[5] = 0.0
+    bits = O.f32_to_bf16_bits(xf)
+    wide = torch.zeros((m, k + 64), dtype=torch.bfloat16, device="cuda")
+    wide[:, :k] = torch.from_numpy(bits.view(np.int16)).cuda().view(torch.bfloat16)
+    for clip in (1.0, 0.9):
+        q, s, z = cuda.quant_token_asym_i4(wide[:, :k], hadamard=True, clip=clip)
+        qo, so, zo = O.quant_token_asym(bits, True, clip=clip, bf16=True)
+        c, co = O.unpack_i4(q.cpu().numpy(), False), O.unpack_i4(qo, False)
+        sd = np.abs(s.cpu().numpy().view(np.uint16).astype(np.int32) - so.view(np.uint16).astype(np.int32))
+        zd = np.abs(z.cpu().numpy().astype(np.float32) - zo.astype(np.float32))
+        same = (sd == 0) & (zd == 0)
+        assert sd.max() <= 1 and zd.max() <= 1 and same.mean() >= 0.95
+        d = np.abs(c[same] - co[same])
+        assert d.max() <= 1 and (d != 0).mean() <= 1e-3, (d.max(), (d != 0).mean())
+
+
 @pytest.mark.parametrize("m,k", [(1, 4096), (7, 11008), (3, 192)])
 def test_token_asym_plain_and_clip(cuda, m, k):
     x = activations(3500 + k % 977, m, k)
