@@ -464,6 +464,11 @@ def run_reference(args, world, rank):
         print(json.dumps({"impl": "reference", "unavailable": "the CPU arm is implemented for the had_quant workload"}))
         return
     from oracle import fake_quant_port as FQ
+    # all the host threads this process may use (torchrun exports OMP_NUM_THREADS=1 to its workers)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except AttributeError:
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     K, rows = 4096, 2048
     H = FQ.hadamard_matrix(K)
     xs = [synth_activations(rows, K, 100 + i, "cpu") for i in range(2)]
