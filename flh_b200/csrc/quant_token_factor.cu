@@ -19,7 +19,8 @@
 namespace flh {
 namespace {
 
-constexpr int kThreadsF = 384;
+constexpr int kEpiWarps = 8;                       // 4: one epilogue warp per TMEM lane quarter; 8: two (column halves)
+constexpr int kThreadsF = 256 + 32 * kEpiWarps;
 __device__ int g_status_tf[4];
 
 struct FactorParams {
@@ -93,9 +94,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 // one or two per thread, the next one always in flight), run the six butterfly bits in registers, wait until the
 // previous pair's MMAs have released the 16-chunk slice of the A planes they write to (one mbarrier per K step of
 // the MMA, so writing overlaps the tail of the previous pair's MMAs), write the three bf16 planes, and one of them
-// issues the MMAs.  Warps 8-11 (128 threads) are the EPILOGUE: TMEM lane quarter warp % 4 (row of the pair =
-// quarter / 2); they read the accumulator twice (row min/max, then codes), hand the TMEM buffer back, and the two
-// warps of a row pack and store that row.  Producers and epilogue meet only through mbarriers (slice_free, acc_full,
+// issues the MMAs.  Warps 8-15 (256 threads) are the EPILOGUE: TMEM lane quarter warp % 4 (row of the pair =
+// quarter / 2), column half (warp - 8) / 4; they read the accumulator twice (row min/max, then codes), hand the
+// TMEM buffer back, and the four warps of a row pack and store that row.  Producers and epilogue meet only through mbarriers (slice_free, acc_full,
 // acc_empty) with bounded waits; named barriers join the warps of one role.  After a timeout every thread keeps
 // walking its loop (without MMAs) so that no named barrier is left waiting.
 __global__ void __launch_bounds__(kThreadsF, 1) quant_token_factor_kernel(const FactorParams p) {
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(kThreadsF, 1) quant_token_factor_kernel(const 
     }
     if (tid == 0) {
         for (int sl = 0; sl < Fp / 16; ++sl) mbar_init(slice_free(sl), 1);
-        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), kEpiWarps); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -260,11 +261,14 @@ __global__ void __launch_bounds__(kThreadsF, 1) quant_token_factor_kernel(const 
         }
     } else {
         // ================================================================= epilogue
-        const int eq = warp & 3;                                     // TMEM lane quarter
+        constexpr int kH = kEpiWarps / 4;                            // column parts per lane quarter
+        constexpr int kRowThreads = 64 * kH;                         // epilogue threads of one row
+        const int eq = warp & 3, eh = (warp - 8) >> 2;               // TMEM lane quarter, column part
         const int er = eq >> 1, ej = (eq & 1) * 32 + lane;           // row of the pair, position inside the chunk
-        const int et = ej;                                           // 0..63 among the two warps of this row
-        const int c_lo = 0, c_hi = Fp / 16;
-        const int rslot = eq & 1;                                    // this warp's slot in the row's reduction
+        const int et = eh * 64 + ej;                                 // index among the epilogue threads of this row
+        const int nch = Fp / 16;
+        const int c_lo = kH == 1 ? 0 : (eh == 0 ? 0 : (nch + 1) / 2), c_hi = kH == 1 ? nch : (eh == 0 ? (nch + 1) / 2 : nch);
+        const int rslot = (eq & 1) * kH + eh;                        // this warp's slot in the row's reduction
         bool ok = true;
         long it = 0;
         for (long pair = blockIdx.x; pair < npairs; pair += gridDim.x, ++it) {
@@ -317,11 +321,11 @@ __global__ void __launch_bounds__(kThreadsF, 1) quant_token_factor_kernel(const 
                 }
             }
             const float vmin = warp_min(fminf(mn[0], mn[1])), vmax = warp_max(fmaxf(mx[0], mx[1]));
-            if (lane == 0) { red[(er * 2 + rslot) * 2] = vmin; red[(er * 2 + rslot) * 2 + 1] = vmax; }
-            bar_sync_named(2 + er, 64);                              // the two warps of this row
+            if (lane == 0) { red[(er * 2 * kH + rslot) * 2] = vmin; red[(er * 2 * kH + rslot) * 2 + 1] = vmax; }
+            bar_sync_named(2 + er, kRowThreads);                     // the epilogue warps of this row
             float a = 0.0f, b = 0.0f;
 #pragma unroll
-            for (int g = 0; g < 2; ++g) { a = fminf(a, red[(er * 2 + g) * 2]); b = fmaxf(b, red[(er * 2 + g) * 2 + 1]); }
+            for (int g = 0; g < 2 * kH; ++g) { a = fminf(a, red[(er * 2 * kH + g) * 2]); b = fmaxf(b, red[(er * 2 * kH + g) * 2 + 1]); }
             const TokenRowParams rp = token_row_params(a, b, p.clip, p.c);
             const long row = 2 * pair + er;
             if (et == 0 && row < p.M && ok) { p.scale[row] = rp.scale; p.zero[row] = __float2half_rn(rp.zero); }
@@ -377,11 +381,11 @@ __global__ void __launch_bounds__(kThreadsF, 1) quant_token_factor_kernel(const 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty(buf));              // this warp is done with the TMEM buffer
-            bar_sync_named(2 + er, 64);                              // the codes of this row are staged
+            bar_sync_named(2 + er, kRowThreads);                     // the codes of this row are staged
             if (row < p.M && ok) {
                 const int per_row = K >> 4;
                 uint2 *qrow = reinterpret_cast<uint2 *>(p.q + row * (long)(K >> 1));
-                for (int i = et; i < per_row; i += 64) qrow[i] = pack16(*reinterpret_cast<const uint4 *>(cb + er * K + 16 * i));
+                for (int i = et; i < per_row; i += kRowThreads) qrow[i] = pack16(*reinterpret_cast<const uint4 *>(cb + er * K + 16 * i));
             }
             // (the next pair's first named barrier orders these reads before the next writes of cb and red)
         }
