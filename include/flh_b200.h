@@ -87,7 +87,7 @@ int flh_b200_hadamard_f16_inplace(void *x, long rows, int n, void *stream);
  * scale.  The kfac x kfac factor is applied on the tensor cores with hadamard = 1 and kfac >= 64 (exact 3-term
  * bfloat16 split of the binary32 inputs, binary32 accumulation: same value up to the order of the
  * roundings; the reference's own matmul has no fixed order either) or, with hadamard = 2, summed
- * k' ascending on the CUDA cores (bit-exact with the CPU oracle, ~10x slower for kfac = 172).
+ * k' ascending on the CUDA cores (bit-exact with the CPU oracle, about five times slower for kfac = 172).
  * Quantiser: ActQuantizer.find_params / asym_quant (fake_quant/quant_utils.py:94-128, 17-21)
  * with the scale rounded to f16 before use.  q [M, K/2] codes 0..15; scale, zero [M] f16.
  * clip = the quantiser's clip_ratio in (0, 1]. */
