@@ -7,6 +7,7 @@ Workloads (synthetic, seeded; shapes from the reference's benchmark configuratio
   had_quant     (default) fused full-width Hadamard + per-token asymmetric int4 quantiser + packing,
                 f16 X [16384, 4096] ~ N(0,1) with 0.1 % outlier channels x20; metric = algorithmic GB/s
                 (bytes = M * (2K + K/2 + 4)).  One step = one launch over one batch.
+  norm_quant    fused RMS-norm + per-token asymmetric int4 (the decoder's hidden-state step); --rows / --k.
   gemm_prefill  int4 GEMM + dequant, M = 2048, 4096 -> 12288, group-128 scales; metric = TOPS (2MNK).
   gemm_decode   int4 GEMM + dequant, M = 16, 4096 -> 22016; metric = GB/s on packed-weight bytes.
 The default run also measures the other kernels briefly and reports them under "extra".
@@ -252,6 +253,26 @@ def run_ours(args, world, rank, local, dist):
             out["extra"] = extras(C, device, peaks)
             if world == 1:
                 out["cpu_baseline"] = cpu_had_quant(K, sample_rows=1024, reps=8)
+    elif args.workload == "norm_quant":
+        # the decoder's hidden-state step: RMS-norm (weight 1) + per-token asymmetric int4 + pack, no transform
+        M, K = args.rows, args.k
+        xs = [synth_activations(M, K, 100 + i + 10 * rank, device) for i in range(3)]
+        step_bytes = M * (2 * K + K // 2 + 4)
+
+        def fn(i):
+            C.rmsnorm_quant_token_asym_i4(xs[i % 3], 1e-5, hadamard=False)
+
+        with ClockSampler(local) as cs:
+            t = timed_loop(fn, steps, warmup, dist, device, sampler=cs)
+        ach = step_bytes * steps / t / 1e9
+        out.update(metric="norm_quant_GBps", unit="GB/s", value=world * ach, ms_per_step=t / steps * 1e3, dtype="f32",
+                   config={"workload": f"fused RMS-norm + per-token asymmetric int4 quant + pack (no transform), f16 X[{M},{K}] per GPU",
+                           "M_per_gpu": M, "K": K, "bytes_per_step_per_gpu": step_bytes,
+                           "l2": f"three rotating {M * K * 2 // 1000000} MB inputs", "parallelism": f"token-sharded x{world}, no collective"},
+                   clocks=cs.summary(), gpu_launches=steps,
+                   roofline={"kernel": "quant_token_warp_kernel<f16, warps per row = %d, no transform, norm>" % (K // 4096), "bound": "hbm",
+                             "achieved": ach, "peak": peaks["hbm_gbs"], "peak_src": peaks["src"], "unit": "GB/s",
+                             "frac": ach / peaks["hbm_gbs"], "traffic": None})
     elif args.workload == "had_quant_group":
         # FLH's own CUDA contract: group-128 binary16 transform + symmetric int4 + pack
         M, K = 16384, 4096
