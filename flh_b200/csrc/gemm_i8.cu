@@ -200,7 +200,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int it = 0, u = 0;
             bool ok = true;
             unsigned long long w2 = 0, w3 = 0, w4 = 0;
-            for (int tile = first; tile < p.num_tiles && ok; tile += step, ++u) {
+            // The outcome of the wait is made warp-uniform by a vote, and a warp that gave up keeps walking the tile loop
+        // (no waits, no TMEM reads, no stores): the four warps meet at named barriers and at warp-wide tcgen05.ld, so
+        // none of them may leave alone.
+        for (int tile = first; tile < p.num_tiles; tile += step, ++u) {
                 const int buf = u & 1;
                 if (u >= 2 && !wait_i8(acc_empty(buf), ((u >> 1) & 1) ^ 1, abort_flag, 12, &w2)) { ok = false; break; }
                 for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -229,7 +232,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t tlane = tmem + ((uint32_t)(wq * 32) << 16);
         int u = 0;
         bool ok = true;
-        for (int tile = first; tile < p.num_tiles && ok; tile += step, ++u) {
+        // The outcome of the wait is made warp-uniform by a vote, and a warp that gave up keeps walking the tile loop
+        // (no waits, no TMEM reads, no stores): the four warps meet at named barriers and at warp-wide tcgen05.ld, so
+        // none of them may leave alone.
+        for (int tile = first; tile < p.num_tiles; tile += step, ++u) {
             const int m0 = (tile % p.m_blocks) * (PAIR ? 2 * BM : BM) + (int)rank * BM;
             const int n0 = (tile / p.m_blocks) * BN;
             const int row = m0 + wq * 32 + lane;
@@ -243,10 +249,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const float sa = __half2float(p.a_scale[rowc]) * (1.0f / 256.0f);
             const int za = A_UNSIGNED ? (int)__half2float(p.a_zero[rowc]) : 0;
             const int buf = u & 1;
-            if (!wait_i8(acc_full(buf), (u >> 1) & 1, abort_flag, 16)) { ok = false; break; }
+            ok = __all_sync(0xffffffffu, ok && wait_i8(acc_full(buf), (u >> 1) & 1, abort_flag, 16));
             tc_fence_after();
 #pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
+            for (int cc = 0; cc < BN / 32 && ok; ++cc) {
                 uint32_t v[32];
                 tc_ld32(tlane + buf * BN + cc * 32, v);
                 tc_wait_ld();

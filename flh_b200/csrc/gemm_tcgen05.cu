@@ -373,7 +373,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         unsigned long long w6 = 0;
 
-        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        // A wait that runs out must not split the warpgroup: its threads meet at named barriers and at warp-wide
+        // tcgen05.ld.  So the outcome of every wait is made warp-uniform by a vote, and a warp that gave up keeps
+        // walking the loops (no waits, no TMEM reads, no stores) and still reaches every named barrier.
+        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
             const int m0 = (tile % p.m_blocks) * BM, n0 = (tile / p.m_blocks) * BN;
             const int row = m0 + wq * 32 + lane;
             const int rowc = row < p.M ? row : p.M - 1;
@@ -399,12 +402,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (!A_UNSIGNED) sa *= (1.0f / 256.0f);
                     const int za = A_UNSIGNED ? (int)__half2float(p.a_zero[(long)rowc * p.ga_cols + gas * kb]) : 0;
                     const uint64_t sa2 = pack2(sa, sa);
-                    if (!mbar_wait(acc_full(buf), (u >> 1) & 1, abort_flag, 6, &w6)) { ok = false; break; }
+                    ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full(buf), (u >> 1) & 1, abort_flag, 6, &w6));
                     tc_fence_after();
                     const float *sb = sbuf + slot * BN + cbase;
                     const int *rs = rbuf + slot * BN + cbase;
 #pragma unroll
                     for (int cc = 0; cc < 4; ++cc) {
+                        if (!ok) break;
                         uint32_t v[32];
                         tc_ld32(tlane + buf * BN + cc * 32, v);
                         tc_wait_ld();
@@ -447,10 +451,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const float sa = __half2float(p.a_scale[rowc]) * (1.0f / 256.0f);
                 const int za = A_UNSIGNED ? (int)__half2float(p.a_zero[rowc]) : 0;
                 const int buf = u & 1;
-                if (!mbar_wait(acc_full(buf), (u >> 1) & 1, abort_flag, 7, &w6)) { ok = false; break; }
+                ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full(buf), (u >> 1) & 1, abort_flag, 7, &w6));
                 tc_fence_after();
 #pragma unroll 1
-                for (int cc = 0; cc < BN / 32; ++cc) {
+                for (int cc = 0; cc < BN / 32 && ok; ++cc) {
                     uint32_t v[32];
                     tc_ld32(tlane + buf * BN + cc * 32, v);
                     tc_wait_ld();

@@ -129,12 +129,17 @@ class DecoderLayer(torch.nn.Module):
         qh = rope(qh.view(B, S, self.nh, hd), pos, cfg.rope_theta).transpose(1, 2)
         kh = rope(kh.view(B, S, self.nkv, hd), pos, cfg.rope_theta).transpose(1, 2)
         vh = vh.view(B, S, self.nkv, hd).transpose(1, 2)
+        mask, causal = None, S > 1
         if cache is not None:
             kc, vc, cur = cache
             kc[:, :, cur:cur + S] = kh
             vc[:, :, cur:cur + S] = vh
             kh, vh = kc[:, :, :cur + S], vc[:, :, :cur + S]
-        att = F.scaled_dot_product_attention(qh, kh, vh, is_causal=(S > 1), enable_gqa=self.nh != self.nkv)
+            if cur > 0 and S > 1:
+                # a chunk appended to a filled cache: query i sees keys 0 .. cur + i (torch's is_causal aligns the
+                # triangle with the top-left corner, which is only right for cur = 0)
+                mask, causal = torch.ones(S, cur + S, dtype=torch.bool, device=x.device).tril(diagonal=cur), False
+        att = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, is_causal=causal, enable_gqa=self.nh != self.nkv)
         att = att.transpose(1, 2).reshape(B, S, self.nh * hd)
         s, z, q = self.q_attn(att)
         x = x + self.o(q, s, z)

@@ -187,6 +187,9 @@ class LinearFLH(torch.nn.Module):
             self.bias = None
         self._rowsum = None
         self._w_i8 = None          # optional int8 copy of the weights for large-batch GEMMs (prepack_int8)
+        # 0: no full-width rotation on the input side; b >= 1: the weight was rotated with matmul_hadU over b equal
+        # blocks of K (b = 1 is the plain full-width transform; b = tp is what a row-parallel shard needs)
+        self.full_hadamard_blocks = 0
 
     # -- offline side ---------------------------------------------------------------------------
     def _pack_weights(self, w_int, scale, zero):
@@ -209,10 +212,12 @@ class LinearFLH(torch.nn.Module):
     @staticmethod
     def from_float(module: torch.nn.Linear, weight_bits=4, weight_group_size=128, weight_sym=True,
                    dual_hadamard=False, in_group_size=None, out_group_size=None, clip_ratio=1.0,
-                   no_hadamard=False, full_hadamard=False):
+                   no_hadamard=False, full_hadamard=False, hadamard_blocks=1):
         """flh/nn/linear.py:190-285: rotate the weight on its input side (block-diagonal groups of
         in_group_size, or the full-width matmul_hadU transform with full_hadamard=True), optionally
-        on its output side too, then RTN-quantise and pack."""
+        on its output side too, then RTN-quantise and pack.  hadamard_blocks = b applies the full-width
+        transform to each of b equal blocks of K instead of to K as a whole: a row-parallel layer split over
+        b ranks rotates each rank's K / b activations on its own, so its weight must be rotated the same way."""
         assert weight_bits == 4 and weight_sym, "the packed path stores symmetric int4 weights"
         W = module.weight.data.clone()
         lin = LinearFLH(module.in_features, module.out_features, bias=module.bias is not None, dtype=W.dtype,
@@ -221,7 +226,13 @@ class LinearFLH(torch.nn.Module):
         if module.bias is not None:
             lin.bias.copy_(module.bias.data)
         if not no_hadamard:
-            W = matmul_hadU(W.double()).to(W.dtype) if full_hadamard else hadamard_group(W, in_group_size or -1)
+            if full_hadamard:
+                N_, K_ = W.shape
+                assert K_ % hadamard_blocks == 0, "K must split evenly into hadamard_blocks"
+                W = matmul_hadU(W.double().reshape(N_, hadamard_blocks, K_ // hadamard_blocks)).reshape(N_, K_).to(W.dtype)
+                lin.full_hadamard_blocks = hadamard_blocks
+            else:
+                W = hadamard_group(W, in_group_size or -1)
             if dual_hadamard:
                 W = hadamard_group(W.T.contiguous(), out_group_size or -1).T.contiguous()
                 if module.bias is not None:

@@ -20,9 +20,11 @@ from .nn import LinearFLH
 
 
 def _clone_meta(lin: LinearFLH, in_features: int, out_features: int) -> LinearFLH:
-    return LinearFLH(in_features, out_features, bias=lin.bias is not None, dtype=lin.w_scale.dtype,
-                     device=lin.w_packed.device, dual_hadamard=lin.dual_hadamard, in_group_size=lin.in_group_size,
-                     out_group_size=lin.out_group_size, no_hadamard=lin.no_hadamard, group_size=lin.weight_group_size)
+    out = LinearFLH(in_features, out_features, bias=lin.bias is not None, dtype=lin.w_scale.dtype,
+                    device=lin.w_packed.device, dual_hadamard=lin.dual_hadamard, in_group_size=lin.in_group_size,
+                    out_group_size=lin.out_group_size, no_hadamard=lin.no_hadamard, group_size=lin.weight_group_size)
+    out.full_hadamard_blocks = lin.full_hadamard_blocks
+    return out
 
 
 def shard_column(lin: LinearFLH, rank: int, world: int) -> LinearFLH:
@@ -41,11 +43,19 @@ def shard_column(lin: LinearFLH, rank: int, world: int) -> LinearFLH:
 
 def shard_row(lin: LinearFLH, rank: int, world: int) -> LinearFLH:
     """Columns [rank*K/world, (rank+1)*K/world) of every weight row.  The bias stays on rank 0 only, so
-    that the all-reduced sum carries it once."""
+    that the all-reduced sum carries it once.  A weight rotated with the full-width transform can only be
+    split where the transform is block-diagonal: it must have been made with
+    LinearFLH.from_float(full_hadamard=True, hadamard_blocks=world), because each rank rotates its K / world
+    activations by themselves and (W H_K)[:, shard] is not W[:, shard] H_{K/world}."""
     N, K = lin.out_features, lin.in_features
     assert K % world == 0 and (K // world) % 128 == 0, "K / tp must be a multiple of 128"
+    if lin.full_hadamard_blocks not in (0, world) and world > 1:
+        raise ValueError(f"this weight was rotated over {lin.full_hadamard_blocks} block(s) of K; a row-parallel split over "
+                         f"{world} ranks needs from_float(full_hadamard=True, hadamard_blocks={world})")
     k = K // world
     out = _clone_meta(lin, k, N)
+    if lin.full_hadamard_blocks:
+        out.full_hadamard_blocks = 1                # the shard's own K is rotated as a whole
     out.w_packed.copy_(lin.w_packed.view(N, K // 2)[:, rank * k // 2:(rank + 1) * k // 2].reshape(-1))
     g = lin.w_scale.shape[1]
     if g > 1:

@@ -196,7 +196,8 @@ int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group);
  *     Shapes that need no split (many output columns) run the plain streaming kernel, scratch untouched.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
  *     that first call outside any stream capture.  Every GPU that loads the library carries the array
- *     until the process exits.
+ *     until the process exits.  The looked-up address is kept in a plain per-device table: two host threads
+ *     making the first call on one device at the same moment both look it up and store the same value.
  *   - All calls on a device share the one array and it keeps the previous call's contents; each call
  *     re-zeroes the counters on `stream` before the kernel.  Two calls whose kernels could overlap on the
  *     GPU (different streams, no ordering between them) race on it: order them or use the workspace form.

@@ -155,4 +155,6 @@ def pack_nib(q):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and not os.environ.get("FLH_REFERENCE"):
+        raise SystemExit("usage: %s <FLH checkout>   (or set FLH_REFERENCE)" % sys.argv[0])
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["FLH_REFERENCE"])

@@ -86,6 +86,28 @@ def _worker(rank, world, port, tmp):
             if not asym:    # same quantised activations as the full layer: only the summation order differs
                 err = (y_row.float() - y_full.float()).abs().max() / y_full.float().abs().max()
                 assert err < 2e-3, f"row-parallel vs single device: {err}"
+        # row-parallel with the online full-width transform (the down_proj of the per-token mode): every rank rotates
+        # its own K / tp activations, so the weight is rotated per block of K / tp = 3584 = 28 * 128; the summed output
+        # must approximate the float layer x @ W^T as well as the single-device layer does
+        K, N, M = 7168, 128, 4
+        lin = torch.nn.Linear(K, N, bias=False)
+        lin.weight.data = torch.randn(N, K, generator=g) * 0.02
+        x = torch.randn(M, K, generator=g).half()
+        ref = x.float() @ lin.weight.data.half().float().t()
+        whole = LinearFLH.from_float(lin.half(), weight_group_size=-1, full_hadamard=True)
+        with pytest.raises(ValueError):
+            shard_row(whole, rank, world)                    # rotated over K as a whole: not splittable
+        q, s, z = O.quant_token_asym(x.numpy(), True)
+        y_whole = whole(torch.from_numpy(q), torch.from_numpy(s).view(M, 1), torch.from_numpy(z).view(M, 1))
+        blocked = LinearFLH.from_float(lin.half(), weight_group_size=-1, full_hadamard=True, hadamard_blocks=world)
+        kk = K // world
+        qm, sm, zm = O.quant_token_asym(np.ascontiguousarray(x.numpy()[:, rank * kk:(rank + 1) * kk]), True)
+        row = RowParallelLinearFLH(shard_row(blocked, rank, world))
+        y_row = row(torch.from_numpy(qm), torch.from_numpy(sm).view(M, 1), torch.from_numpy(zm).view(M, 1))
+        # W4A4 quantisation noise, as a relative Frobenius error; a shard rotated the wrong way is uncorrelated (~1.4)
+        err_whole = (y_whole.float() - ref).norm() / ref.norm()
+        err_row = (y_row.float() - ref).norm() / ref.norm()
+        assert err_whole < 0.3 and err_row < 1.5 * err_whole + 0.02, (err_row, err_whole)
         if rank == 0:
             open(os.path.join(tmp, "ok"), "w").write("ok")
     finally:
