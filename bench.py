@@ -43,6 +43,17 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
 
 
+def recorded_traffic(kernel, M, K):
+    """DRAM bytes per launch of `kernel` at this shape, as recorded in its ncu summary under profiles/ (a line
+    `dram_bytes_per_launch: <number>`); (None, reason) when no summary of this kernel and shape is committed."""
+    import re
+    path = os.path.join(ROOT, "profiles", f"{kernel}_M{M}_K{K}.md")
+    if not os.path.exists(path):
+        return None, f"no profiles/{os.path.basename(path)}"
+    m = re.search(r"dram_bytes_per_launch:\s*([0-9.eE+]+)", open(path).read())
+    return (float(m.group(1)), f"recorded from profiles/{os.path.basename(path)} (ncu)") if m else (None, "no dram_bytes_per_launch line")
+
+
 def synth_activations(m, k, seed, device, dtype=torch.float16):
     g = torch.Generator(device="cpu").manual_seed(seed)
     x = torch.randn(m, k, generator=g)
@@ -53,7 +64,10 @@ def synth_activations(m, k, seed, device, dtype=torch.float16):
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs.  The NVML handle is
+    looked up by the UUID of the CUDA device (NVML numbers every GPU of the host, CUDA only the visible ones)."""
+
+    PERIOD_S = 0.02          # 50 Hz: enough for a region of a few ms upward, and no load on the launching thread
 
     def __init__(self, index):
         self.samples, self.reasons, self.max_mhz = [], set(), None
@@ -63,7 +77,13 @@ class ClockSampler:
             import pynvml
             pynvml.nvmlInit()
             self.nv = pynvml
-            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            uuid = str(torch.cuda.get_device_properties(index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except TypeError:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
         except Exception:
             self.nv = None
@@ -83,7 +103,7 @@ class ClockSampler:
                         self.reasons.add(k)
             except Exception:
                 pass
-            time.sleep(0.001)
+            time.sleep(self.PERIOD_S)
 
     def __enter__(self):
         if self.nv:
@@ -120,7 +140,7 @@ def dist_setup(args):
     return world, rank, local, None
 
 
-def timed_loop(fn, steps, warmup, dist, device, graph=False, sampler=None):
+def timed_loop(fn, steps, warmup, dist, device, graph=False, sampler=None, settle_s=0.0):
     """W warm-up steps, then exactly `steps` steps between barrier+synchronize; CUDA events on the
     current stream; returns seconds (max over ranks).  graph=True: the `steps` steps are recorded into
     one CUDA graph (after the warm-up) and the timed region is its launch — for steps shorter than the
@@ -136,6 +156,11 @@ def timed_loop(fn, steps, warmup, dist, device, graph=False, sampler=None):
                 fn(i)
         g.replay()          # one untimed replay
         torch.cuda.synchronize()
+        if settle_s > 0:    # the same launches for a while, untimed: the clock sampler sees the GPU under this load
+            t_end = time.perf_counter() + settle_s
+            while time.perf_counter() < t_end:
+                g.replay()
+                torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
@@ -188,28 +213,38 @@ def run_ours(args, world, rank, local, dist):
         M, K = args.rows, args.k
         xs = [synth_activations(M, K, 100 + i + 10 * rank, device) for i in range(3)]   # 3 x 134 MB > L2
         step_bytes = M * (2 * K + K // 2 + 4)
+        # caller-owned outputs: the timed loop allocates nothing
+        outs3 = [(torch.empty((M, K // 2), dtype=torch.uint8, device=device), torch.empty((M,), dtype=torch.float16, device=device),
+                  torch.empty((M,), dtype=torch.float16, device=device)) for _ in range(3)]
+        exact = bool(args.exact)
 
         def fn(i):
-            C.quant_token_asym_i4(xs[i % 3], hadamard=True)
+            C.quant_token_asym_i4(xs[i % 3], hadamard=True, exact=exact, out=outs3[i % 3])
 
+        # the K steps are recorded once into a CUDA graph and the timed region is its launch: a step is a 30-50 us kernel,
+        # shorter than what the host may need per launch when eight ranks share the cores
         with ClockSampler(local) as cs:
-            t = timed_loop(fn, steps, warmup, dist, device, sampler=cs)
+            t = timed_loop(fn, steps, warmup, dist, device, sampler=cs, graph=True, settle_s=0.15)
         value = world * step_bytes * steps / t / 1e9
+        kfac = C._sign_bits(K, device)[0]
+        kernel = _lib.load().flh_b200_quant_token_kernel(M, K, 2 if exact else 1, kfac).decode()
         out.update(metric="had_quant_GBps", unit="GB/s", value=value, ms_per_step=t / steps * 1e3, dtype="f32",
-                   config={"workload": "fused full-width Hadamard (binary32) + per-token asymmetric int4 quant + pack, "
+                   config={"workload": "fused full-width Hadamard (binary32 accumulation) + per-token asymmetric int4 quant + pack, "
                                        f"f16 X[{M},{K}] per GPU, 0.1% outlier channels x20",
                            "M_per_gpu": M, "K": K, "bytes_per_step_per_gpu": step_bytes,
+                           "transform": "reference summation order (bit-exact)" if exact else "high part on tcgen05 (default; <= 0.1 % of codes off by one vs the reference order)",
                            "l2": f"three rotating {M * K * 2 // 1000000} MB inputs" + (", each larger than the 126 MB L2" if M * K * 2 > L2_BYTES else ""),
+                           "timing": f"the {steps} steps recorded into one CUDA graph, timed as one replay; outputs pre-allocated",
                            "parallelism": f"token-sharded x{world}, no collective"},
-                   clocks=cs.summary(), gpu_launches=steps)
+                   clocks=dict(cs.summary(), window="150 ms of the same launches directly before the timed region, and the timed region"),
+                   gpu_launches=steps)
         ach = step_bytes * steps / t / 1e9
-        headline = (M, K) == (16384, 4096)
-        out["roofline"] = {"kernel": "quant_token_warp_kernel<f16, warps per row = %d, transform, no norm>" % (K // 4096) if K in (4096, 8192) and M >= 512 else "quant_token_factor_kernel" if K == 11008 and M >= 256 else "quant_token_asym_kernel", "bound": "hbm", "achieved": ach,
+        traffic, traffic_src = recorded_traffic(kernel, M, K)
+        out["roofline"] = {"kernel": kernel, "bound": "hbm", "achieved": ach,
                            "peak": peaks["hbm_gbs"], "peak_src": peaks["src"], "unit": "GB/s",
                            "frac": ach / peaks["hbm_gbs"],
-                           # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
-                           # summarised in profiles/quant_token_asym_M16384_K4096.md (134.3 MB + 17.4 MB)
-                           "traffic": 151.8e6 if headline else None, "traffic_unit": "bytes/launch (ncu)", "algorithmic_bytes": step_bytes}
+                           # dram__bytes_read.sum + dram__bytes_write.sum of one launch, read from the ncu summary of this kernel
+                           "traffic": traffic, "traffic_unit": "bytes/launch", "traffic_src": traffic_src, "algorithmic_bytes": step_bytes}
         # ---- end to end through the public API with host buffers ----
         xh = [x.cpu().pin_memory() for x in xs[:2]]
         qh = torch.empty((M, K // 2), dtype=torch.uint8).pin_memory()
@@ -225,7 +260,6 @@ def run_ours(args, world, rank, local, dist):
         ev_in = [torch.cuda.Event() for _ in range(2)]
         ev_used = [torch.cuda.Event() for _ in range(2)]       # the kernel has consumed xd[b]
         ev_out = [torch.cuda.Event() for _ in range(2)]        # the results of buffer set b are on the host
-        outs = [None, None]
 
         def e2e(i):
             b = i % 2
@@ -235,8 +269,7 @@ def run_ours(args, world, rank, local, dist):
                 ev_in[b].record(s_in)
             main.wait_event(ev_in[b])
             main.wait_event(ev_out[b])                         # the previous results of this set have left the device
-            q, s_, z = C.quant_token_asym_i4(xd[b], hadamard=True)
-            outs[b] = (q, s_, z)                               # keep the device tensors alive until they are copied
+            q, s_, z = C.quant_token_asym_i4(xd[b], hadamard=True, exact=exact, out=outs3[b])
             ev_used[b].record(main)
             s_out.wait_event(ev_used[b])
             with torch.cuda.stream(s_out):
@@ -249,8 +282,16 @@ def run_ours(args, world, rank, local, dist):
         out["e2e"] = {"value": world * step_bytes * steps / te / 1e9, "unit": "GB/s",
                       "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * K // 2 + 4 * M,
                       "ms_per_step": te / steps * 1e3}
+        tp = None
+        if world > 1 and not args.no_extra:       # collective work: every rank takes part
+            try:
+                tp = tp_extras(C, dist, world, rank, device)
+            except Exception as e:                # the headline line must still be printed
+                tp = {"tp_extras_error": repr(e)}
         if rank == 0 and not args.no_extra:
-            out["extra"] = extras(C, device, peaks)
+            out["extra"] = extras(C, device, peaks) if world == 1 else {}
+            if tp:
+                out["extra"].update(tp)
             if world == 1:
                 out["cpu_baseline"] = cpu_had_quant(K, sample_rows=1024, reps=8)
     elif args.workload == "norm_quant":
@@ -382,6 +423,101 @@ def run_ours(args, world, rank, local, dist):
         out["device_status"] = st
     if rank == 0:
         print(json.dumps(out), flush=True)
+
+
+def tp_extras(C, dist, world, rank, device, layers=8):
+    """Tensor-parallel side measurements, run by every rank when WORLD_SIZE > 1 (the headline stays the token-sharded
+    quantiser): a row-parallel layer checked against a single-GPU run that sums the same per-shard partial outputs in
+    binary32; the all-reduce by itself at the two message sizes of the 70B-shaped model; and that model (`layers`
+    layers) in prefill and decode with a per-component CUDA-event breakdown."""
+    from flh_b200 import timing
+    from flh_b200.model import Decoder, DecoderConfig, LLAMA3_70B
+    from flh_b200.nn import ActQuantizer, LinearFLH
+    from flh_b200.tp import RowParallelLinearFLH, shard_row
+    ex = {}
+    # ---- (1) row-parallel parity: o_proj of the 70B shape (8192 -> 8192), 256 tokens, both activation modes ----
+    K, N, M = 8192, 8192, 256
+    g = torch.Generator(device="cpu").manual_seed(1234)                  # same tensors on every rank
+    for mode in ("group_sym", "token_asym"):
+        sym = mode == "group_sym"
+        full = LinearFLH(K, N, dtype=torch.float16, device=device, group_size=128 if sym else -1, in_group_size=128)
+        full.w_packed.copy_(torch.randint(0, 256, full.w_packed.shape, dtype=torch.uint8, generator=g).to(device))
+        full.w_scale.copy_((torch.rand(full.w_scale.shape, generator=g) * 0.015 + 0.005).half().to(device))
+        x = torch.randn(M, K, generator=g).half().to(device)
+        aq = ActQuantizer(bits=4, group_size=128 if sym else -1, sym=sym, use_hadamard=False, packed_output=True)
+        kk = K // world
+        parts = []
+        for r in range(world):                                           # every rank can form every partial: inputs are replicated
+            parts.append(shard_row(full, r, world)(*_reorder(aq(x[:, r * kk:(r + 1) * kk].contiguous()))))
+        ref = torch.stack([p_.float() for p_ in parts]).sum(0)           # binary32 sum of the f16 partials
+        y = RowParallelLinearFLH(shard_row(full, rank, world))(*_reorder(aq(x[:, rank * kk:(rank + 1) * kk].contiguous())))
+        rel = ((y.float() - ref).abs().max() / ref.abs().max()).reshape(1)
+        dist.all_reduce(rel, op=dist.ReduceOp.MAX)
+        ex[f"tp_parity_max_rel_{mode}"] = float(rel.item())
+        del full, parts
+    ex["tp_parity_max_rel"] = max(ex["tp_parity_max_rel_group_sym"], ex["tp_parity_max_rel_token_asym"])
+    ex["tp_parity_bound"] = 1e-3
+    # ---- (2) the all-reduce by itself: 134 MB (prefill 4 x 2048 x 8192 f16) and 1 MB (decode 64 x 8192 f16) ----
+    for name, numel, iters in (("134MB", 4 * 2048 * 8192, 10), ("1MB", 64 * 8192, 50)):
+        buf = torch.zeros(numel, dtype=torch.float16, device=device)
+        for _ in range(3):
+            dist.all_reduce(buf)
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            dist.all_reduce(buf)
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e-3 / iters], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t = float(t.item())
+        if name == "134MB":
+            ex["allreduce_134MB_busbw_GBps"] = 2.0 * (world - 1) / world * numel * 2 / t / 1e9
+            ex["allreduce_134MB_ms"] = t * 1e3
+        else:
+            ex["allreduce_1MB_us"] = t * 1e6
+        del buf
+    # ---- (3) the 70B-shaped decoder, `layers` layers, TP = world: tok/s and where the device time goes ----
+    for mode in ("token_asym", "group_sym"):
+        cfg = DecoderConfig(**dict(LLAMA3_70B, n_layers=layers), vocab=32000, act_mode=mode, tp=world)
+        model = Decoder(cfg, device, seed=0, group=None, with_head=True)
+        if mode == "token_asym":
+            model.prepack_int8()
+        ids = torch.randint(100, 200, (4, 2048), device=device)
+        t = timed_loop(lambda i: model(ids), 3, 3, dist, device)
+        ex[f"llama70b_{layers}L_prefill_tok_per_s_{mode}"] = 4 * 2048 * 3 / t
+        with timing.collect() as tc:
+            model(ids)
+        ex[f"llama70b_{layers}L_prefill_breakdown_ms_{mode}"] = {k_: round(v, 3) for k_, v in tc.summary().items()}
+        if mode == "token_asym":
+            ex["llama70b_%dL_prefill_tok_per_s" % layers] = ex[f"llama70b_{layers}L_prefill_tok_per_s_{mode}"]
+            B, ctx = 64, 1024
+            cache = model.new_cache(B, ctx + 8)
+            for c in cache:
+                c[0].normal_(); c[1].normal_()
+            ids1 = torch.randint(100, 200, (B, 1), device=device)
+            fn = lambda i: model(ids1, cache=cache, start=ctx)
+            try:
+                t = timed_loop(fn, 10, 3, dist, device, graph=True)
+                ex["llama70b_%dL_decode_cuda_graph" % layers] = True
+            except Exception as e:
+                sys.stderr.write(f"decode graph capture failed ({e}); timing plain launches\n")
+                t = timed_loop(fn, 10, 3, dist, device)
+                ex["llama70b_%dL_decode_cuda_graph" % layers] = False
+            ex["llama70b_%dL_decode_tok_per_s" % layers] = B * 10 / t
+            with timing.collect() as tc:
+                fn(0)
+            ex[f"llama70b_{layers}L_decode_breakdown_ms_eager"] = {k_: round(v, 3) for k_, v in tc.summary().items()}
+            del cache
+        del model
+        torch.cuda.empty_cache()
+    return ex
+
+
+def _reorder(szq):
+    """ActQuantizer returns (scale, zero, packed); the linears take (packed, scale, zero)."""
+    s_, z_, q_ = szq
+    return q_, s_, z_
 
 
 def _time(fn, iters=10, warm=3, graph=False):
@@ -526,6 +662,7 @@ def main():
     ap.add_argument("--k", type=int, default=4096, help="had_quant: hidden size K (default: the headline 4096)")
     ap.add_argument("--prepack", action="store_true",
                     help="gemm_prefill / llama*_prefill with token_asym: keep an int8 copy of the weights (expanded once, outside the timed region)")
+    ap.add_argument("--exact", action="store_true", help="had_quant: the transform in the reference's summation order (bit-exact mode) instead of the default")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements and the CPU baseline (profiling runs)")
     args = ap.parse_args()
     world, rank, local, dist = dist_setup(args)

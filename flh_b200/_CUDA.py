@@ -37,6 +37,11 @@ def _ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
+def _guard(device):
+    """Device guard around a C-ABI call (the library launches on the current device)."""
+    return torch.cuda.device(device)
+
+
 # --------------------------------------------------------------------------- the nine pybind names
 def gemm_i4_dequant_o16(A, B, A_scale, B_scale):
     """flh/cuda/flh_cuda_bindings.cpp:75-113.  u8[M,K/2], u8[N,K/2], f16[M,*], f16[N,*] -> f16[M,N]."""
@@ -63,7 +68,7 @@ def _fht(x, n):
     _check(x.dim() == 2, "Input tensor must be 2D")
     _check(x.shape[1] == n, f"Last dimension must be {n}")
     _check(x.is_contiguous(), "Input tensor must be contiguous")
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         _lib.check(_lib.load().flh_b200_hadamard_f16_inplace(_ptr(x), x.shape[0], n, _stream(x)), "hadamard_transform")
     return x
 
@@ -91,7 +96,7 @@ def _quant_group(x, gs, hadamard):
     rows = x.shape[0]
     q = torch.empty((rows, gs // 2), dtype=torch.uint8, device=x.device)
     s = torch.empty((rows,), dtype=torch.float16, device=x.device)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         _lib.check(_lib.load().flh_b200_quant_group_sym_i4(_ptr(x), rows, gs, int(hadamard), _ptr(q), _ptr(s), _stream(x)),
                    "quant_group_sym_i4")
     return [q, s]
@@ -118,10 +123,19 @@ def quant_and_pack_i4_gs(x, group_size):
 
 
 def gemm_i4_dequant_o16_gs(A, B, A_scale, B_scale, group_size):
-    """flh/cuda/flh_cuda_bindings.cpp:253-299.  Only group 128 is served by this build; the
-    reference kernel itself applies one scale per 128-K block whatever group_size says."""
+    """flh/cuda/flh_cuda_bindings.cpp:253-299: u8[M,K/2], u8[N,K/2], f16[M,K/gs], f16[N,K/gs], gs in {32,64,128}
+    -> f16[M,N].  Every K-group of gs elements is scaled with its own pair of scales (the reference kernel,
+    flh/kernels/gemm_and_dequant_i4_gs.cu:408, applies the first scale of each 128-K block to the whole block,
+    which is only right for gs = 128)."""
+    _check(A.is_cuda and B.is_cuda and A_scale.is_cuda and B_scale.is_cuda, "tensors must be CUDA")
+    _check(A.dtype == torch.uint8 and B.dtype == torch.uint8, "A and B must be uint8 packed int4")
+    _check(A_scale.dtype == torch.float16 and B_scale.dtype == torch.float16, "scales must be float16")
+    _check(A.is_contiguous() and B.is_contiguous() and A_scale.is_contiguous() and B_scale.is_contiguous(),
+           "tensors must be contiguous")
     _check(group_size in (32, 64, 128), "group_size must be 32, 64, or 128")
     _check(A.dim() == 2 and B.dim() == 2, "A/B must be 2D")
+    _check(A_scale.dim() == 2 and B_scale.dim() == 2, "scale must be 2D")
+    _check(B.shape[1] == A.shape[1], "B.shape[1] must equal A.shape[1]")
     K = A.shape[1] * 2
     _check(K % group_size == 0, "K must be divisible by group_size")
     g = K // group_size
@@ -129,8 +143,7 @@ def gemm_i4_dequant_o16_gs(A, B, A_scale, B_scale, group_size):
     _check(A_scale.shape[1] == g, "A_scale.shape[1] must equal K/group_size")
     _check(B_scale.shape[0] == B.shape[0], "B_scale.shape[0] must equal N")
     _check(B_scale.shape[1] == g, "B_scale.shape[1] must equal K/group_size")
-    _check(group_size == 128, "flh_b200 serves group_size 128 only")
-    return gemm_i4_dequant_o16(A, B, A_scale, B_scale)
+    return gemm_i4_dequant(A, B, A_scale, B_scale)
 
 
 # --------------------------------------------------------------------------- extended entry points
@@ -138,38 +151,54 @@ _SIGN_CACHE: dict = {}
 
 
 def _sign_bits(n: int, device):
-    """(kfac, device uint32 bit rows or None) for width n, cached per device."""
+    """(kfac, device uint32 bit rows or None) for width n, cached per (width, device)."""
+    key = (n, str(device))
+    hit = _SIGN_CACHE.get(key)
+    if hit is not None:
+        return hit
     signs, k = get_hadK(n)
     if k == 1:
-        return 1, None
-    key = (k, str(device))
-    if key not in _SIGN_CACHE:
+        _SIGN_CACHE[key] = (1, None)
+        return _SIGN_CACHE[key]
+    tkey = ("table", k, str(device))
+    if tkey not in _SIGN_CACHE:
         s8 = np.ascontiguousarray(signs, dtype=np.int8)
         out = np.zeros((_lib.load().flh_b200_sign_table_bytes(k) + 3) // 4, dtype=np.uint32)
         _lib.check(_lib.load().flh_b200_pack_signs(s8.ctypes.data_as(ctypes.c_void_p), k,
                                                    out.ctypes.data_as(ctypes.c_void_p)), "pack_signs")
-        _SIGN_CACHE[key] = torch.from_numpy(out.view(np.int32)).to(device)
-    return k, _SIGN_CACHE[key]
+        _SIGN_CACHE[tkey] = torch.from_numpy(out.view(np.int32)).to(device)
+    _SIGN_CACHE[key] = (k, _SIGN_CACHE[tkey])
+    return _SIGN_CACHE[key]
 
 
-def quant_token_asym_i4(x, hadamard: bool = True, clip: float = 1.0, exact_factor: bool = False):
+def quant_token_asym_i4(x, hadamard: bool = True, clip: float = 1.0, exact: bool = False, exact_factor=None, out=None):
     """x [M, K] f16/bf16 (row stride allowed) -> (q u8[M,K/2] codes 0..15, scale f16[M], zero f16[M]).
     hadamard=True applies the full-width transform of matmul_hadU (flh/functional/hadamard.py:92-113)
-    before the per-token asymmetric quantiser of fake_quant/quant_utils.py:94-128.  For K = kfac * 2^m the
-    kfac x kfac factor runs on the tensor cores; exact_factor=True sums it sequentially instead (bit-exact
-    with the CPU oracle, slower)."""
+    before the per-token asymmetric quantiser of fake_quant/quant_utils.py:94-128.  By default the high part
+    of the transform (the kfac x kfac factor and the butterfly bits above 64) is summed by the tensor cores
+    (K = P * 64, P <= 256): same values up to the order of binary32 additions, the same order for every
+    batch size.  exact=True keeps the sequential order of the reference (bit-exact with the CPU oracle,
+    slower).  out=(q, scale, zero) writes into caller tensors instead of allocating."""
+    if exact_factor is not None:        # earlier name of `exact`
+        exact = bool(exact_factor)
     _check(x.is_cuda, "Input tensor must be on CUDA")
     _check(x.dtype in (torch.float16, torch.bfloat16), "Input tensor must be float16 or bfloat16")
     _check(x.dim() == 2 and x.stride(1) == 1, "Input tensor must be 2D with unit inner stride")
     M, K = x.shape
     kfac, bits = _sign_bits(K, x.device) if hadamard else (1, None)
-    q = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
-    s = torch.empty((M,), dtype=torch.float16, device=x.device)
-    z = torch.empty((M,), dtype=torch.float16, device=x.device)
-    with torch.cuda.device(x.device):
+    if out is not None:
+        q, s, z = out
+        _check(q.dtype == torch.uint8 and q.is_contiguous() and q.numel() == M * (K // 2) and q.device == x.device, "out[0] must be contiguous uint8 [M, K/2]")
+        _check(s.dtype == torch.float16 and s.numel() == M and z.dtype == torch.float16 and z.numel() == M and s.is_contiguous() and z.is_contiguous(),
+               "out[1], out[2] must be contiguous float16 [M]")
+    else:
+        q = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
+        s = torch.empty((M,), dtype=torch.float16, device=x.device)
+        z = torch.empty((M,), dtype=torch.float16, device=x.device)
+    with _guard(x.device):
         _lib.check(_lib.load().flh_b200_quant_token_asym_i4(
             _ptr(x), BF16 if x.dtype == torch.bfloat16 else F16, M, K, x.stride(0) if M > 1 else K,
-            (2 if exact_factor else 1) if hadamard else 0, kfac,
+            (2 if exact else 1) if hadamard else 0, kfac,
             _ptr(bits), float(clip), _ptr(q), _ptr(s), _ptr(z), _stream(x)), "quant_token_asym_i4")
     return q, s, z
 
@@ -184,7 +213,7 @@ def rmsnorm_quant_token_asym_i4(x, eps: float, hadamard: bool = False, clip: flo
     q = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
     s = torch.empty((M,), dtype=torch.float16, device=x.device)
     z = torch.empty((M,), dtype=torch.float16, device=x.device)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         _lib.check(_lib.load().flh_b200_rmsnorm_quant_token_asym_i4(
             _ptr(x), BF16 if x.dtype == torch.bfloat16 else F16, M, K, x.stride(0), float(eps), int(hadamard), float(clip),
             _ptr(q), _ptr(s), _ptr(z), _stream(x)), "rmsnorm_quant_token_asym_i4")
@@ -197,7 +226,7 @@ def rmsnorm_quant_group_sym_i4(x, eps: float, hadamard: bool = False):
     M, K = x.shape
     q = torch.empty((M * (K // 128), 64), dtype=torch.uint8, device=x.device)
     s = torch.empty((M * (K // 128),), dtype=torch.float16, device=x.device)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         _lib.check(_lib.load().flh_b200_rmsnorm_quant_group_sym_i4(_ptr(x), M, K, float(eps), int(hadamard), _ptr(q), _ptr(s), _stream(x)),
                    "rmsnorm_quant_group_sym_i4")
     return [q, s]
@@ -208,7 +237,7 @@ def weight_rowsum(B, group: int):
     _check(B.is_cuda and B.dtype == torch.uint8 and B.dim() == 2 and B.is_contiguous(), "B must be a contiguous CUDA uint8 matrix")
     N, K = B.shape[0], B.shape[1] * 2
     rs = torch.empty((N, K // group), dtype=torch.int32, device=B.device)
-    with torch.cuda.device(B.device):
+    with _guard(B.device):
         _lib.check(_lib.load().flh_b200_weight_rowsum(_ptr(B), N, K, group, _ptr(rs), _stream(B)), "weight_rowsum")
     return rs
 
@@ -255,7 +284,7 @@ def gemm_i4_dequant(A, B, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=Non
     ag, bg = K // A_scale.shape[1], K // B_scale.shape[1]
     D = out if out is not None else torch.empty((M, N), dtype=out_dtype, device=A.device)
     lib = _lib.load()
-    with torch.cuda.device(A.device):
+    with _guard(A.device):
         stream = _stream(A)
         need = lib.flh_b200_gemm_workspace_bytes(M, N, K, ag, bg, algo)
         resolved = algo if algo != GEMM_AUTO else lib.flh_b200_gemm_pick_algo(M, N, K, ag, bg)
@@ -277,7 +306,7 @@ def expand_i4(B):
     _check(B.is_cuda and B.dtype == torch.uint8 and B.dim() == 2 and B.is_contiguous(), "B must be a contiguous CUDA uint8 matrix")
     N, Kp = B.shape
     out = torch.empty((N, 2 * Kp), dtype=torch.uint8, device=B.device)
-    with torch.cuda.device(B.device):
+    with _guard(B.device):
         _lib.check(_lib.load().flh_b200_expand_i4(_ptr(B), N, 2 * Kp, _ptr(out), _stream(B)), "expand_i4")
     return out
 
@@ -288,7 +317,7 @@ def gemm_i8w_dequant(A, B8, A_scale, B_scale, A_zero=None, B_rowsum=None, bias=N
     N, K = B8.shape
     _check(K == 2 * Kp, "B8 must be [N, K] for A [M, K/2]")
     D = out if out is not None else torch.empty((M, N), dtype=out_dtype, device=A.device)
-    with torch.cuda.device(A.device):
+    with _guard(A.device):
         stream = _stream(A)
         ws = _scratch(A.device, stream, M * K)
         _lib.check(_lib.load().flh_b200_gemm_i8w_dequant(
@@ -308,6 +337,13 @@ def gemm_wait_profile():
     """Nanoseconds the tcgen05 GEMM's roles waited on each other since the last call (see the header)."""
     out = (ctypes.c_ulonglong * 8)()
     _lib.check(_lib.load().flh_b200_gemm_wait_profile(out), "gemm_wait_profile")
+    return list(out)
+
+
+def quant_token_wait_profile():
+    """Nanoseconds the roles of the tensor-core token quantiser waited on each other since the last call (see the header)."""
+    out = (ctypes.c_ulonglong * 8)()
+    _lib.check(_lib.load().flh_b200_quant_token_wait_profile(out), "quant_token_wait_profile")
     return list(out)
 
 

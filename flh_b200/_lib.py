@@ -22,6 +22,7 @@ SIGNATURES = {
     "flh_b200_hadamard_f16_inplace": (c_int, [c_void_p, c_long, c_int, c_void_p]),
     "flh_b200_quant_token_asym_i4": (c_int, [c_void_p, c_int, c_long, c_long, c_long, c_int, c_int, c_void_p, c_float,
                                              c_void_p, c_void_p, c_void_p, c_void_p]),
+    "flh_b200_quant_token_kernel": (ctypes.c_char_p, [c_long, c_long, c_int, c_int]),
     "flh_b200_sign_table_bytes": (c_size_t, [c_int]),
     "flh_b200_pack_signs": (c_int, [c_void_p, c_int, c_void_p]),
     "flh_b200_weight_rowsum": (c_int, [c_void_p, c_long, c_long, c_long, c_void_p, c_void_p]),
@@ -39,6 +40,7 @@ SIGNATURES = {
     "flh_b200_gemm_pick_algo": (c_int, [c_long, c_long, c_long, c_long, c_long]),
     "flh_b200_gemm_status": (c_int, [c_void_p]),
     "flh_b200_gemm_wait_profile": (c_int, [c_void_p]),
+    "flh_b200_quant_token_wait_profile": (c_int, [c_void_p]),
     "flhDenseLayerGEMM_i4_o16": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]),
 }
 

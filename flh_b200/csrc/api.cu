@@ -37,6 +37,9 @@ int launch_weight_rowsum(const uint8_t *, long, long, long, int32_t *, cudaStrea
 int launch_gemm_mma_tile(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
                          const int32_t *, const void *, void *, long, long, long, long, long, int,
                          cudaStream_t);
+int launch_gemm_mma_tile_gs(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
+                            const int32_t *, const void *, void *, long, long, long, long, long, int, int,
+                            cudaStream_t);
 int launch_gemm_stream(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
                        const int32_t *, const void *, void *, long, long, long, long, long, int,
                        int, void *, cudaStream_t);
@@ -55,6 +58,10 @@ int launch_expand_i4(const uint8_t *, long, long, uint8_t *, cudaStream_t);
 int gemm_i8_status(int *);
 int quant_token_factor_status(int *);
 int quant_token_factor_status_clear();
+const char *quant_token_kernel_name(long, long, int, int);
+int quant_token_tc_status(int *);
+int quant_token_tc_wait_profile(unsigned long long *);
+int quant_token_tc_status_clear();
 int gemm_i8_wait_profile(unsigned long long *);
 int gemm_i8_status_clear();
 
@@ -161,6 +168,10 @@ int flh_b200_rmsnorm_quant_token_asym_i4(const void *x, int in_dtype, long M, lo
     return launch_quant_token_warp(x, in_dtype, M, K, ld, hadamard, eps, clip, q, scale, zero, static_cast<cudaStream_t>(stream));
 }
 
+const char *flh_b200_quant_token_kernel(long M, long K, int hadamard, int kfac) {
+    return quant_token_kernel_name(M, K, hadamard, kfac);
+}
+
 size_t flh_b200_sign_table_bytes(int kfac) {
     if (kfac <= 0) return 0;
     const size_t bits_bytes = ((size_t)kfac * ((kfac + 31) / 32) * 4 + 15) / 16 * 16;
@@ -194,6 +205,7 @@ int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t
 }
 
 int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group) {
+    if ((a_group < b_group ? a_group : b_group) < 128) return FLH_B200_GEMM_MMA_SYNC;    // K-groups of 32 / 64
     if (M <= 64) return stream_splits(M, N, K) > 1 ? FLH_B200_GEMM_STREAM_SPLITK : FLH_B200_GEMM_STREAM;
     // large batches without group scales: expanding both operands to int8 first pays for itself
     if (a_group == K && b_group == K && M >= 1024)
@@ -215,14 +227,24 @@ int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_s
     FLH_REQUIRE(M >= 0 && N >= 0 && K > 0, FLH_B200_EINVAL, "bad shape M=%ld N=%ld K=%ld", M, N, K);
     FLH_REQUIRE(K % 128 == 0 && K <= 65536, FLH_B200_EINVAL, "K must be a multiple of 128 and <= 65536 (got %ld)", K);
     FLH_REQUIRE(N % 128 == 0, FLH_B200_EINVAL, "N must be a multiple of 128 (got %ld)", N);
-    FLH_REQUIRE(a_group == 128 || a_group == K, FLH_B200_EINVAL, "a_group must be 128 or K (got %ld)", a_group);
-    FLH_REQUIRE(b_group == 128 || b_group == K, FLH_B200_EINVAL, "b_group must be 128 or K (got %ld)", b_group);
+    const long gmin = a_group < b_group ? a_group : b_group;       // the K-group the integer sums are cut into
+    FLH_REQUIRE(gmin == 32 || gmin == 64 || gmin == 128 || gmin == K, FLH_B200_EINVAL,
+                "the smaller of a_group and b_group must be 32, 64, 128 or K (got %ld, %ld)", a_group, b_group);
+    FLH_REQUIRE(a_group == gmin || a_group == K, FLH_B200_EINVAL, "a_group must be %ld or K (got %ld)", gmin, a_group);
+    FLH_REQUIRE(b_group == gmin || b_group == K, FLH_B200_EINVAL, "b_group must be %ld or K (got %ld)", gmin, b_group);
     FLH_REQUIRE(out_dtype == FLH_B200_F16 || out_dtype == FLH_B200_BF16, FLH_B200_EINVAL, "out_dtype must be F16 or BF16");
     if (M == 0 || N == 0) return 0;
     FLH_REQUIRE(A && B && a_scale && b_scale && D, FLH_B200_EINVAL, "null pointer");
     FLH_REQUIRE(!a_zero || b_rowsum, FLH_B200_EINVAL, "a_zero needs b_rowsum");
     FLH_REQUIRE(aligned16(A) && aligned16(B), FLH_B200_EALIGN, "A and B must be 16-byte aligned");
     FLH_REQUIRE((reinterpret_cast<uintptr_t>(D) & 15) == 0, FLH_B200_EALIGN, "D must be 16-byte aligned");
+    if (gmin == 32 || gmin == 64) {
+        // groups narrower than the 128-K stage: the mma.sync tile kernel that folds every group's sum with its own scales
+        FLH_REQUIRE(algo == FLH_B200_GEMM_AUTO || algo == FLH_B200_GEMM_MMA_SYNC, FLH_B200_EUNSUPPORTED,
+                    "K-groups of %ld are served by the mma.sync tile kernel only (algo AUTO or MMA_SYNC)", gmin);
+        return launch_gemm_mma_tile_gs(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, (int)gmin,
+                                       out_dtype, static_cast<cudaStream_t>(stream));
+    }
     if (algo == FLH_B200_GEMM_AUTO) {
         algo = flh_b200_gemm_pick_algo(M, N, K, a_group, b_group);
         // without (enough) scratch the split-K form quietly gives way to the plain streaming kernel
@@ -330,7 +352,15 @@ int flh_b200_gemm_status(int *out) {
     if (out[0]) return gemm_i8_status_clear();
     rc = quant_token_factor_status(out);
     if (rc) return rc;
-    return out[0] ? quant_token_factor_status_clear() : 0;
+    if (out[0]) return quant_token_factor_status_clear();
+    rc = quant_token_tc_status(out);
+    if (rc) return rc;
+    return out[0] ? quant_token_tc_status_clear() : 0;
+}
+
+int flh_b200_quant_token_wait_profile(unsigned long long *out) {
+    FLH_REQUIRE(out, FLH_B200_EINVAL, "null pointer");
+    return quant_token_tc_wait_profile(out);
 }
 
 int flh_b200_gemm_wait_profile(unsigned long long *out) {

@@ -210,6 +210,130 @@ gemm_tile_kernel(const GemmParams p) {
 }
 
 // --------------------------------------------------------------------------------------------
+// Tile kernel for K-groups of GS = 32 or 64 (the *_gs entry points of the reference, which scale every 128-K block with
+// the FIRST scale of the block whatever the group size; here every group of GS elements gets its own scales).  Same CTA tile and
+// cp.async ring as above; the difference is the order in which a 128-K stage is fed to the tensor cores: one
+// m16n8k32 per 32-element sub-block (thread t takes the t-th 32-bit word of the sub-block's 16 packed bytes), so that
+// the int32 fragment after 1 (GS = 32) or 2 (GS = 64) instructions is the exact integer sum of one group and can be
+// folded into the binary32 accumulator with that group's scales.
+template <bool A_UNSIGNED, int GS>
+__global__ void __launch_bounds__(256)
+gemm_tile_gs_kernel(const GemmParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int wm = warp >> 2, wn = warp & 3;
+    const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * TBN;
+    const int KB = p.K / 128;
+    const long ldk = p.K / 2;
+    const int G = p.K / GS;                                  // groups per row (row sums are [N][G])
+    const bool has_zero = p.a_zero != nullptr;
+
+    auto load_stage = [&](int stage, int kb) {
+        uint8_t *sA = smem + stage * TSTAGE_BYTES, *sB = sA + TBM * 64;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int ch = tid + i * 256, row = ch >> 2, c = ch & 3;
+            const int gr = m0 + row;
+            const uint8_t *src = p.A + (long)(gr < p.M ? gr : p.M - 1) * ldk + kb * 64 + c * 16;
+            cp_async16(smem_u32(sA + row * 64 + c * 16), src, gr < p.M ? 16 : 0);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int ch = tid + i * 256, row = ch >> 2, c = ch & 3;
+            cp_async16(smem_u32(sB + row * 64 + c * 16), p.B + (long)(n0 + row) * ldk + kb * 64 + c * 16, 16);
+        }
+    };
+
+    int32_t c[4][4][4];
+    float acc[4][4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { c[i][j][k] = 0; acc[i][j][k] = 0.0f; }
+#pragma unroll
+    for (int s = 0; s < TSTAGES - 1; ++s) {
+        if (s < KB) load_stage(s, s);
+        cp_async_commit();
+    }
+    // fold the integer sums of group grp into the accumulators
+    auto dequant_all = [&](int grp) {
+        const int ga = p.ga_cols == 1 ? 0 : grp, gb = p.gb_cols == 1 ? 0 : grp;
+        float sb[4][2];
+        int rs[4][2];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int col = n0 + wn * 32 + j * 8 + 2 * t + e;
+                sb[j][e] = __half2float(p.b_scale[(long)col * p.gb_cols + gb]);
+                rs[j][e] = has_zero ? p.b_rowsum[(long)col * G + grp] : 0;
+            }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = min(m0 + wm * 64 + i * 16 + g + 8 * h, p.M - 1);
+                const float sa = __half2float(p.a_scale[(long)r * p.ga_cols + ga]);
+                const int za = has_zero ? (int)__half2float(p.a_zero[(long)r * p.ga_cols + ga]) : 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int32_t I = (c[i][j][2 * h + e] >> 8) - za * rs[j][e];
+                        acc[i][j][2 * h + e] = __fmaf_rn((float)I, __fmul_rn(sa, sb[j][e]), acc[i][j][2 * h + e]);
+                        c[i][j][2 * h + e] = 0;
+                    }
+            }
+        }
+    };
+
+    for (int kb = 0; kb < KB; ++kb) {
+        cp_async_wait<TSTAGES - 2>();
+        __syncthreads();
+        if (kb + TSTAGES - 1 < KB) load_stage((kb + TSTAGES - 1) % TSTAGES, kb + TSTAGES - 1);
+        cp_async_commit();
+        const uint8_t *sA = smem + (kb % TSTAGES) * TSTAGE_BYTES, *sB = sA + TBM * 64;
+#pragma unroll
+        for (int sub = 0; sub < 4; ++sub) {                   // 32-element sub-block = 16 packed bytes = one word per thread t
+            uint32_t bw[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) bw[j] = *reinterpret_cast<const uint32_t *>(sB + (wn * 32 + j * 8 + g) * 64 + sub * 16 + t * 4);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t al = *reinterpret_cast<const uint32_t *>(sA + (wm * 64 + i * 16 + g) * 64 + sub * 16 + t * 4);
+                const uint32_t ah = *reinterpret_cast<const uint32_t *>(sA + (wm * 64 + i * 16 + g + 8) * 64 + sub * 16 + t * 4);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    mma_i8<A_UNSIGNED>(c[i][j], even16(al), even16(ah), odd16(al), odd16(ah), even16(bw[j]), odd16(bw[j]));
+            }
+            if (GS == 32) dequant_all(kb * 4 + sub);
+            else if (sub & 1) dequant_all(kb * 2 + (sub >> 1));
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int col = n0 + wn * 32 + j * 8 + 2 * t;
+            float b0 = 0.f, b1 = 0.f;
+            if (p.bias) { b0 = __half2float(p.bias[col]); b1 = __half2float(p.bias[col + 1]); }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = m0 + wm * 64 + i * 16 + g + 8 * h;
+                if (r < p.M) {
+                    float v0 = acc[i][j][2 * h], v1 = acc[i][j][2 * h + 1];
+                    if (p.bias) { v0 = __fadd_rn(v0, b0); v1 = __fadd_rn(v1, b1); }
+                    store_pair(p.D, p.out_bf16, (long)r * p.N + col, v0, v1);
+                }
+            }
+        }
+}
+
+// --------------------------------------------------------------------------------------------
 // Streaming kernel for decode (M <= 64): HBM-bound on the packed weight bytes.
 //
 // The weights are the ROW operand of mma.m16n8k32 (16 output channels per warp), the tokens the
@@ -530,6 +654,23 @@ int launch_gemm_mma_tile(const uint8_t *A, const uint8_t *B, const void *a_scale
         gemm_tile_kernel<false><<<grid, 256, smem, stream>>>(p);
     }
     return cuda_status(cudaGetLastError(), "gemm_tile launch");
+}
+
+// K-groups of 32 or 64: a_group and b_group are each gs or K.
+int launch_gemm_mma_tile_gs(const uint8_t *A, const uint8_t *B, const void *a_scale, const void *a_zero,
+                            const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D,
+                            long M, long N, long K, long a_group, long b_group, int gs, int out_dtype,
+                            cudaStream_t stream) {
+    const GemmParams p = make_params(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype);
+    const int smem = TSTAGES * TSTAGE_BYTES;
+    dim3 grid((unsigned)(N / TBN), (unsigned)((M + TBM - 1) / TBM));
+    using Kern = void (*)(const GemmParams);
+    const Kern kern = a_zero ? (gs == 32 ? gemm_tile_gs_kernel<true, 32> : gemm_tile_gs_kernel<true, 64>)
+                             : (gs == 32 ? gemm_tile_gs_kernel<false, 32> : gemm_tile_gs_kernel<false, 64>);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_status(e, "gemm_tile_gs attribute");
+    kern<<<grid, 256, smem, stream>>>(p);
+    return cuda_status(cudaGetLastError(), "gemm_tile_gs launch");
 }
 
 template <int WARPS, int NT, bool U, bool G, bool SPLIT>

@@ -497,9 +497,17 @@ static long token_warp_min_rows() {
     return v;
 }
 
+int launch_quant_token_tc(const void *x, int in_dtype, long M, long K, long ld, int kfac, const uint32_t *sign_bits,
+                          float clip, uint8_t *q, void *scale, void *zero, cudaStream_t stream);
+
 int launch_quant_token_asym(const void *x, int in_dtype, long M, long K, long ld, int hadamard,
                             int kfac, const uint32_t *sign_bits, float clip, uint8_t *q,
                             void *scale, void *zero, cudaStream_t stream) {
+    if (hadamard == 1) {
+        // default transform: the high part on the tensor cores, for every batch size (K = P * 64, P <= 256)
+        const int rc = launch_quant_token_tc(x, in_dtype, M, K, ld, kfac, sign_bits, clip, q, scale, zero, stream);
+        if (rc != -1000) return rc;
+    }
     if ((!hadamard || kfac == 1) && (K == 4096 || K == 8192) && M >= token_warp_min_rows() &&
         (hadamard || (reinterpret_cast<uintptr_t>(q) & 15) == 0))          // its untransformed form stores 16 bytes at a time
         return launch_quant_token_warp(x, in_dtype, M, K, ld, hadamard, -1.0f, clip, q, scale, zero, stream);
@@ -561,6 +569,17 @@ int launch_quant_token_asym(const void *x, int in_dtype, long M, long K, long ld
         case 2: return launch_one<6, 2, false, true>(p, M, stream);
         default: return launch_one<6, 3, false, true>(p, M, stream);
     }
+}
+
+bool quant_token_tc_takes(long K, int kfac);
+
+// The __global__ function launch_quant_token_asym picks for a shape (for pointers aligned to 16 bytes).
+const char *quant_token_kernel_name(long M, long K, int hadamard, int kfac) {
+    if (!hadamard) kfac = 1;
+    if (hadamard == 1 && quant_token_tc_takes(K, kfac)) return "quant_token_tc_kernel";
+    if ((!hadamard || kfac == 1) && (K == 4096 || K == 8192) && M >= token_warp_min_rows()) return "quant_token_warp_kernel";
+    if (hadamard == 1 && kfac >= 64 && K == (long)kfac * 64 && M >= 256) return "quant_token_factor_kernel";
+    return "quant_token_asym_kernel";
 }
 
 }  // namespace flh

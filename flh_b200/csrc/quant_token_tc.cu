@@ -1,0 +1,505 @@
+// Per-token quantiser with the HIGH part of the full-width Hadamard transform on the 5th-generation tensor cores.
+//
+// A row of K = P * 64 values is a P x 64 matrix X[p][j] (j contiguous).  The transform of matmul_hadU
+// (flh/functional/hadamard.py:92-113), (hadK (x) H_{2^a} (x) H_64) x, factors into two commuting steps:
+//   1. over p:  T[p'][j] = sum_p G[p'][p] X[p][j],  G = hadK (x) H_{2^a}  (a P x P matrix of +-1, P = kfac * 2^a)
+//   2. over j:  six butterfly bits on the 64 values of each p'.
+// Step 1 runs FIRST, on the raw 16-bit inputs: every product with +-1 is exact, so tcgen05.mma (kind::f16) with
+// binary32 accumulation in TMEM needs no operand splitting — A = G (K-major, built once per CTA in shared memory
+// from the sign bits), B = the row itself exactly as it lies in global memory (TMA with the 128-byte swizzle, read as
+// an N-major operand: j is the contiguous N dimension, p the contraction), D[p'][j] in TMEM with one p' per lane.
+// Step 2 then needs no data movement at all: a thread reads its lane's 64 columns with one tcgen05.ld and runs the six
+// bits in registers (packed binary32 pairs), takes part in the row's min/max, and turns its 64 consecutive outputs
+// into 32 bytes of codes.  The CUDA cores do 6 of the 12+ butterfly bits instead of all of them.
+//
+// The sums of step 1 are accumulated by the tensor core in its own order, so the result is not bit-identical to the
+// sequential butterflies (that order is hadamard = 2): same values up to binary32 rounding of the accumulation.  The
+// order does not depend on the batch: every M takes this kernel.
+//
+// Shapes: P <= 64: two rows per MMA (A = diag(G, G), 128 x 128); 64 < P <= 128: one row per MMA (M = 128);
+// 128 < P <= 256: one row on two MMAs (M = 256 as two tiles).  Roles of the persistent CTA: 16 epilogue warps (four
+// groups of four, one group per 128-lane accumulator tile), one TMA thread, one MMA thread.  Rings: shared-memory stages
+// (TMA -> MMA), 64-column TMEM slots (MMA -> epilogue).  All mbarrier waits are bounded; a wait that runs out sets a status word,
+// the warps keep walking their loops without touching the tensor core so that every named barrier is still reached.
+#include "tc_common.cuh"
+#include "token_common.cuh"
+
+namespace flh {
+namespace {
+
+constexpr int kEpiWarpsTc = 16;
+constexpr int kThreadsTc = kEpiWarpsTc * 32 + 128;       // + one warpgroup holding the TMA warp and the MMA warp
+constexpr int kSlots = 8;                                // 64-column accumulator slots in TMEM (512 columns)
+constexpr int kMaxStages = 8;
+__device__ int g_status_tc[4];
+// Diagnostic (flh_b200_quant_token_wait_profile): nanoseconds summed over CTAs — [0] CTA lifetime, [1] TMA thread waiting for a free
+// stage, [2] MMA thread waiting for TMA data, [3] MMA thread waiting for a free accumulator slot, [4] epilogue warps waiting
+// for a finished accumulator (summed over the 16 warps), [5] set-up (A operand, barriers, TMEM allocation).
+__device__ unsigned long long g_wait_tc[8];
+
+struct TcQuantParams {
+    long M;
+    int K, P;                  // K = P * 64
+    int kfac, B;               // P = kfac * B, B a power of two
+    int words;                 // 32-bit words per row of the sign-bit table
+    const uint32_t *sign_bits; // kfac rows of bits (1 = negative), or null for kfac = 1
+    int R, T;                  // rows per 128-lane accumulator block (2 when P <= 64), tiles per row (2 when P > 128)
+    int NB;                    // 64-column blocks per MMA: N = 64 * NB, i.e. R * NB rows per unit
+    int Kdim, Mtot;            // contraction length of the MMAs (multiple of 16), rows of A (128 or 256)
+    int a_bytes, stage_bytes, stages;
+    int bf16;
+    float clip, c;
+    uint8_t *q;
+    __half *scale, *zero;
+};
+
+__device__ __forceinline__ uint64_t umma_desc_tc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&v)[64]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
+        "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]),
+          "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]),
+          "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]),
+          "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]),
+          "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
+        : "r"(taddr) : "memory");
+}
+
+// six butterfly bits over 64 values held as 32 packed pairs (pair k = elements 2k, 2k + 1); bit 0 inside the pairs
+__device__ __forceinline__ void bfly6_pairs(uint64_t (&p)[32]) {
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+        float a, b;
+        unpack2(p[k], a, b);
+        p[k] = pack2(__fadd_rn(a, b), __fsub_rn(a, b));
+    }
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            if ((k & h) == 0) {
+                const uint64_t a = p[k], b = p[k + h];
+                p[k] = add2(a, b);
+                p[k + h] = sub2(a, b);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
+    uint32_t r;
+    asm volatile("redux.sync.max.u32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// PROFILE: time every wait with %globaltimer and add the sums to g_wait_tc (flh_b200_quant_token_wait_profile).
+template <bool PROFILE>
+__global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcQuantParams p) {
+    extern __shared__ uint8_t smem_dyn[];
+    const uint32_t raw = smem_u32(smem_dyn);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *sm = smem_dyn + (base - raw);
+    const int S = p.stages, T = p.T, R = p.R, NB = p.NB;
+    const int BPU = T * NB;                              // 128-lane x 64-column accumulator blocks per unit (1, 2 or 4)
+    const int NU = kSlots / BPU;                         // units whose accumulators fit TMEM
+    const int NT = 4 / BPU;                              // epilogue teams (each takes every NT-th unit)
+    const uint32_t a_base = base, st_base = base + p.a_bytes;
+    const int aux = p.a_bytes + S * p.stage_bytes;
+    uint32_t *red = reinterpret_cast<uint32_t *>(sm + aux);   // [2][8 rows in flight][8 warps of a row][|min| bits, max bits]
+    const uint32_t bars = base + aux + 1024;
+    auto stage_full = [&](int s) { return bars + 8u * s; };
+    auto stage_empty = [&](int s) { return bars + 8u * (kMaxStages + s); };
+    auto slot_full = [&](int u) { return bars + 8u * (2 * kMaxStages + u); };
+    auto slot_empty = [&](int u) { return bars + 8u * (2 * kMaxStages + kSlots + u); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + aux + 1024 + 8 * (2 * kMaxStages + 2 * kSlots));
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 2);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t t_start = PROFILE ? gtimer() : 0;
+
+    // ---- one-time set-up: A = G (or diag(G, G)) as a K-major operand with the 128-byte swizzle ----
+    // element (m, k): K atom kb = k / 64 at (kb * Mtot / 8 + m / 8) * 1024, row m % 8 of 128 bytes, 16-byte chunk ((k % 64) / 8) ^ (m % 8).
+    // G[p'][p] = S[a'][a] * (-1)^popc(b' & b) with p = a * B + b (B a power of two): per row the signs of the factor come as
+    // one bit row of the table (staged in shared memory first), the Sylvester part is a parity.
+    {
+        uint32_t *sgn = reinterpret_cast<uint32_t *>(sm + aux + 2048);      // kfac * words words (<= 172 * 6 * 4 bytes)
+        if (p.sign_bits)
+            for (int i = tid; i < p.kfac * p.words; i += kThreadsTc) sgn[i] = p.sign_bits[i];
+        __syncthreads();
+        const int katoms = (p.Kdim + 63) >> 6;
+        const int cpr = katoms * 8;                                         // 16-byte chunks per row of A
+        const int chunks = p.Mtot * cpr;
+        const int logB = 31 - __clz(p.B);
+        const uint32_t one = p.bf16 ? 0x3F80u : 0x3C00u;
+        for (int i = tid; i < chunks; i += kThreadsTc) {
+            const int m = i / cpr, kc = i - m * cpr;                        // row of A, 16-byte chunk along K
+            const int pr = R == 2 ? (m & 63) : m, blk_m = R == 2 ? (m >> 6) : 0;
+            uint32_t w[4] = {0u, 0u, 0u, 0u};
+            const int k0 = kc * 8;
+            const int pc0 = R == 2 ? (k0 & 63) : k0, blk_k = R == 2 ? (k0 >> 6) : 0;
+            if (pr < p.P && blk_k == blk_m && pc0 < p.P && k0 < p.Kdim) {
+                const int ar = pr >> logB, br = pr & (p.B - 1);
+                const uint32_t *row = sgn + ar * p.words;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int pc = pc0 + e;
+                    if (pc < p.P) {
+                        const int ac = pc >> logB, bc = pc & (p.B - 1);
+                        uint32_t neg = __popc((uint32_t)(br & bc)) & 1u;
+                        if (p.sign_bits) neg ^= (row[ac >> 5] >> (ac & 31)) & 1u;
+                        w[e >> 1] |= (one | (neg << 15)) << (16 * (e & 1));
+                    }
+                }
+            }
+            const int kb = kc >> 3, cc = kc & 7;
+            *reinterpret_cast<uint4 *>(sm + (kb * (p.Mtot >> 3) + (m >> 3)) * 1024 + (m & 7) * 128 + ((cc ^ (m & 7)) << 4)) =
+                make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+    if (tid == 0) {
+        for (int s = 0; s < kMaxStages; ++s) { mbar_init(stage_full(s), 1); mbar_init(stage_empty(s), 1); }
+        for (int u = 0; u < kSlots; ++u) { mbar_init(slot_full(u), 1); mbar_init(slot_empty(u), 4 * BPU); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    fence_proxy_async();
+    if (warp == kEpiWarpsTc + 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const long n_units = (p.M + R * NB - 1) / (R * NB);
+    if (PROFILE && tid == 0) atomicAdd(&g_wait_tc[5], gtimer() - t_start);
+    // a bounded wait, timed as a whole when profiling (try_wait may itself block for a while before it returns)
+    auto wait = [&](uint32_t bar, uint32_t parity, int code, unsigned long long &acc) {
+        const uint64_t ta = PROFILE ? gtimer() : 0;
+        const bool got = mbar_wait_status(g_status_tc, bar, parity, abort_flag, code);
+        if (PROFILE) acc += gtimer() - ta;
+        return got;
+    };
+
+    if (warp >= kEpiWarpsTc) {
+        if (warp == kEpiWarpsTc && lane == 0) {
+            // ============================================================= TMA producer
+            long it = 0;
+            unsigned long long w1 = 0;
+            for (long unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
+                const int s = (int)(it % S);
+                if (!wait(stage_empty(s), (uint32_t)(((it / S) & 1) ^ 1), 31, w1)) break;
+                mbar_expect_tx(stage_full(s), (uint32_t)p.stage_bytes);
+                tma_load_3d(st_base + s * p.stage_bytes, &map_x, 0, 0, (int)(unit * R * NB), stage_full(s));
+            }
+            if (PROFILE) atomicAdd(&g_wait_tc[1], w1);
+        } else if (warp == kEpiWarpsTc + 1 && lane == 0) {
+            // ============================================================= MMA issuer
+            const uint32_t fmt = p.bf16 ? 1u : 0u;
+            // D binary32, A / B format, B N-major (bit 16), N = 64 NB, M = 128
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)((64 * NB) >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            const uint32_t nblk = (uint32_t)p.stage_bytes / (uint32_t)NB;          // bytes between the 64-column blocks of B (one block = R rows)
+            const int ksteps = p.Kdim >> 4;
+            long it = 0;
+            unsigned long long w2 = 0, w3 = 0;
+            for (long unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
+                const int s = (int)(it % S), u = (int)(it % NU);
+                if (!wait(stage_full(s), (uint32_t)((it / S) & 1), 32, w2)) break;
+                if (!wait(slot_empty(u), (uint32_t)(((it / NU) & 1) ^ 1), 33, w3)) break;
+                tc_fence_after();
+                const uint32_t bst = st_base + s * p.stage_bytes;
+                for (int t = 0; t < T; ++t) {
+                    const uint32_t d = tmem + (uint32_t)((u * BPU + t * NB) * 64);
+                    for (int ks = 0; ks < ksteps; ++ks) {
+                        // A: K-major, 8-row groups 1024 bytes apart; K step of 16 = 32 bytes inside the 128-byte row, next atom after 4
+                        const uint64_t ad = umma_desc_tc(a_base + ((ks >> 2) * (p.Mtot >> 3) + t * 16) * 1024 + (ks & 3) * 32, 16, 1024);
+                        // B: N-major (64 values of j = one 128-byte row per p), 8-row groups 1024 bytes apart (SBO), 16 rows per
+                        // K step; the NB blocks of 64 columns (different token rows) lie nblk bytes apart (LBO)
+                        const uint64_t bd = umma_desc_tc(bst + ks * 2048, nblk, 1024);
+                        const uint32_t acc = ks ? 1u : 0u;
+                        asm volatile("{\n\t.reg .pred pp;\n\tsetp.ne.b32 pp, %4, 0;\n\t"
+                                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pp;\n\t}"
+                                     ::"r"(d), "l"(ad), "l"(bd), "r"(idesc), "r"(acc) : "memory");
+                    }
+                }
+                tc_commit(stage_empty(s));
+                tc_commit(slot_full(u));
+            }
+            if (PROFILE) { atomicAdd(&g_wait_tc[2], w2); atomicAdd(&g_wait_tc[3], w3); }
+        }
+    } else {
+        // ================================================================= epilogue
+        const int g = warp >> 2, quarter = warp & 3;
+        const int team = g / BPU, b = g - team * BPU;                // this group's block of the unit
+        const int tile = b / NB, nb = b - tile * NB;                 // accumulator tile of the row, 64-column block of the MMA
+        const int wpr = R == 2 ? 2 : 4 * T;                          // warps that share one row
+        const int m = quarter * 32 + lane;                           // TMEM lane = row of the accumulator tile
+        const int riu = R == 2 ? nb * 2 + (m >> 6) : nb;             // row of the unit
+        const int pp = R == 2 ? (m & 63) : tile * 128 + m;           // p' of this thread
+        const int rslot = R == 2 ? (quarter & 1) : tile * 4 + quarter;   // this warp among the warps of its row
+        const int rt = team * R * NB + riu;                          // row in flight: named barrier 1 + rt (at most 8)
+        const bool live = pp < p.P;
+        const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * 64);
+        uint8_t *qbase = p.q + pp * 32;
+        const long qld = (long)(p.K >> 1);
+        bool ok = true;
+        int n = 0;
+        unsigned long long w4 = 0;
+        for (long it = team;; it += NT, ++n) {
+            const long unit = blockIdx.x + it * gridDim.x;
+            if (unit >= n_units) break;
+            const int u = (int)(it % NU);
+            ok = __all_sync(0xffffffffu, ok && wait(slot_full(u), (uint32_t)((it / NU) & 1), 34, w4));
+            uint64_t v[32];
+            if (ok) {
+                tc_fence_after();
+                uint32_t rawv[64];
+                tmem_ld64(tbase + (uint32_t)(u * BPU * 64), rawv);
+                tc_wait_ld();
+#pragma unroll
+                for (int k = 0; k < 32; ++k) v[k] = ((uint64_t)rawv[2 * k + 1] << 32) | rawv[2 * k];
+            } else {
+#pragma unroll
+                for (int k = 0; k < 32; ++k) v[k] = 0ull;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(slot_empty(u));               // the accumulator is in registers: the slot is free
+            bfly6_pairs(v);
+            // ---- row minimum (<= 0) and maximum (>= 0): the bit pattern of a non-negative binary32 orders like an
+            //      unsigned integer, so |min| and max go through one redux.sync each ----
+            float mn0 = 0.0f, mn1 = 0.0f, mx0 = 0.0f, mx1 = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 32; k += 2) {
+                float x0, x1, x2, x3;
+                unpack2(v[k], x0, x1);
+                unpack2(v[k + 1], x2, x3);
+                mn0 = min3(mn0, x0, x1); mx0 = max3(mx0, x0, x1);
+                mn1 = min3(mn1, x2, x3); mx1 = max3(mx1, x2, x3);
+            }
+            const uint32_t wmin = warp_max_u32(__float_as_uint(fminf(mn0, mn1)) & 0x7fffffffu);
+            const uint32_t wmax = warp_max_u32(__float_as_uint(fmaxf(mx0, mx1)) & 0x7fffffffu);
+            uint32_t *rd_ = red + (n & 1) * 128 + rt * 16;
+            if (lane == 0) *reinterpret_cast<uint2 *>(rd_ + rslot * 2) = make_uint2(wmin, wmax);
+            bar_sync_named(1 + rt, 32 * wpr);
+            uint32_t umin, umax;
+            {
+                const uint4 e0 = *reinterpret_cast<const uint4 *>(rd_);
+                umin = max(e0.x, e0.z); umax = max(e0.y, e0.w);
+                if (wpr > 2) {
+                    const uint4 e1 = *reinterpret_cast<const uint4 *>(rd_ + 4);
+                    umin = max(umin, max(e1.x, e1.z)); umax = max(umax, max(e1.y, e1.w));
+                }
+                if (wpr > 4) {
+                    const uint4 e2 = *reinterpret_cast<const uint4 *>(rd_ + 8), e3 = *reinterpret_cast<const uint4 *>(rd_ + 12);
+                    umin = max(umin, max(max(e2.x, e2.z), max(e3.x, e3.z))); umax = max(umax, max(max(e2.y, e2.w), max(e3.y, e3.w)));
+                }
+            }
+            const TokenRowParams rp = token_row_params(__uint_as_float(umin | 0x80000000u), __uint_as_float(umax), p.clip, p.c);
+            const long row = unit * (R * NB) + riu;
+            if (ok && row < p.M) {
+                if (pp == 0) { p.scale[row] = rp.scale; p.zero[row] = __float2half_rn(rp.zero); }
+                if (live) {
+                    // y = fma(x, rd, M + zero) = M + code with M = 1.5 * 2^23 (the sum is rounded to an integer, ties to even on the
+                    // code); the codes of four neighbours (c0, c1 | c2, c3 as two packed pairs) are joined in binary32, every value an
+                    // exact integer: (c2, c3) = y23 - M;  u = (c2, c3) * 256 + y01 = M + (c0 + 256 c2, c1 + 256 c3);
+                    // w = (u.hi - M) * 16 + u.lo = M + c0 + 16 c1 + 256 c2 + 4096 c3: the low 16 bits of w's pattern are the two bytes
+                    const float Mf = 12582912.0f;
+                    const float Mzf = __fadd_rn(Mf, rp.zero);
+                    const uint64_t rd2 = pack2(rp.rd, rp.rd), Mz2 = pack2(Mzf, Mzf), nM2 = pack2(-Mf, -Mf), c256 = pack2(256.0f, 256.0f);
+#pragma unroll
+                    for (int k = 0; k < 32; ++k) v[k] = fma2(v[k], rd2, Mz2);
+                    if (rp.clamp) {
+#pragma unroll
+                        for (int k = 0; k < 32; ++k) {
+                            float x0, x1;
+                            unpack2(v[k], x0, x1);
+                            v[k] = pack2(fmaxf(fminf(x0, Mf + 15.0f), Mf), fmaxf(fminf(x1, Mf + 15.0f), Mf));
+                        }
+                    }
+                    uint32_t o[8];
+#pragma unroll
+                    for (int wd = 0; wd < 8; ++wd) {
+                        uint32_t hw[2];
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            const int k = wd * 4 + hh * 2;
+                            float lo, hi;
+                            unpack2(fma2(add2(v[k + 1], nM2), c256, v[k]), lo, hi);
+                            hw[hh] = __float_as_uint(__fmaf_rn(__fsub_rn(hi, Mf), 16.0f, lo));
+                        }
+                        o[wd] = __byte_perm(hw[0], hw[1], 0x5410);
+                    }
+                    uint4 *dst = reinterpret_cast<uint4 *>(qbase + row * qld);
+                    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                }
+            }
+        }
+        if (PROFILE && lane == 0) atomicAdd(&g_wait_tc[4], w4);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (PROFILE && tid == 0) atomicAdd(&g_wait_tc[0], gtimer() - t_start);
+    if (warp == kEpiWarpsTc + 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFnTc)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+EncodeTiledFnTc encode_fn_tc() {
+    static EncodeTiledFnTc fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFnTc>(ptr);
+    }
+    return fn;
+}
+
+// The tensor map of an input is a pure function of (pointer, M, P, row stride, box): the last few are remembered per
+// host thread, so that a serving loop that re-uses its buffers encodes each map once.
+struct MapKey {
+    const void *x; long M, ld; int P, boxP, R;
+    bool operator==(const MapKey &o) const { return x == o.x && M == o.M && ld == o.ld && P == o.P && boxP == o.boxP && R == o.R; }
+};
+struct MapCache { MapKey key[8]; CUtensorMap map[8]; int used = 0, next = 0; };
+
+int get_map(const MapKey &k, CUtensorMap *out) {
+    static thread_local MapCache cache;
+    for (int i = 0; i < cache.used; ++i)
+        if (cache.key[i] == k) { *out = cache.map[i]; return 0; }
+    EncodeTiledFnTc fn = encode_fn_tc();
+    if (!fn) return fail(FLH_B200_EUNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
+    // x as [M][P][64] 16-bit values: dimension 0 = j (contiguous), 1 = p (128 bytes apart), 2 = row (ld * 2 bytes apart);
+    // chunks past P and rows past M read as zero
+    cuuint64_t dims[3] = {64u, (cuuint64_t)k.P, (cuuint64_t)k.M};
+    cuuint64_t strides[2] = {128u, (cuuint64_t)k.ld * 2u};
+    cuuint32_t box[3] = {64u, (cuuint32_t)k.boxP, (cuuint32_t)k.R};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(k.x), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FLH_B200_EINVAL, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    const int slot = cache.used < 8 ? cache.used++ : (cache.next++ & 7);
+    cache.key[slot] = k;
+    cache.map[slot] = m;
+    *out = m;
+    return 0;
+}
+
+}  // namespace
+
+// Shapes this kernel takes: K = P * 64 with P = kfac * 2^a <= 256.
+bool quant_token_tc_takes(long K, int kfac) {
+    if (K % 64 != 0 || kfac < 1) return false;
+    const long P = K / 64;
+    if (P > 256 || P % kfac != 0) return false;
+    const long B = P / kfac;
+    return (B & (B - 1)) == 0;
+}
+
+// Full-width transform + per-token asymmetric int4 for K = P * 64, P = kfac * 2^a <= 256.  Returns -1000 when the shape
+// (or an alignment) is not one this kernel takes; the caller then uses the CUDA-core kernels.
+int launch_quant_token_tc(const void *x, int in_dtype, long M, long K, long ld, int kfac, const uint32_t *sign_bits,
+                          float clip, uint8_t *q, void *scale, void *zero, cudaStream_t stream) {
+    if (M < 1 || !quant_token_tc_takes(K, kfac)) return -1000;
+    const int P = (int)(K / 64);
+    const int B = P / kfac;
+    if ((reinterpret_cast<uintptr_t>(q) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0 || ld % 8 != 0) return -1000;
+    if (M > 0x7fffffffL / 2) return -1000;                       // TMA coordinates are 32-bit
+    TcQuantParams p;
+    p.M = M; p.K = (int)K; p.P = P; p.kfac = kfac; p.B = B;
+    p.words = (kfac + 31) / 32;
+    p.sign_bits = kfac > 1 ? sign_bits : nullptr;
+    p.R = P <= 64 ? 2 : 1;
+    p.T = P > 128 ? 2 : 1;
+    const int boxP = p.R == 2 ? 64 : (P + 15) / 16 * 16;
+    p.Kdim = p.R == 2 ? 128 : boxP;
+    p.Mtot = 128 * p.T;
+    p.a_bytes = ((p.Kdim + 63) / 64) * p.Mtot * 128;
+    const int budget = 227 * 1024 - 7168 - 1024 - p.a_bytes;     // aux (reductions, barriers, sign words) + alignment slack
+    // the widest MMA (N = 64 NB columns, NB rows or row pairs per instruction) that leaves room for two stages; small
+    // batches take narrower ones so that the rows spread over more SMs
+    int NB = 4 / p.T;
+    while (NB > 1 && (2 * p.R * NB * boxP * 128 > budget || (M + (long)p.R * NB - 1) / ((long)p.R * NB) < kNumSMs)) NB >>= 1;
+    p.NB = NB;
+    p.stage_bytes = p.R * NB * boxP * 128;
+    int stages = budget / p.stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return -1000;
+    p.stages = stages;
+    p.bf16 = in_dtype == FLH_B200_BF16;
+    p.clip = clip;
+    p.c = sqrtf((float)K);
+    p.q = q;
+    p.scale = static_cast<__half *>(scale);
+    p.zero = static_cast<__half *>(zero);
+    CUtensorMap map;
+    MapKey key{x, M, ld, P, boxP, p.R * NB};
+    int rc = get_map(key, &map);
+    if (rc) return rc;
+    const int smem = p.a_bytes + stages * p.stage_bytes + 7168 + 1024;
+    // FLH_B200_TC_PROFILE=1 (read once): the variant that times its waits for flh_b200_quant_token_wait_profile
+    static int profile = -1;
+    if (profile < 0) { const char *e = getenv("FLH_B200_TC_PROFILE"); profile = (e && atoi(e) != 0) ? 1 : 0; }
+    using Kern = void (*)(const CUtensorMap, const TcQuantParams);
+    const Kern kern = profile ? quant_token_tc_kernel<true> : quant_token_tc_kernel<false>;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+    if (dev < 0 || !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return cuda_status(e, "quant_token_tc smem attribute");
+        if (dev >= 0) attr_done[dev] = true;
+    }
+    const long n_units = (M + (long)p.R * NB - 1) / ((long)p.R * NB);
+    const long grid = n_units < kNumSMs ? n_units : kNumSMs;
+    kern<<<(unsigned)grid, kThreadsTc, smem, stream>>>(map, p);
+    return cuda_status(cudaGetLastError(), "quant_token_tc launch");
+}
+
+int quant_token_tc_wait_profile(unsigned long long *out8) {
+    cudaError_t e = cudaMemcpyFromSymbol(out8, g_wait_tc, sizeof(unsigned long long) * 8);
+    if (e != cudaSuccess) return cuda_status(e, "wait profile read");
+    unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    return cuda_status(cudaMemcpyToSymbol(g_wait_tc, z, sizeof(z)), "wait profile clear");
+}
+
+int quant_token_tc_status(int *out4) {
+    return cuda_status(cudaMemcpyFromSymbol(out4, g_status_tc, sizeof(int) * 4), "status read");
+}
+int quant_token_tc_status_clear() {
+    int z[4] = {0, 0, 0, 0};
+    return cuda_status(cudaMemcpyToSymbol(g_status_tc, z, sizeof(z)), "status clear");
+}
+
+}  // namespace flh

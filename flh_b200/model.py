@@ -23,7 +23,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from . import _CUDA
+from . import _CUDA, timing
 from .nn import ActQuantizer, LinearFLH
 from .tp import ColumnParallelLinearFLH, RowParallelLinearFLH
 
@@ -123,32 +123,43 @@ class DecoderLayer(torch.nn.Module):
         cfg = self.cfg
         B, S, _ = x.shape
         hd = cfg.head_dim
-        s, z, q = self._norm_quant(self.norm1, self.q_in, x)
+        with timing.region("quant"):
+            s, z, q = self._norm_quant(self.norm1, self.q_in, x)
         qkv = self.qkv(q, s, z)
-        qh, kh, vh = qkv.split((self.nh * hd, self.nkv * hd, self.nkv * hd), dim=-1)
-        qh = rope(qh.view(B, S, self.nh, hd), pos, cfg.rope_theta).transpose(1, 2)
-        kh = rope(kh.view(B, S, self.nkv, hd), pos, cfg.rope_theta).transpose(1, 2)
-        vh = vh.view(B, S, self.nkv, hd).transpose(1, 2)
-        mask, causal = None, S > 1
-        if cache is not None:
-            kc, vc, cur = cache
-            kc[:, :, cur:cur + S] = kh
-            vc[:, :, cur:cur + S] = vh
-            kh, vh = kc[:, :, :cur + S], vc[:, :, :cur + S]
-            if cur > 0 and S > 1:
-                # a chunk appended to a filled cache: query i sees keys 0 .. cur + i (torch's is_causal aligns the
-                # triangle with the top-left corner, which is only right for cur = 0)
-                mask, causal = torch.ones(S, cur + S, dtype=torch.bool, device=x.device).tril(diagonal=cur), False
-        att = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, is_causal=causal, enable_gqa=self.nh != self.nkv)
-        att = att.transpose(1, 2).reshape(B, S, self.nh * hd)
-        s, z, q = self.q_attn(att)
-        x = x + self.o(q, s, z)
-        s, z, q = self._norm_quant(self.norm2, self.q_mlp, x)
+        with timing.region("glue"):
+            qh, kh, vh = qkv.split((self.nh * hd, self.nkv * hd, self.nkv * hd), dim=-1)
+            qh = rope(qh.view(B, S, self.nh, hd), pos, cfg.rope_theta).transpose(1, 2)
+            kh = rope(kh.view(B, S, self.nkv, hd), pos, cfg.rope_theta).transpose(1, 2)
+            vh = vh.view(B, S, self.nkv, hd).transpose(1, 2)
+            mask, causal = None, S > 1
+            if cache is not None:
+                kc, vc, cur = cache
+                kc[:, :, cur:cur + S] = kh
+                vc[:, :, cur:cur + S] = vh
+                kh, vh = kc[:, :, :cur + S], vc[:, :, :cur + S]
+                if cur > 0 and S > 1:
+                    # a chunk appended to a filled cache: query i sees keys 0 .. cur + i (torch's is_causal aligns the
+                    # triangle with the top-left corner, which is only right for cur = 0)
+                    mask, causal = torch.ones(S, cur + S, dtype=torch.bool, device=x.device).tril(diagonal=cur), False
+        with timing.region("attention"):
+            att = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, is_causal=causal, enable_gqa=self.nh != self.nkv)
+            att = att.transpose(1, 2).reshape(B, S, self.nh * hd)
+        with timing.region("quant"):
+            s, z, q = self.q_attn(att)
+        y = self.o(q, s, z)
+        with timing.region("glue"):
+            x = x + y
+        with timing.region("quant"):
+            s, z, q = self._norm_quant(self.norm2, self.q_mlp, x)
         gu = self.gate_up(q, s, z)
-        g, u = gu.chunk(2, dim=-1)
-        a = F.silu(g) * u
-        s, z, q = self.q_down(a)
-        return x + self.down(q, s, z)
+        with timing.region("glue"):
+            g, u = gu.chunk(2, dim=-1)
+            a = F.silu(g) * u
+        with timing.region("quant"):
+            s, z, q = self.q_down(a)
+        y = self.down(q, s, z)
+        with timing.region("glue"):
+            return x + y
 
 
 class Decoder(torch.nn.Module):

@@ -16,6 +16,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from . import timing
 from .nn import LinearFLH
 
 
@@ -76,7 +77,8 @@ class ColumnParallelLinearFLH(torch.nn.Module):
         self.shard, self.group, self.gather_output = shard, group, gather_output
 
     def forward(self, x, a_scale=None, a_zero=None, **kw):
-        y = self.shard(x, a_scale, a_zero, **kw)
+        with timing.region("gemm"):
+            y = self.shard(x, a_scale, a_zero, **kw)
         if self.gather_output and dist.is_initialized() and dist.get_world_size(self.group) > 1:
             parts = [torch.empty_like(y) for _ in range(dist.get_world_size(self.group))]
             dist.all_gather(parts, y.contiguous(), group=self.group)
@@ -91,7 +93,9 @@ class RowParallelLinearFLH(torch.nn.Module):
 
     def forward(self, x, a_scale=None, a_zero=None, **kw):
         """x, a_scale, a_zero: this rank's slice of the quantised activations."""
-        y = self.shard(x, a_scale, a_zero, **kw)
+        with timing.region("gemm"):
+            y = self.shard(x, a_scale, a_zero, **kw)
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
-            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+            with timing.region("allreduce"):
+                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         return y

@@ -82,18 +82,27 @@ int flh_b200_hadamard_f16_inplace(void *x, long rows, int n, void *stream);
  * hadamard = 0: quantise x itself.  hadamard = 1 or 2: quantise (hadK (x) H_p) x / sqrt(K) with
  * K = kfac * p, p a power of two >= 64; kfac = 1 for a power-of-two K, otherwise one of the
  * orders get_hadK knows (flh/functional/hadamard.py:39-89) with sign_bits = the factor table made
- * by flh_b200_pack_signs (copied to the device, 16-byte aligned).  The butterflies run in binary32
- * in the order of matmul_hadU (flh/functional/hadamard.py:92-113); 1/sqrt(K) is folded into the
- * scale.  The kfac x kfac factor is applied on the tensor cores with hadamard = 1 and kfac >= 64 (exact 3-term
- * bfloat16 split of the binary32 inputs, binary32 accumulation: same value up to the order of the
- * roundings; the reference's own matmul has no fixed order either) or, with hadamard = 2, summed
- * k' ascending on the CUDA cores (bit-exact with the CPU oracle, about five times slower for kfac = 172).
+ * by flh_b200_pack_signs (copied to the device, 16-byte aligned); 1/sqrt(K) is folded into the scale.
+ *   hadamard = 2: binary32 butterflies in the order of matmul_hadU (flh/functional/hadamard.py:92-113), the
+ *     kfac x kfac factor summed k' ascending: bit-exact with the CPU oracle for every K.
+ *   hadamard = 1 (default of the Python layer): for K = P * 64 with P <= 256 (4096, 8192, 11008, 14336, 16384 and the
+ *     tensor-parallel shards 7168 / 3584 ...) the part of the transform above the lowest six bits — a P x P matrix of
+ *     +-1 — is applied first, to the raw 16-bit inputs, by tcgen05.mma (products exact, binary32 accumulation in the
+ *     tensor core's order); the lowest six bits follow as binary32 butterflies.  Same values up to the order of the
+ *     binary32 additions (the reference's own matmul has no fixed order either); measured against the oracle: at most
+ *     0.1 % of all codes differ, by one step, scales within one f16 ulp.  Every M takes the same kernel, so a row's
+ *     codes do not depend on the batch it arrives in.  Other K (28672, 32768): as hadamard = 2, except that factors of
+ *     order >= 64 are summed by mma.sync.
  * Quantiser: ActQuantizer.find_params / asym_quant (fake_quant/quant_utils.py:94-128, 17-21)
  * with the scale rounded to f16 before use.  q [M, K/2] codes 0..15; scale, zero [M] f16.
  * clip = the quantiser's clip_ratio in (0, 1]. */
 int flh_b200_quant_token_asym_i4(const void *x, int in_dtype, long M, long K, long ld,
                                  int hadamard, int kfac, const uint32_t *sign_bits, float clip,
                                  uint8_t *q, void *scale, void *zero, void *stream);
+
+/* Diagnostic: the name of the kernel flh_b200_quant_token_asym_i4 launches for this shape (16-byte aligned pointers
+ * assumed).  A static string.  No counterpart in FLH. */
+const char *flh_b200_quant_token_kernel(long M, long K, int hadamard, int kfac);
 
 /* RMS-norm (weight 1, as FLH leaves it after folding the norm weight into the next linear) fused in front of the
  * per-token asymmetric quantiser, K = 4096 or 8192: the decoder's "norm -> quantise" pair as one pass over the row.
@@ -134,8 +143,11 @@ int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t
 
 /* D[M, N] = dequantising int4 x int4 GEMM.
  *   A [M, K/2], B [N, K/2] packed int4 (B signed; A signed when a_zero == NULL, else unsigned);
- *   a_scale [M, K/a_group] f16, a_group in {128, K};  a_zero NULL or f16 like a_scale (integer
- *   values 0..15);  b_scale [N, K/b_group] f16, b_group in {128, K};
+ *   a_scale [M, K/a_group] f16, a_group in {g, K};  a_zero NULL or f16 like a_scale (integer
+ *   values 0..15);  b_scale [N, K/b_group] f16, b_group in {g, K};  g in {32, 64, 128} is the K-group the
+ *   integer sums are cut into (groups of 32 and 64 — the reference's *_gs entry points — are served by the
+ *   mma.sync tile kernel, algo AUTO or MMA_SYNC; every group is scaled with its own scales, where the reference
+ *   kernel flh/kernels/gemm_and_dequant_i4_gs.cu:408 takes the first scale of each 128-K block for the whole block);
  *   b_rowsum [N, K/min(a_group, b_group)] int32, required when a_zero != NULL;
  *   bias NULL or [N] f16;  D f16 or bf16 (out_dtype).
  *   With g running over K-groups of min(a_group, b_group) in ascending order:
@@ -219,6 +231,12 @@ int flh_b200_gemm_status(int *out);
  * int8 slot, out[6] epilogue on a finished accumulator).  Reads and clears; SYNCHRONISES the device.
  * out: 8 x unsigned long long in HOST memory.  No counterpart in FLH. */
 int flh_b200_gemm_wait_profile(unsigned long long *out);
+
+/* Diagnostic of the tensor-core token quantiser (quant_token_tc_kernel), same conventions: nanoseconds summed over CTAs
+ * since the last call — out[0] CTA lifetime, out[1] TMA thread on a free shared-memory stage, out[2] MMA thread on TMA
+ * data, out[3] MMA thread on a free accumulator slot, out[4] the 16 epilogue warps on a finished accumulator (summed
+ * over warps), out[5] set-up.  Reads and clears; SYNCHRONISES the device.  out: 8 x unsigned long long in HOST memory. */
+int flh_b200_quant_token_wait_profile(unsigned long long *out);
 
 /* The reference's one true C symbol, same signature and meaning
  * (flh/kernels/gemm_and_dequant_i4.cu:471-480): group-128 symmetric scales, f16 output,

@@ -108,6 +108,32 @@ def test_mma_tile_kernel_bias_bf16(cuda):
     run_case(cuda, MMA, make_case(6, 130, 128, 128, 128, 128, False, bias=True))
 
 
+@pytest.mark.parametrize("gs", [32, 64])
+@pytest.mark.parametrize("m", [1, 16, 130, 300])
+@pytest.mark.parametrize("groups", [("g", "g", False), ("g", "g", True), (0, "g", True), ("g", 0, False)])
+def test_group_32_64(cuda, gs, m, groups):
+    """K-groups of 32 and 64 (the reference's *_gs entry points, flh/kernels/gemm_and_dequant_i4_gs.cu:335-492), every
+    group scaled with its own scales: bit-exact against the oracle, which folds one exact integer sum per group."""
+    ag, bg, asym = groups
+    ag, bg = (gs if ag == "g" else 0), (gs if bg == "g" else 0)
+    run_case(cuda, 0, make_case(60 * m + gs, m, 256, 1024, ag, bg, asym, bias=(m == 16)), bf16=(m == 130))
+
+
+@pytest.mark.parametrize("gs", [32, 64, 128])
+def test_gs_binding(cuda, gs):
+    """gemm_i4_dequant_o16_gs (flh/cuda/flh_cuda_bindings.cpp:253-299) with the scale shapes the reference's
+    quantiser emits, [.., K / gs]: equal to the oracle; and a wrong scale shape raises as TORCH_CHECK does."""
+    m, n, k = 70, 384, 2048
+    ap, bp, sa, sb, _, _ = make_case(900 + gs, m, n, k, gs, gs, False)
+    d = cuda.gemm_i4_dequant_o16_gs(_dev(ap), _dev(bp), _dev(sa), _dev(sb), gs)
+    ref = O.gemm_i4_dequant(ap, bp, sa, sb)
+    assert np.array_equal(d.cpu().numpy().view(np.uint16), ref.view(np.uint16))
+    with pytest.raises(RuntimeError):
+        cuda.gemm_i4_dequant_o16_gs(_dev(ap), _dev(bp), _dev(sa)[:, :-1].contiguous(), _dev(sb), gs)
+    with pytest.raises(RuntimeError):
+        cuda.gemm_i4_dequant_o16_gs(_dev(ap), _dev(bp), _dev(sa), _dev(sb), 48)
+
+
 def test_c_symbol_of_the_reference(cuda):
     # flhDenseLayerGEMM_i4_o16: same signature as flh/kernels/gemm_and_dequant_i4.cu:471-480
     import ctypes
