@@ -104,7 +104,21 @@ def save_quantized(model: Decoder, save_directory: str) -> None:
         json.dump(arch, f, indent=2)
 
 
-def _linear_from(sd, names, k, device, gs, rows=None, cols=None, group_cols=None):
+def _load_state_dict(path):
+    """model.pt as a dict of CPU tensors, memory-mapped where torch can.  The reference writes it with pickle protocol 4
+    (modeling_llama.py:1107), which torch's restricted unpickler does not read: such a file — a plain dict of tensors
+    written by save_quantized — is then read with the full unpickler."""
+    import pickle
+    for kw in ({"mmap": True, "weights_only": True}, {"weights_only": True}, {"mmap": True, "weights_only": False},
+               {"weights_only": False}):
+        try:
+            return torch.load(path, map_location="cpu", **kw)
+        except (TypeError, RuntimeError, pickle.UnpicklingError):
+            continue
+    raise RuntimeError(f"cannot read {path}")
+
+
+def _linear_from(sd, names, k, device, gs, rows=None, cols=None):
     """One LinearFLH from the saved tensors of `names` (concatenated along the output rows), restricted to rows
     [rows[0], rows[1]) of EACH named tensor or to K-columns [cols[0], cols[1]); only the slice is copied to the device."""
     wps, wss, wzs, bs = [], [], [], []
@@ -148,10 +162,7 @@ def load_quantized(load_directory: str, device="cuda", tp_rank: int = 0, tp_worl
     if quant.get("weight_bits", 4) != 4 or quant.get("act_bits", 4) != 4:
         raise ValueError("flh_b200 serves W4A4 checkpoints")
     path = os.path.join(load_directory, "model.pt")
-    try:
-        sd = torch.load(path, map_location="cpu", mmap=True, weights_only=True)
-    except (TypeError, RuntimeError):
-        sd = torch.load(path, map_location="cpu", weights_only=True)
+    sd = _load_state_dict(path)
     kw = {ours: arch[hf] for hf, ours in _ARCH_KEYS.items() if hf in arch}
     kw.setdefault("n_kv_heads", kw["n_heads"])
     if n_layers is not None:
@@ -190,11 +201,8 @@ def load_quantized(load_directory: str, device="cuda", tp_rank: int = 0, tp_worl
         down = _linear_from(sd, [p + "mlp.down_proj"], cfg.ffn, device, gs,
                             cols=(tp_rank * cfg.ffn // tp_world, (tp_rank + 1) * cfg.ffn // tp_world))
         down.full_hadamard_blocks = 1 if blocks else 0
-        if tp_rank != 0:                      # the all-reduced sum carries a bias once
-            for lin in (layer.o.shard if False else None, ):
-                pass
         layer.down = RowParallelLinearFLH(down, group)
-        for lin in (layer.o.shard, layer.down.shard):
+        for lin in (layer.o.shard, layer.down.shard):      # the all-reduced sum must carry a bias once
             if lin.bias is not None and tp_rank != 0:
                 lin.bias.zero_()
         layer.norm1.weight.data.copy_(sd[p + "input_layernorm.weight"])

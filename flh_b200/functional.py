@@ -60,3 +60,20 @@ def unpack_i4(x: torch.Tensor, signed: bool = True) -> torch.Tensor:
         lo = torch.where(lo >= 8, lo - 16, lo)
         hi = torch.where(hi >= 8, hi - 16, hi)
     return torch.stack((lo, hi), dim=-1).reshape(*x.shape[:-1], x.shape[-1] * 2)
+
+
+def expand_i4_reference(packed):
+    """Host restatement of flh_b200_expand_i4: packed int4 [rows, K/2] -> bytes [rows, K] holding 16 * code (the nibble in the
+    byte's high half), per 32 elements the 16 even ones then the 16 odd ones."""
+    rows, kp = packed.shape
+    b = packed.view(rows, kp // 16, 16)
+    even, odd = (b << 4) & 0xF0, b & 0xF0
+    return torch.cat((even, odd), dim=-1).reshape(rows, 2 * kp)
+
+
+def compress_i8(expanded):
+    """Inverse of the int8 expansion (flh_b200_expand_i4 / expand_i4_reference): bytes [rows, K] -> packed int4 [rows, K/2] in
+    the checkpoint layout (byte j = element 2j in the low nibble, 2j + 1 in the high one).  Lossless."""
+    rows, k = expanded.shape
+    b = expanded.view(rows, k // 32, 2, 16)
+    return ((b[:, :, 0, :] >> 4) | (b[:, :, 1, :] & 0xF0)).reshape(rows, k // 2)

@@ -56,7 +56,9 @@ def matmul_hadU(X: torch.Tensor) -> torch.Tensor:
     if k > 1:
         hk = torch.from_numpy(signs.astype(np.float64)).to(device=X.device, dtype=X.dtype)
         x = hk @ x
-    return (x.reshape(X.shape) / math.sqrt(n)).to(X.dtype)
+    # (a tensor divisor: torch's CUDA kernels turn a division by a Python scalar into a multiplication by its reciprocal,
+    # which is not the same rounding as the host's division)
+    return (x.reshape(X.shape) / torch.tensor(math.sqrt(n), dtype=x.dtype, device=x.device)).to(X.dtype)
 
 
 def hadamard_group(X: torch.Tensor, group_size: int) -> torch.Tensor:

@@ -131,8 +131,10 @@ class WeightQuantizer(torch.nn.Module):
             return
         g = self._grouped(self._prep(weight))
         with torch.no_grad():
+            # divisors are tensors: torch's CUDA kernels replace a division by a Python scalar with a multiplication by its
+            # reciprocal, and a weight converted on the GPU must come out bit-equal to one converted on the host
             if self.sym:
-                qmax = 2 ** (self.bits - 1) - 1
+                qmax = torch.tensor(float(2 ** (self.bits - 1) - 1), dtype=g.dtype, device=g.device)
                 if self.group_size <= 0 and self.channel_wise:
                     xmax = torch.maximum(g.amin(dim=-1).clamp(max=0).abs(), g.amax(dim=-1).clamp(min=0)).clamp(min=1e-5)
                     scale = xmax / qmax
@@ -140,7 +142,7 @@ class WeightQuantizer(torch.nn.Module):
                     scale = torch.clamp(g.abs().amax(dim=-1) / qmax, min=1e-8)
                 zero = torch.zeros_like(scale)
             else:
-                qmax = 2 ** self.bits - 1
+                qmax = torch.tensor(float(2 ** self.bits - 1), dtype=g.dtype, device=g.device)
                 mx, mn = g.amax(dim=-1), g.amin(dim=-1)
                 scale = torch.clamp((mx - mn) / qmax, min=1e-8)
                 zero = -mn / scale
