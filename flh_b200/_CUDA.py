@@ -203,6 +203,53 @@ def quant_token_asym_i4(x, hadamard: bool = True, clip: float = 1.0, exact: bool
     return q, s, z
 
 
+def silu_mul(gu):
+    """SiLU(gate) * up of the merged gate/up GEMM output gu [M, 2F] (row stride allowed) -> [M, F] (include/flh_b200.h)."""
+    _check(gu.is_cuda and gu.dtype in (torch.float16, torch.bfloat16), "gu must be a CUDA float16 or bfloat16 tensor")
+    _check(gu.dim() == 2 and gu.stride(1) == 1 and gu.shape[1] % 2 == 0, "gu must be [M, 2F] with unit inner stride")
+    M, F = gu.shape[0], gu.shape[1] // 2
+    out = torch.empty((M, F), dtype=gu.dtype, device=gu.device)
+    with _guard(gu.device):
+        _lib.check(_lib.load().flh_b200_silu_mul(_ptr(gu), BF16 if gu.dtype == torch.bfloat16 else F16, M, F,
+                                                 gu.stride(0) if M > 1 else 2 * F, _ptr(out), _stream(gu)), "silu_mul")
+    return out
+
+
+def silu_mul_quant_token_asym_i4(gu, hadamard: bool = True, clip: float = 1.0, exact: bool = False):
+    """SiLU(gate) * up of gu [M, 2F], then (optionally the full-width transform and) the per-token asymmetric quantiser:
+    one kernel when the tensor-core quantiser takes the width (hadamard=True, exact=False, F = P * 64 with P <= 256), else
+    silu_mul followed by quant_token_asym_i4 — the same result either way.  -> (q u8[M, F/2], scale f16[M], zero f16[M])."""
+    _check(gu.is_cuda and gu.dtype in (torch.float16, torch.bfloat16), "gu must be a CUDA float16 or bfloat16 tensor")
+    _check(gu.dim() == 2 and gu.stride(1) == 1 and gu.shape[1] % 2 == 0, "gu must be [M, 2F] with unit inner stride")
+    M, F = gu.shape[0], gu.shape[1] // 2
+    lib = _lib.load()
+    if hadamard and not exact and M > 0:
+        kfac, bits = _sign_bits(F, gu.device)
+        if lib.flh_b200_quant_token_kernel(M, F, 1, kfac) == b"quant_token_tc_kernel":
+            q = torch.empty((M, F // 2), dtype=torch.uint8, device=gu.device)
+            s = torch.empty((M,), dtype=torch.float16, device=gu.device)
+            z = torch.empty((M,), dtype=torch.float16, device=gu.device)
+            with _guard(gu.device):
+                _lib.check(lib.flh_b200_silu_mul_quant_token_asym_i4(
+                    _ptr(gu), BF16 if gu.dtype == torch.bfloat16 else F16, M, F, gu.stride(0) if M > 1 else 2 * F, 1, kfac,
+                    _ptr(bits), float(clip), _ptr(q), _ptr(s), _ptr(z), _stream(gu)), "silu_mul_quant_token_asym_i4")
+            return q, s, z
+    return quant_token_asym_i4(silu_mul(gu), hadamard=hadamard, clip=clip, exact=exact)
+
+
+def rope_kv(qkv, cos, sin, q_out, k_cache, v_cache, B, S, nh, nkv, cur):
+    """Rotary embedding of q and k + KV-cache write from the merged QKV GEMM output (include/flh_b200.h: flh_b200_rope_kv_f16).
+    qkv f16 [B*S, (nh + 2 nkv) * D] contiguous; cos, sin f32 [S, D/2]; q_out [B, nh, S, D]; caches [B, nkv, T, D] contiguous."""
+    _check(qkv.is_cuda and qkv.dtype == torch.float16 and qkv.is_contiguous(), "qkv must be a contiguous CUDA float16 tensor")
+    _check(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous(), "cos / sin must be contiguous float32")
+    _check(q_out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous(), "outputs must be contiguous")
+    D = q_out.shape[-1]
+    with _guard(qkv.device):
+        _lib.check(_lib.load().flh_b200_rope_kv_f16(_ptr(qkv), _ptr(cos), _ptr(sin), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+                                                    B, S, nh, nkv, D, k_cache.shape[2], cur, _stream(qkv)), "rope_kv")
+    return q_out
+
+
 def rmsnorm_quant_token_asym_i4(x, eps: float, hadamard: bool = False, clip: float = 1.0):
     """RMS-norm (weight 1) + per-token asymmetric int4 in one pass, K = 4096 or 8192 (include/flh_b200.h).
     x [M, K] f16/bf16 (row stride allowed) -> (q u8[M,K/2], scale f16[M], zero f16[M])."""

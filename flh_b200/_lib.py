@@ -23,6 +23,11 @@ SIGNATURES = {
     "flh_b200_quant_token_asym_i4": (c_int, [c_void_p, c_int, c_long, c_long, c_long, c_int, c_int, c_void_p, c_float,
                                              c_void_p, c_void_p, c_void_p, c_void_p]),
     "flh_b200_quant_token_kernel": (ctypes.c_char_p, [c_long, c_long, c_int, c_int]),
+    "flh_b200_silu_mul": (c_int, [c_void_p, c_int, c_long, c_long, c_long, c_void_p, c_void_p]),
+    "flh_b200_silu_mul_quant_token_asym_i4": (c_int, [c_void_p, c_int, c_long, c_long, c_long, c_int, c_int, c_void_p, c_float,
+                                                      c_void_p, c_void_p, c_void_p, c_void_p]),
+    "flh_b200_rope_kv_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_int, c_void_p]),
     "flh_b200_sign_table_bytes": (c_size_t, [c_int]),
     "flh_b200_pack_signs": (c_int, [c_void_p, c_int, c_void_p]),
     "flh_b200_weight_rowsum": (c_int, [c_void_p, c_long, c_long, c_long, c_void_p, c_void_p]),

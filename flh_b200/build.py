@@ -14,7 +14,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["api.cu", "quant_group.cu", "quant_token.cu", "quant_token_warp.cu", "quant_token_factor.cu", "quant_token_tc.cu", "gemm_mma.cu", "gemm_tcgen05.cu", "gemm_i8.cu"]
+SOURCES = ["api.cu", "quant_group.cu", "quant_token.cu", "quant_token_warp.cu", "quant_token_factor.cu", "quant_token_tc.cu", "act.cu", "gemm_mma.cu", "gemm_tcgen05.cu", "gemm_i8.cu"]
 LIB = os.path.join(HERE, "libflh_b200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
@@ -31,7 +31,7 @@ def _stale(target: str, deps) -> bool:
 
 def build(verbose: bool = False, force: bool = False) -> str:
     nvcc = os.environ.get("NVCC", "nvcc")
-    headers = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "token_common.cuh"), os.path.join(CSRC, "tc_common.cuh"), os.path.join(HERE, "..", "include", "flh_b200.h")]
+    headers = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "token_common.cuh"), os.path.join(CSRC, "tc_common.cuh"), os.path.join(CSRC, "act_common.cuh"), os.path.join(HERE, "..", "include", "flh_b200.h")]
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
     jobs = []

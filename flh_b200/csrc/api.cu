@@ -59,6 +59,9 @@ int gemm_i8_status(int *);
 int quant_token_factor_status(int *);
 int quant_token_factor_status_clear();
 const char *quant_token_kernel_name(long, long, int, int);
+int launch_silu_mul(const void *, int, long, long, long, void *, cudaStream_t);
+int launch_silu_mul_quant_token_tc(const void *, int, long, long, long, int, const uint32_t *, float, uint8_t *, void *, void *, cudaStream_t);
+int launch_rope_kv(const void *, const float *, const float *, void *, void *, void *, int, int, int, int, int, int, int, cudaStream_t);
 int quant_token_tc_status(int *);
 int quant_token_tc_wait_profile(unsigned long long *);
 int quant_token_tc_status_clear();
@@ -166,6 +169,44 @@ int flh_b200_rmsnorm_quant_token_asym_i4(const void *x, int in_dtype, long M, lo
     FLH_REQUIRE(aligned16(x), FLH_B200_EALIGN, "x must be 16-byte aligned");
     FLH_REQUIRE(aligned16(q), FLH_B200_EALIGN, "q must be 16-byte aligned");
     return launch_quant_token_warp(x, in_dtype, M, K, ld, hadamard, eps, clip, q, scale, zero, static_cast<cudaStream_t>(stream));
+}
+
+int flh_b200_silu_mul(const void *gu, int in_dtype, long M, long F, long ld, void *out, void *stream) {
+    FLH_REQUIRE(M >= 0 && F > 0 && F % 8 == 0, FLH_B200_EINVAL, "bad shape M=%ld F=%ld (F must be a multiple of 8)", M, F);
+    FLH_REQUIRE(in_dtype == FLH_B200_F16 || in_dtype == FLH_B200_BF16, FLH_B200_EINVAL, "in_dtype must be F16 or BF16");
+    FLH_REQUIRE(ld >= 2 * F && ld % 8 == 0, FLH_B200_EALIGN, "row stride %ld must be >= 2F and a multiple of 8", ld);
+    if (M == 0) return 0;
+    FLH_REQUIRE(gu && out, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(aligned16(gu) && aligned16(out), FLH_B200_EALIGN, "gu and out must be 16-byte aligned");
+    return launch_silu_mul(gu, in_dtype, M, F, ld, out, static_cast<cudaStream_t>(stream));
+}
+
+int flh_b200_silu_mul_quant_token_asym_i4(const void *gu, int in_dtype, long M, long F, long ld, int hadamard, int kfac,
+                                          const uint32_t *sign_bits, float clip, uint8_t *q, void *scale, void *zero,
+                                          void *stream) {
+    FLH_REQUIRE(M >= 0 && F > 0 && F % 64 == 0, FLH_B200_EINVAL, "bad shape M=%ld F=%ld (F must be a multiple of 64)", M, F);
+    FLH_REQUIRE(in_dtype == FLH_B200_F16 || in_dtype == FLH_B200_BF16, FLH_B200_EINVAL, "in_dtype must be F16 or BF16");
+    FLH_REQUIRE(ld >= 2 * F && ld % 8 == 0, FLH_B200_EALIGN, "row stride %ld must be >= 2F and a multiple of 8", ld);
+    FLH_REQUIRE(clip > 0.0f && clip <= 1.0f, FLH_B200_EINVAL, "clip must be in (0, 1]");
+    FLH_REQUIRE(kfac >= 1 && F % kfac == 0 && (kfac == 1 || sign_bits), FLH_B200_EINVAL, "kfac=%d must divide F=%ld and come with its sign bits", kfac, F);
+    if (hadamard != 1) return fail(FLH_B200_EUNSUPPORTED, "the fused form exists for hadamard = 1 only; run flh_b200_silu_mul and the quantiser separately");
+    if (M == 0) return 0;
+    FLH_REQUIRE(gu && q && scale && zero, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(aligned16(gu) && aligned16(q), FLH_B200_EALIGN, "gu and q must be 16-byte aligned");
+    const int rc = launch_silu_mul_quant_token_tc(gu, in_dtype, M, F, ld, kfac, sign_bits, clip, q, scale, zero, static_cast<cudaStream_t>(stream));
+    if (rc == -1000) return fail(FLH_B200_EUNSUPPORTED, "F=%ld is not a width the tensor-core quantiser takes (F = P * 64, P <= 256); run the two steps separately", F);
+    return rc;
+}
+
+int flh_b200_rope_kv_f16(const void *qkv, const float *cos, const float *sin, void *q_out, void *k_cache, void *v_cache,
+                         int B, int S, int nh, int nkv, int D, int T, int cur, void *stream) {
+    FLH_REQUIRE(B >= 0 && S >= 0 && nh > 0 && nkv > 0 && D > 0 && D % 8 == 0, FLH_B200_EINVAL, "bad shape B=%d S=%d nh=%d nkv=%d D=%d", B, S, nh, nkv, D);
+    FLH_REQUIRE(cur >= 0 && cur + S <= T, FLH_B200_EINVAL, "positions %d .. %d do not fit a cache of %d", cur, cur + S - 1, T);
+    if (B == 0 || S == 0) return 0;
+    FLH_REQUIRE(qkv && cos && sin && q_out && k_cache && v_cache, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(aligned16(qkv) && aligned16(cos) && aligned16(sin) && aligned16(q_out) && aligned16(k_cache) && aligned16(v_cache),
+                FLH_B200_EALIGN, "pointers must be 16-byte aligned");
+    return launch_rope_kv(qkv, cos, sin, q_out, k_cache, v_cache, B, S, nh, nkv, D, T, cur, static_cast<cudaStream_t>(stream));
 }
 
 const char *flh_b200_quant_token_kernel(long M, long K, int hadamard, int kfac) {

@@ -21,8 +21,10 @@
 // groups of four, one group per 128-lane accumulator tile), one TMA thread, one MMA thread.  Rings: shared-memory stages
 // (TMA -> MMA), 64-column TMEM slots (MMA -> epilogue).  All mbarrier waits are bounded; a wait that runs out sets a status word,
 // the warps keep walking their loops without touching the tensor core so that every named barrier is still reached.
+#include <string.h>
 #include "tc_common.cuh"
 #include "token_common.cuh"
+#include "act_common.cuh"
 
 namespace flh {
 namespace {
@@ -45,9 +47,13 @@ struct TcQuantParams {
     const uint32_t *sign_bits; // kfac rows of bits (1 = negative), or null for kfac = 1
     int R, T;                  // rows per 128-lane accumulator block (2 when P <= 64), tiles per row (2 when P > 128)
     int NB;                    // 64-column blocks per MMA: N = 64 * NB, i.e. R * NB rows per unit
+    int CK, nchunks;           // a stage holds CK rows of the contraction (the K dimension of the MMAs) of every row of the unit;
+                               // a unit is nchunks stages (1 when R = 2)
     int Kdim, Mtot;            // contraction length of the MMAs (multiple of 16), rows of A (128 or 256)
     int a_bytes, stage_bytes, stages;
     int bf16;
+    const uint8_t *gu;         // FUSE: merged gate/up matrix [M][2K] (gate = the first K columns), row stride gu_ld_bytes
+    long gu_ld_bytes;
     float clip, c;
     uint8_t *q;
     __half *scale, *zero;
@@ -112,7 +118,10 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 }
 
 // PROFILE: time every wait with %globaltimer and add the sums to g_wait_tc (flh_b200_quant_token_wait_profile).
-template <bool PROFILE>
+// FUSE: the rows are not read by TMA but MADE by the epilogue warps — SiLU(gate) * up of the merged gate/up GEMM output
+// (act_common.cuh), written into the stages in the layout TMA would have produced; the unit after the one whose
+// accumulators are being turned into codes is made first, so the tensor core always has a unit to work on.
+template <bool PROFILE, bool FUSE>
 __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcQuantParams p) {
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t raw = smem_u32(smem_dyn);
@@ -176,7 +185,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
         }
     }
     if (tid == 0) {
-        for (int s = 0; s < kMaxStages; ++s) { mbar_init(stage_full(s), 1); mbar_init(stage_empty(s), 1); }
+        for (int s = 0; s < kMaxStages; ++s) { mbar_init(stage_full(s), FUSE ? kEpiWarpsTc : 1); mbar_init(stage_empty(s), 1); }
         for (int u = 0; u < kSlots; ++u) { mbar_init(slot_full(u), 1); mbar_init(slot_empty(u), 4 * BPU); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -201,15 +210,18 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
     };
 
     if (warp >= kEpiWarpsTc) {
-        if (warp == kEpiWarpsTc && lane == 0) {
+        if (!FUSE && warp == kEpiWarpsTc && lane == 0) {
             // ============================================================= TMA producer
-            long it = 0;
+            long it = 0;                                 // stages issued so far
             unsigned long long w1 = 0;
-            for (long unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
-                const int s = (int)(it % S);
-                if (!wait(stage_empty(s), (uint32_t)(((it / S) & 1) ^ 1), 31, w1)) break;
-                mbar_expect_tx(stage_full(s), (uint32_t)p.stage_bytes);
-                tma_load_3d(st_base + s * p.stage_bytes, &map_x, 0, 0, (int)(unit * R * NB), stage_full(s));
+            bool ok = true;
+            for (long unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+                for (int c = 0; c < p.nchunks; ++c, ++it) {
+                    const int s = (int)(it % S);
+                    if (!wait(stage_empty(s), (uint32_t)(((it / S) & 1) ^ 1), 31, w1)) { ok = false; break; }
+                    mbar_expect_tx(stage_full(s), (uint32_t)p.stage_bytes);
+                    tma_load_3d(st_base + s * p.stage_bytes, &map_x, 0, c * p.CK, (int)(unit * R * NB), stage_full(s));
+                }
             }
             if (PROFILE) atomicAdd(&g_wait_tc[1], w1);
         } else if (warp == kEpiWarpsTc + 1 && lane == 0) {
@@ -218,31 +230,36 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
             // D binary32, A / B format, B N-major (bit 16), N = 64 NB, M = 128
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)((64 * NB) >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
             const uint32_t nblk = (uint32_t)p.stage_bytes / (uint32_t)NB;          // bytes between the 64-column blocks of B (one block = R rows)
-            const int ksteps = p.Kdim >> 4;
-            long it = 0;
+            const int ksteps = (R == 2 ? p.Kdim : p.CK) >> 4;          // K steps of 16 per stage
+            long it = 0, sc = 0;                                       // units, stages consumed so far
             unsigned long long w2 = 0, w3 = 0;
-            for (long unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++it) {
-                const int s = (int)(it % S), u = (int)(it % NU);
-                if (!wait(stage_full(s), (uint32_t)((it / S) & 1), 32, w2)) break;
+            bool ok = true;
+            for (long unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ++it) {
+                const int u = (int)(it % NU);
                 if (!wait(slot_empty(u), (uint32_t)(((it / NU) & 1) ^ 1), 33, w3)) break;
-                tc_fence_after();
-                const uint32_t bst = st_base + s * p.stage_bytes;
-                for (int t = 0; t < T; ++t) {
-                    const uint32_t d = tmem + (uint32_t)((u * BPU + t * NB) * 64);
-                    for (int ks = 0; ks < ksteps; ++ks) {
-                        // A: K-major, 8-row groups 1024 bytes apart; K step of 16 = 32 bytes inside the 128-byte row, next atom after 4
-                        const uint64_t ad = umma_desc_tc(a_base + ((ks >> 2) * (p.Mtot >> 3) + t * 16) * 1024 + (ks & 3) * 32, 16, 1024);
-                        // B: N-major (64 values of j = one 128-byte row per p), 8-row groups 1024 bytes apart (SBO), 16 rows per
-                        // K step; the NB blocks of 64 columns (different token rows) lie nblk bytes apart (LBO)
-                        const uint64_t bd = umma_desc_tc(bst + ks * 2048, nblk, 1024);
-                        const uint32_t acc = ks ? 1u : 0u;
-                        asm volatile("{\n\t.reg .pred pp;\n\tsetp.ne.b32 pp, %4, 0;\n\t"
-                                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pp;\n\t}"
-                                     ::"r"(d), "l"(ad), "l"(bd), "r"(idesc), "r"(acc) : "memory");
+                for (int c = 0; c < p.nchunks; ++c, ++sc) {
+                    const int s = (int)(sc % S);
+                    if (!wait(stage_full(s), (uint32_t)((sc / S) & 1), 32, w2)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t bst = st_base + s * p.stage_bytes;
+                    for (int t = 0; t < T; ++t) {
+                        const uint32_t d = tmem + (uint32_t)((u * BPU + t * NB) * 64);
+                        for (int ks = 0; ks < ksteps; ++ks) {
+                            const int kg = c * ksteps + ks;            // K step within the whole contraction
+                            // A: K-major, 8-row groups 1024 bytes apart; K step of 16 = 32 bytes inside the 128-byte row, next atom after 4
+                            const uint64_t ad = umma_desc_tc(a_base + ((kg >> 2) * (p.Mtot >> 3) + t * 16) * 1024 + (kg & 3) * 32, 16, 1024);
+                            // B: N-major (64 values of j = one 128-byte row per p), 8-row groups 1024 bytes apart (SBO), 16 rows per
+                            // K step; the NB blocks of 64 columns (different token rows) lie nblk bytes apart (LBO)
+                            const uint64_t bd = umma_desc_tc(bst + ks * 2048, nblk, 1024);
+                            const uint32_t acc = kg ? 1u : 0u;
+                            asm volatile("{\n\t.reg .pred pp;\n\tsetp.ne.b32 pp, %4, 0;\n\t"
+                                         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pp;\n\t}"
+                                         ::"r"(d), "l"(ad), "l"(bd), "r"(idesc), "r"(acc) : "memory");
+                        }
                     }
+                    tc_commit(stage_empty(s));
                 }
-                tc_commit(stage_empty(s));
-                tc_commit(slot_full(u));
+                if (ok) tc_commit(slot_full(u));
             }
             if (PROFILE) { atomicAdd(&g_wait_tc[2], w2); atomicAdd(&g_wait_tc[3], w3); }
         }
@@ -264,9 +281,59 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
         bool ok = true;
         int n = 0;
         unsigned long long w4 = 0;
+        // FUSE (one team of all sixteen warps, NT = 1): make the stages of unit number `iu` of this CTA
+        auto produce = [&](long iu) {
+            const long unit = blockIdx.x + iu * gridDim.x;
+            const int rows = R * NB, rowbytes_k = p.CK * 128;        // token rows of a stage, bytes of one token row in a stage
+            const long F2 = (long)p.K * 2;                           // bytes from a gate element to its up element
+            for (int c = 0; c < p.nchunks; ++c) {
+                const long sc = iu * p.nchunks + c;
+                const int s = (int)(sc % S);
+                unsigned long long w0 = 0;
+                ok = __all_sync(0xffffffffu, ok && wait(stage_empty(s), (uint32_t)(((sc / S) & 1) ^ 1), 35, w0));
+                uint8_t *st = sm + p.a_bytes + s * p.stage_bytes;
+                if (ok) {
+                    for (int xr = 0; xr < rows; ++xr) {
+                        const long row = unit * rows + xr;
+                        const uint8_t *grow = p.gu + row * p.gu_ld_bytes;
+                        // 16-byte pieces of this token row's part of the stage: piece j = (contraction row j / 8, chunk j % 8)
+                        for (int j0 = tid; j0 < p.CK * 8; j0 += 4 * kEpiWarpsTc * 32) {
+                            uint4 g[4], u[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const int j = j0 + q * kEpiWarpsTc * 32;
+                                const int pl = j >> 3, c16 = j & 7;
+                                const int prow = (R == 2 ? 0 : c * p.CK) + pl;
+                                g[q] = make_uint4(0u, 0u, 0u, 0u); u[q] = g[q];
+                                if (j < p.CK * 8 && prow < p.P && row < p.M) {
+                                    const uint8_t *src = grow + ((long)prow * 64 + c16 * 8) * 2;
+                                    g[q] = ldg_nc_v4(src);
+                                    u[q] = ldg_nc_v4(src + F2);
+                                }
+                            }
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const int j = j0 + q * kEpiWarpsTc * 32;
+                                if (j < p.CK * 8) {
+                                    const int pl = j >> 3, c16 = j & 7;
+                                    const int rs = xr * p.CK + pl;           // 128-byte row of the stage
+                                    const uint4 a = p.bf16 ? silu_mul_8<true>(g[q], u[q]) : silu_mul_8<false>(g[q], u[q]);
+                                    *reinterpret_cast<uint4 *>(st + (long)xr * rowbytes_k + pl * 128 + ((c16 ^ (rs & 7)) << 4)) = a;
+                                }
+                            }
+                        }
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(stage_full(s));
+            }
+        };
+        if (FUSE && (long)blockIdx.x < n_units) produce(0);
         for (long it = team;; it += NT, ++n) {
             const long unit = blockIdx.x + it * gridDim.x;
             if (unit >= n_units) break;
+            if (FUSE && unit + gridDim.x < n_units) produce(it + 1);
             const int u = (int)(it % NU);
             ok = __all_sync(0xffffffffu, ok && wait(slot_full(u), (uint32_t)((it / NU) & 1), 34, w4));
             uint64_t v[32];
@@ -387,7 +454,7 @@ EncodeTiledFnTc encode_fn_tc() {
 // The tensor map of an input is a pure function of (pointer, M, P, row stride, box): the last few are remembered per
 // host thread, so that a serving loop that re-uses its buffers encodes each map once.
 struct MapKey {
-    const void *x; long M, ld; int P, boxP, R;
+    const void *x; long M, ld; int P, boxP, R;          // boxP: contraction rows per TMA box, R: token rows per box
     bool operator==(const MapKey &o) const { return x == o.x && M == o.M && ld == o.ld && P == o.P && boxP == o.boxP && R == o.R; }
 };
 struct MapCache { MapKey key[8]; CUtensorMap map[8]; int used = 0, next = 0; };
@@ -427,14 +494,16 @@ bool quant_token_tc_takes(long K, int kfac) {
     return (B & (B - 1)) == 0;
 }
 
-// Full-width transform + per-token asymmetric int4 for K = P * 64, P = kfac * 2^a <= 256.  Returns -1000 when the shape
-// (or an alignment) is not one this kernel takes; the caller then uses the CUDA-core kernels.
-int launch_quant_token_tc(const void *x, int in_dtype, long M, long K, long ld, int kfac, const uint32_t *sign_bits,
-                          float clip, uint8_t *q, void *scale, void *zero, cudaStream_t stream) {
+// Full-width transform + per-token asymmetric int4 for K = P * 64, P = kfac * 2^a <= 256.  x: the rows to quantise, or
+// null with gu = the merged gate/up matrix [M][2K] whose SiLU(gate) * up is to be quantised (row stride ld either way).
+// Returns -1000 when the shape (or an alignment) is not one this kernel takes; the caller then uses the CUDA-core kernels.
+static int launch_tc(const void *x, const void *gu, int in_dtype, long M, long K, long ld, int kfac, const uint32_t *sign_bits,
+                     float clip, uint8_t *q, void *scale, void *zero, cudaStream_t stream) {
     if (M < 1 || !quant_token_tc_takes(K, kfac)) return -1000;
     const int P = (int)(K / 64);
     const int B = P / kfac;
-    if ((reinterpret_cast<uintptr_t>(q) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0 || ld % 8 != 0) return -1000;
+    const void *in = gu ? gu : x;
+    if ((reinterpret_cast<uintptr_t>(q) & 15) != 0 || (reinterpret_cast<uintptr_t>(in) & 15) != 0 || ld % 8 != 0) return -1000;
     if (M > 0x7fffffffL / 2) return -1000;                       // TMA coordinates are 32-bit
     TcQuantParams p;
     p.M = M; p.K = (int)K; p.P = P; p.kfac = kfac; p.B = B;
@@ -447,12 +516,21 @@ int launch_quant_token_tc(const void *x, int in_dtype, long M, long K, long ld, 
     p.Mtot = 128 * p.T;
     p.a_bytes = ((p.Kdim + 63) / 64) * p.Mtot * 128;
     const int budget = 227 * 1024 - 7168 - 1024 - p.a_bytes;     // aux (reductions, barriers, sign words) + alignment slack
-    // the widest MMA (N = 64 NB columns, NB rows or row pairs per instruction) that leaves room for two stages; small
-    // batches take narrower ones so that the rows spread over more SMs
+    // MMAs as wide as TMEM allows (N = 64 NB columns: NB rows, or row pairs, per instruction — an MMA costs about the same
+    // for any N); small batches take narrower ones so that the rows spread over more SMs.  A stage holds CK of the Kdim
+    // contraction rows of every row of the unit: the largest divisor of Kdim (in steps of 16) of which two stages fit
+    // beside A (large stages keep more bytes in flight per barrier round trip than many small ones).
     int NB = 4 / p.T;
-    while (NB > 1 && (2 * p.R * NB * boxP * 128 > budget || (M + (long)p.R * NB - 1) / ((long)p.R * NB) < kNumSMs)) NB >>= 1;
+    while (!gu && NB > 1 && (M + (long)p.R * NB - 1) / ((long)p.R * NB) < kNumSMs) NB >>= 1;     // (the fused form works as one team)
+    int CK = p.R == 2 ? 64 : 16;
+    if (p.R == 1) {
+        for (int c = p.Kdim; c >= 16; c -= 16)
+            if (p.Kdim % c == 0 && 2 * NB * c * 128 <= budget) { CK = c; break; }
+    }
     p.NB = NB;
-    p.stage_bytes = p.R * NB * boxP * 128;
+    p.CK = CK;
+    p.nchunks = p.R == 2 ? 1 : p.Kdim / CK;
+    p.stage_bytes = p.R * NB * CK * 128;
     int stages = budget / p.stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return -1000;
@@ -463,28 +541,46 @@ int launch_quant_token_tc(const void *x, int in_dtype, long M, long K, long ld, 
     p.q = q;
     p.scale = static_cast<__half *>(scale);
     p.zero = static_cast<__half *>(zero);
+    p.gu = static_cast<const uint8_t *>(gu);
+    p.gu_ld_bytes = ld * 2;
     CUtensorMap map;
-    MapKey key{x, M, ld, P, boxP, p.R * NB};
-    int rc = get_map(key, &map);
-    if (rc) return rc;
+    memset(&map, 0, sizeof(map));
+    if (!gu) {
+        MapKey key{x, M, ld, P, CK, p.R * NB};
+        const int rc = get_map(key, &map);
+        if (rc) return rc;
+    }
     const int smem = p.a_bytes + stages * p.stage_bytes + 7168 + 1024;
     // FLH_B200_TC_PROFILE=1 (read once): the variant that times its waits for flh_b200_quant_token_wait_profile
     static int profile = -1;
     if (profile < 0) { const char *e = getenv("FLH_B200_TC_PROFILE"); profile = (e && atoi(e) != 0) ? 1 : 0; }
     using Kern = void (*)(const CUtensorMap, const TcQuantParams);
-    const Kern kern = profile ? quant_token_tc_kernel<true> : quant_token_tc_kernel<false>;
-    static bool attr_done[64] = {};
+    const bool fuse = gu != nullptr;
+    const Kern kern = fuse ? (profile ? quant_token_tc_kernel<true, true> : quant_token_tc_kernel<false, true>)
+                           : (profile ? quant_token_tc_kernel<true, false> : quant_token_tc_kernel<false, false>);
+    static bool attr_done[2][64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
-    if (dev < 0 || !attr_done[dev]) {
+    if (dev < 0 || !attr_done[fuse][dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return cuda_status(e, "quant_token_tc smem attribute");
-        if (dev >= 0) attr_done[dev] = true;
+        if (dev >= 0) attr_done[fuse][dev] = true;
     }
     const long n_units = (M + (long)p.R * NB - 1) / ((long)p.R * NB);
     const long grid = n_units < kNumSMs ? n_units : kNumSMs;
     kern<<<(unsigned)grid, kThreadsTc, smem, stream>>>(map, p);
     return cuda_status(cudaGetLastError(), "quant_token_tc launch");
+}
+
+int launch_quant_token_tc(const void *x, int in_dtype, long M, long K, long ld, int kfac, const uint32_t *sign_bits,
+                          float clip, uint8_t *q, void *scale, void *zero, cudaStream_t stream) {
+    return launch_tc(x, nullptr, in_dtype, M, K, ld, kfac, sign_bits, clip, q, scale, zero, stream);
+}
+
+// SiLU(gate) * up of gu [M][2K] (row stride ld elements) -> full-width transform -> per-token asymmetric int4, one kernel.
+int launch_silu_mul_quant_token_tc(const void *gu, int in_dtype, long M, long K, long ld, int kfac, const uint32_t *sign_bits,
+                                   float clip, uint8_t *q, void *scale, void *zero, cudaStream_t stream) {
+    return launch_tc(nullptr, gu, in_dtype, M, K, ld, kfac, sign_bits, clip, q, scale, zero, stream);
 }
 
 int quant_token_tc_wait_profile(unsigned long long *out8) {

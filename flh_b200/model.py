@@ -41,6 +41,8 @@ class DecoderConfig:
     act_mode: str = "group_sym"          # or "token_asym"
     tp: int = 1
     fuse_norm: bool = True               # RMS-norm fused into the per-token quantiser where the kernel exists
+    fuse_glue: bool = True               # rotary embedding + KV-cache write, and SiLU(gate) * up (+ transform + quantiser), as
+                                         # kernels of this library instead of PyTorch tensor operations
 
     @property
     def head_dim(self):
@@ -71,6 +73,13 @@ class RMSNorm(torch.nn.Module):
     def forward(self, x):
         v = x.float()
         return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype) * self.weight
+
+
+def rope_tables(pos, d, theta):
+    """cos, sin [S, d / 2] binary32 of the rotary angles pos * theta^(-2i/d) — the values rope() multiplies with."""
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=pos.device, dtype=torch.float32) / d))
+    ang = pos.float()[:, None] * inv[None, :]
+    return ang.cos().contiguous(), ang.sin().contiguous()
 
 
 def rope(x, pos, theta):
@@ -117,9 +126,9 @@ class DecoderLayer(torch.nn.Module):
             return s.view(lead + (cfg.hidden // 128,)), None, q.view(lead + (cfg.hidden // 2,))
         return quant(norm(x))
 
-    def forward(self, x, pos, cache=None):
+    def forward(self, x, pos, cache=None, tables=None):
         """x [B, S, hidden] f16; pos [S] absolute positions; cache = (k, v) [B, nkv, T, D] with a write
-        cursor `cache[2]`, or None for a cache-less prefill."""
+        cursor `cache[2]`, or None for a cache-less prefill; tables = rope_tables(pos, ...) shared by the layers."""
         cfg = self.cfg
         B, S, _ = x.shape
         hd = cfg.head_dim
@@ -127,20 +136,34 @@ class DecoderLayer(torch.nn.Module):
             s, z, q = self._norm_quant(self.norm1, self.q_in, x)
         qkv = self.qkv(q, s, z)
         with timing.region("glue"):
-            qh, kh, vh = qkv.split((self.nh * hd, self.nkv * hd, self.nkv * hd), dim=-1)
-            qh = rope(qh.view(B, S, self.nh, hd), pos, cfg.rope_theta).transpose(1, 2)
-            kh = rope(kh.view(B, S, self.nkv, hd), pos, cfg.rope_theta).transpose(1, 2)
-            vh = vh.view(B, S, self.nkv, hd).transpose(1, 2)
             mask, causal = None, S > 1
-            if cache is not None:
-                kc, vc, cur = cache
-                kc[:, :, cur:cur + S] = kh
-                vc[:, :, cur:cur + S] = vh
+            cur = 0 if cache is None else cache[2]
+            if cfg.fuse_glue and qkv.dtype == torch.float16:
+                # one kernel: rotary embedding of q and k, q laid out for the attention call, k and v written at their cache positions
+                if tables is None:
+                    tables = rope_tables(pos, hd, cfg.rope_theta)
+                if cache is not None:
+                    kc, vc = cache[0], cache[1]
+                else:
+                    kc = torch.empty((B, self.nkv, S, hd), dtype=qkv.dtype, device=qkv.device)
+                    vc = torch.empty_like(kc)
+                qh = torch.empty((B, self.nh, S, hd), dtype=qkv.dtype, device=qkv.device)
+                _CUDA.rope_kv(qkv.view(B * S, -1), tables[0], tables[1], qh, kc, vc, B, S, self.nh, self.nkv, cur)
                 kh, vh = kc[:, :, :cur + S], vc[:, :, :cur + S]
-                if cur > 0 and S > 1:
-                    # a chunk appended to a filled cache: query i sees keys 0 .. cur + i (torch's is_causal aligns the
-                    # triangle with the top-left corner, which is only right for cur = 0)
-                    mask, causal = torch.ones(S, cur + S, dtype=torch.bool, device=x.device).tril(diagonal=cur), False
+            else:
+                qh, kh, vh = qkv.split((self.nh * hd, self.nkv * hd, self.nkv * hd), dim=-1)
+                qh = rope(qh.view(B, S, self.nh, hd), pos, cfg.rope_theta).transpose(1, 2)
+                kh = rope(kh.view(B, S, self.nkv, hd), pos, cfg.rope_theta).transpose(1, 2)
+                vh = vh.view(B, S, self.nkv, hd).transpose(1, 2)
+                if cache is not None:
+                    kc, vc = cache[0], cache[1]
+                    kc[:, :, cur:cur + S] = kh
+                    vc[:, :, cur:cur + S] = vh
+                    kh, vh = kc[:, :, :cur + S], vc[:, :, :cur + S]
+            if cur > 0 and S > 1:
+                # a chunk appended to a filled cache: query i sees keys 0 .. cur + i (torch's is_causal aligns the
+                # triangle with the top-left corner, which is only right for cur = 0)
+                mask, causal = torch.ones(S, cur + S, dtype=torch.bool, device=x.device).tril(diagonal=cur), False
         with timing.region("attention"):
             att = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, is_causal=causal, enable_gqa=self.nh != self.nkv)
             att = att.transpose(1, 2).reshape(B, S, self.nh * hd)
@@ -152,11 +175,22 @@ class DecoderLayer(torch.nn.Module):
         with timing.region("quant"):
             s, z, q = self._norm_quant(self.norm2, self.q_mlp, x)
         gu = self.gate_up(q, s, z)
-        with timing.region("glue"):
-            g, u = gu.chunk(2, dim=-1)
-            a = F.silu(g) * u
-        with timing.region("quant"):
-            s, z, q = self.q_down(a)
+        if cfg.fuse_glue and cfg.act_mode == "token_asym":
+            # SiLU(gate) * up, the online transform and the quantiser in one kernel (two for widths it does not take)
+            with timing.region("quant"):
+                lead = gu.shape[:-1]
+                q, s, z = _CUDA.silu_mul_quant_token_asym_i4(gu.view(-1, gu.shape[-1]), hadamard=self.q_down.use_hadamard,
+                                                             clip=self.q_down.input_clip_ratio)
+                s, z, q = s.view(lead + (1,)), z.view(lead + (1,)), q.view(lead + (q.shape[-1],))
+        else:
+            with timing.region("glue"):
+                if cfg.fuse_glue:
+                    a = _CUDA.silu_mul(gu.view(-1, gu.shape[-1])).view(gu.shape[:-1] + (gu.shape[-1] // 2,))
+                else:
+                    g, u = gu.chunk(2, dim=-1)
+                    a = F.silu(g) * u
+            with timing.region("quant"):
+                s, z, q = self.q_down(a)
         y = self.down(q, s, z)
         with timing.region("glue"):
             return x + y
@@ -193,9 +227,10 @@ class Decoder(torch.nn.Module):
         B, S = ids.shape
         x = self.embed(ids)
         pos = torch.arange(start, start + S, device=ids.device)
+        tables = rope_tables(pos, self.cfg.head_dim, self.cfg.rope_theta) if self.cfg.fuse_glue else None
         for i, layer in enumerate(self.layers):
             if cache is not None:
                 cache[i][2] = start
-            x = layer(x, pos, None if cache is None else cache[i])
+            x = layer(x, pos, None if cache is None else cache[i], tables)
         x = self.norm(x)
         return x if self.head is None else self.head(x[:, -1:])

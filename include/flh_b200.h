@@ -123,6 +123,36 @@ int flh_b200_rmsnorm_quant_token_asym_i4(const void *x, int in_dtype, long M, lo
 int flh_b200_rmsnorm_quant_group_sym_i4(const void *x, long M, long K, float eps, int hadamard, uint8_t *q,
                                         void *scales, void *stream);
 
+/* ---- the decoder wiring either side of the quantised linears (flh/quantized_model/modeling_llama.py:389-470, 522-526) ---- */
+
+/* SiLU(gate) * up of the MLP.  gu [M, 2F] f16 or bf16 with row stride ld (elements): gate = columns [0, F), up = columns
+ * [F, 2F) — the output of the merged gate/up GEMM; out [M, F] contiguous, same type.  F % 8 == 0, 16-byte aligned pointers.
+ * Defined bit for bit (so that the CPU restatement agrees): e = exp32(-g), s = round16(g / (1 + e)), out = round16(s * u),
+ * every step one IEEE binary32 operation; exp32 is a fixed range reduction + degree-5 polynomial (csrc/act_common.cuh),
+ * within 1 ulp of expf, so the result equals torch's silu(gate) * up except where torch's own expf differs in the last bit.
+ * The reference runs act_fn and the product as separate PyTorch kernels (modeling_llama.py:524). */
+int flh_b200_silu_mul(const void *gu, int in_dtype, long M, long F, long ld, void *out, void *stream);
+
+/* The same followed by the full-width transform and the per-token asymmetric quantiser of flh_b200_quant_token_asym_i4
+ * (hadamard = 1), as ONE kernel: the MLP's "act_fn(gate) * up -> quantizer2" (modeling_llama.py:524-525) with the online
+ * transform of the per-token mode.  The product never reaches global memory: the epilogue warps of the tensor-core
+ * quantiser make the rows in shared memory in place of its TMA loads.  Result: equal to flh_b200_silu_mul followed by
+ * flh_b200_quant_token_asym_i4(hadamard = 1) on its output.  FLH_B200_EUNSUPPORTED when the width is not one the
+ * tensor-core kernel takes (F = P * 64, P <= 256) or hadamard != 1: run the two steps separately then. */
+int flh_b200_silu_mul_quant_token_asym_i4(const void *gu, int in_dtype, long M, long F, long ld, int hadamard, int kfac,
+                                          const uint32_t *sign_bits, float clip, uint8_t *q, void *scale, void *zero,
+                                          void *stream);
+
+/* Rotary embedding + KV-cache write in one pass over the merged QKV GEMM output (f16).
+ * qkv [B * S, (nh + 2 nkv) * D]: per token nh query heads, nkv key heads, nkv value heads of D values; cos, sin [S, D / 2]
+ * binary32 for the S positions of this step; half-split convention (element i pairs with i + D / 2):
+ *   out[i] = x[i] cos[i] - x[i + D/2] sin[i],  out[i + D/2] = x[i + D/2] cos[i] + x[i] sin[i]   (each product and sum rounded
+ *   to binary32 on its own, the result to f16 — the bits separate tensor operations give).
+ * q goes to q_out [B, nh, S, D]; rotated k and plain v go into k_cache / v_cache [B, nkv, T, D] at positions cur .. cur + S - 1.
+ * D % 8 == 0, cur + S <= T.  The reference does this as split, rotary, transpose and cache update (modeling_llama.py:396-440). */
+int flh_b200_rope_kv_f16(const void *qkv, const float *cos, const float *sin, void *q_out, void *k_cache, void *v_cache,
+                         int B, int S, int nh, int nkv, int D, int T, int cur, void *stream);
+
 /* HOST helpers: build the factor table of a kfac x kfac matrix of +1/-1 (int8, row-major, host
  * memory).  Layout: bit rows out[k * words + w], bit b = 1 when signs[k][32 w + b] < 0,
  * words = (kfac + 31) / 32; then, at the next 16-byte boundary, the same matrix as bfloat16 +-1.0

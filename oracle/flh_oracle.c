@@ -389,3 +389,38 @@ void flh_oracle_rmsnorm16(const uint16_t *x, int bf16, long M, long K, long ld, 
 
 void flh_oracle_f32_to_f16(const float *in, uint16_t *out, long n) { for (long i = 0; i < n; ++i) out[i] = f2h(in[i]); }
 void flh_oracle_f16_to_f32(const uint16_t *in, float *out, long n) { for (long i = 0; i < n; ++i) out[i] = h2f(in[i]); }
+
+/* ---- SiLU(gate) * up of the MLP (flh/quantized_model/modeling_llama.py:522-526), as the fused kernels define it:
+ *   e = exp32(-g);  s = round16(g / (1 + e));  out = round16(s * u), every step one IEEE binary32 operation.
+ *   exp32(t), t clamped to [-87, 88]: n = rint(t log2 e); r = t - n ln2 in two fma; y = 1 + r + r^2 P(r) (Cephes expf's
+ *   degree-5 polynomial, Horner with fma); result = y * 2^n.                                                            */
+static inline float exp32(float t) {
+    t = fminf(fmaxf(t, -87.0f), 88.0f);
+    const float n = nearbyintf(t * 1.44269504088896341f);
+    float r = fmaf(n, -0.693359375f, t);
+    r = fmaf(n, 2.12194440e-4f, r);
+    const float z = r * r;
+    float y = 1.9875691500e-4f;
+    y = fmaf(y, r, 1.3981999507e-3f);
+    y = fmaf(y, r, 8.3334519073e-3f);
+    y = fmaf(y, r, 4.1665795894e-2f);
+    y = fmaf(y, r, 1.6666665459e-1f);
+    y = fmaf(y, r, 5.0000001201e-1f);
+    y = fmaf(y, z, r);
+    y = y + 1.0f;
+    uint32_t sb = (uint32_t)((int)n + 127) << 23;
+    float sc; memcpy(&sc, &sb, 4);
+    return y * sc;
+}
+
+/* gu [M][ld] 16-bit values: gate = columns [0, F), up = columns [F, 2F); out [M][F] */
+void flh_oracle_silu_mul16(const uint16_t *gu, int bf16, long M, long F, long ld, uint16_t *out) {
+    for (long m = 0; m < M; ++m)
+        for (long f = 0; f < F; ++f) {
+            const uint16_t gb = gu[m * ld + f], ub = gu[m * ld + F + f];
+            const float g = bf16 ? bf2f(gb) : h2f(gb), u = bf16 ? bf2f(ub) : h2f(ub);
+            const float s = g / (1.0f + exp32(-g));
+            if (bf16) out[m * F + f] = f2bf(bf2f(f2bf(s)) * u);
+            else out[m * F + f] = f2h(h2f(f2h(s)) * u);
+        }
+}

@@ -162,6 +162,17 @@ def rmsnorm16(x: np.ndarray, eps: float, bf16: bool = False) -> np.ndarray:
 
 
 # ----------------------------------------------------------------------------- weights (offline side)
+def silu_mul16(gu: np.ndarray, bf16: bool = False) -> np.ndarray:
+    """SiLU(gate) * up of a merged [M, 2F] gate/up matrix (float16, or uint16 bfloat16 bits) -> [M, F], with the
+    arithmetic the fused kernels define (flh_oracle.c: flh_oracle_silu_mul16)."""
+    xx = np.ascontiguousarray(gu)
+    m, f2 = xx.shape
+    out = np.empty((m, f2 // 2), dtype=np.uint16)
+    lib().flh_oracle_silu_mul16(_p(xx.view(np.uint16), _u16p), ctypes.c_int(int(bf16)), ctypes.c_long(m), ctypes.c_long(f2 // 2),
+                                ctypes.c_long(f2), _p(out, _u16p))
+    return out if bf16 else out.view(np.float16)
+
+
 def rtn_group_sym(w: np.ndarray, group: int = 128):
     """Symmetric RTN int4 with one scale per (row, group).
     Restates WeightQuantizer._calibrate_group_wise / _quantize_group_wise,
