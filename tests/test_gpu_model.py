@@ -51,16 +51,13 @@ def test_llama7b_shaped_layer_matches_pytorch_twin(cuda, monkeypatch, mode):
     tensor-core transform in front of down_proj, 256 tokens) against its PyTorch twin (forward_origin / forward_torch and
     tensor operations for rope, SiLU * up) on the same packed weights.
     Tolerance.  The twins are not bit-level models of the kernels: forward_origin transforms in float64 and quantises
-    against an un-rounded binary32 scale, the kernels against the f16 scale they store, so by construction 2-5e-4 of the
+    against an un-rounded binary32 scale, the kernels against the f16 scale they store, so by construction about 5e-4 of the
     activation codes differ by one step (tests/test_oracle_golden.py measures that rate against the reference's own
-    functions).  One such flip moves one of the K terms of a dot product by one quantisation step, about
-    0.5 sigma_x * |w|; against an output of standard deviation sqrt(K) sigma_x sigma_w with |w| / sigma_w <= 1.7 for
-    uniform int4 codes that is 0.5 * 1.7 / sqrt(4096) = 1.3 % of the output's standard deviation, i.e. about 0.3 % of
-    max |y| per flip per output; a row of 4096 ... 11008 activations carries 2 to 5 flips per linear, the layer chains three
-    quantised linears and an attention, and the maximum is taken over a million outputs: a few percent of max |y| at
-    the worst output, while the error over all outputs (relative Frobenius norm) stays near 1e-3.  Measured on B200:
-    max-norm 1.0e-2 (group_sym) and 2.6e-2 (token_asym).  Bounds used: 5 % of max |y| at the worst output, 1 % in
-    Frobenius norm."""
+    functions).  A flipped code moves its activation by one quantisation step, about 0.5 sigma_x in the per-token mode, so
+    the activation vector — and with it the output of the linear — moves by sqrt(5e-4) * 0.5 = 1.1 % in relative
+    Frobenius norm; three quantised linears in sequence and the attention add up to 1-2 %.  The worst single output (of a
+    million) lies a few times higher relative to max |y|.  Measured on B200: Frobenius 0.6 % (group_sym) and 1.1 %
+    (token_asym), worst output 0.8-1.0 % and 2.6-3.6 % of max |y|.  Bounds used: 3 % in Frobenius norm, 8 % of max |y|."""
     from flh_b200.model import Decoder, DecoderConfig
     cfg = DecoderConfig(hidden=4096, n_heads=32, n_kv_heads=32, ffn=11008, n_layers=1, vocab=512, act_mode=mode)
     m = Decoder(cfg, torch.device("cuda"), seed=11, with_head=False)
@@ -74,4 +71,4 @@ def test_llama7b_shaped_layer_matches_pytorch_twin(cuda, monkeypatch, mode):
     err = ((y - y_ref).abs().max() / y_ref.abs().max()).item()
     fro = ((y - y_ref).norm() / y_ref.norm()).item()
     print(f"{mode}: max |y - y_twin| / max |y_twin| = {err:.2e}, Frobenius {fro:.2e}")
-    assert err < 5e-2 and fro < 1e-2, (err, fro)
+    assert err < 8e-2 and fro < 3e-2, (err, fro)
