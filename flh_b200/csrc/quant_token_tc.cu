@@ -168,16 +168,35 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
             if (pr < p.P && blk_k == blk_m && pc0 < p.P && k0 < p.Kdim) {
                 const int ar = pr >> logB, br = pr & (p.B - 1);
                 const uint32_t *row = sgn + ar * p.words;
+                uint32_t neg8;                                              // bit e: the sign of element pc0 + e
+                if (p.B >= 8) {
+                    // the eight columns share one column of the factor; their Sylvester bits are b0 .. b0 + 7 with b0 a multiple
+                    // of 8, so the parity splits into a common part and the 8-point Walsh row of br & 7
+                    const int ac = pc0 >> logB, bc0 = pc0 & (p.B - 1);
+                    uint32_t common = __popc((uint32_t)(br & bc0)) & 1u;
+                    if (p.sign_bits) common ^= (row[ac >> 5] >> (ac & 31)) & 1u;
+                    // Walsh rows of order 8 as bit masks: bit e of row r = parity(r & e)
+                    const uint32_t walsh8 = (0x00u) | (0xAAu << 8) | (0xCCu << 16) | (0x66u << 24);
+                    const uint32_t walsh8b = (0xF0u) | (0x5Au << 8) | (0x3Cu << 16) | (0x96u << 24);
+                    const int r7 = br & 7;
+                    const uint32_t wr = ((r7 < 4 ? walsh8 : walsh8b) >> (8 * (r7 & 3))) & 0xFFu;
+                    neg8 = wr ^ (common ? 0xFFu : 0u);
+                } else if (p.B == 1) {
+                    neg8 = p.sign_bits ? (row[pc0 >> 5] >> (pc0 & 31)) & 0xFFu : 0u;   // eight neighbouring bits of the factor's row
+                } else {
+                    neg8 = 0;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const int pc = pc0 + e;
-                    if (pc < p.P) {
-                        const int ac = pc >> logB, bc = pc & (p.B - 1);
+                    for (int e = 0; e < 8; ++e) {
+                        const int pc = pc0 + e, ac = pc >> logB, bc = pc & (p.B - 1);
                         uint32_t neg = __popc((uint32_t)(br & bc)) & 1u;
-                        if (p.sign_bits) neg ^= (row[ac >> 5] >> (ac & 31)) & 1u;
-                        w[e >> 1] |= (one | (neg << 15)) << (16 * (e & 1));
+                        if (p.sign_bits && ac < p.kfac) neg ^= (row[ac >> 5] >> (ac & 31)) & 1u;
+                        neg8 |= neg << e;
                     }
                 }
+                const int nvalid = p.P - pc0 < 8 ? p.P - pc0 : 8;
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    if (e < nvalid) w[e >> 1] |= (one | (((neg8 >> e) & 1u) << 15)) << (16 * (e & 1));
             }
             const int kb = kc >> 3, cc = kc & 7;
             *reinterpret_cast<uint4 *>(sm + (kb * (p.Mtot >> 3) + (m >> 3)) * 1024 + (m & 7) * 128 + ((cc ^ (m & 7)) << 4)) =
@@ -330,12 +349,14 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
             }
         };
         if (FUSE && (long)blockIdx.x < n_units) produce(0);
-        for (long it = team;; it += NT, ++n) {
-            const long unit = blockIdx.x + it * gridDim.x;
-            if (unit >= n_units) break;
-            if (FUSE && unit + gridDim.x < n_units) produce(it + 1);
-            const int u = (int)(it % NU);
-            ok = __all_sync(0xffffffffu, ok && wait(slot_full(u), (uint32_t)((it / NU) & 1), 34, w4));
+        const int nu_mask = NU - 1, nu_log = 31 - __clz(NU);          // NU is 8, 4 or 2
+        const int units_i = (int)n_units, stride = (int)gridDim.x, rows_pu = R * NB;
+        for (int it = team;; it += NT, ++n) {
+            const int unit = (int)blockIdx.x + it * stride;
+            if (unit >= units_i) break;
+            if (FUSE && unit + stride < units_i) produce(it + 1);
+            const int u = it & nu_mask;
+            ok = __all_sync(0xffffffffu, ok && wait(slot_full(u), (uint32_t)((it >> nu_log) & 1), 34, w4));
             uint64_t v[32];
             if (ok) {
                 tc_fence_after();
@@ -382,7 +403,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
                 }
             }
             const TokenRowParams rp = token_row_params(__uint_as_float(umin | 0x80000000u), __uint_as_float(umax), p.clip, p.c);
-            const long row = unit * (R * NB) + riu;
+            const long row = (long)unit * rows_pu + riu;
             if (ok && row < p.M) {
                 if (pp == 0) { p.scale[row] = rp.scale; p.zero[row] = __float2half_rn(rp.zero); }
                 if (live) {

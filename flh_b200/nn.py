@@ -262,9 +262,10 @@ class LinearFLH(torch.nn.Module):
             self._w_i8 = _CUDA.expand_i4(self.w_packed.view(self.out_features, self.in_features // 2))
         return self
 
-    def forward(self, x, a_scale=None, a_zero=None, x_is_packed=True, is_symmetric=None, out_dtype=None):
+    def forward(self, x, a_scale=None, a_zero=None, x_is_packed=True, is_symmetric=None, out_dtype=None, out=None):
         """x: packed activations [.., K/2]; a_scale [.., K/gs] (group mode) or [.., 1] (per token);
-        a_zero None or like a_scale.  Returns [.., N] in the dtype of w_scale (flh/nn/linear.py:125-133)."""
+        a_zero None or like a_scale.  Returns [.., N] in the dtype of w_scale (flh/nn/linear.py:125-133); out = a
+        contiguous [M, N] tensor to write into instead of allocating."""
         lead = x.shape[:-1]
         M = x.numel() // x.shape[-1]
         a_scale = a_scale.reshape(M, -1)
@@ -275,11 +276,11 @@ class LinearFLH(torch.nn.Module):
             rs = self.w_rowsum(min(ga, gb))
         if self._w_i8 is not None and a_scale.shape[1] == 1 and M >= self.PREPACK_MIN_ROWS:
             y = _CUDA.gemm_i8w_dequant(x.reshape(M, -1), self._w_i8, a_scale, self.w_scale, A_zero=a_zero, B_rowsum=rs,
-                                       bias=self.bias, out_dtype=out_dtype or self.w_scale.dtype)
+                                       bias=self.bias, out_dtype=out_dtype or self.w_scale.dtype, out=out)
         else:
             y = _CUDA.gemm_i4_dequant(x.reshape(M, -1), self.w_packed.view(self.out_features, self.in_features // 2),
                                       a_scale, self.w_scale, A_zero=a_zero, B_rowsum=rs, bias=self.bias,
-                                      out_dtype=out_dtype or self.w_scale.dtype)
+                                      out_dtype=out_dtype or self.w_scale.dtype, out=out)
         return y.view(lead + (self.out_features,))
 
     def forward_torch(self, x, a_scale=None, a_zero=None, x_is_packed=True, is_symmetric=None):
