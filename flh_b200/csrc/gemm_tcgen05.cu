@@ -406,12 +406,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tc_fence_after();
                     const float *sb = sbuf + slot * BN + cbase;
                     const int *rs = rbuf + slot * BN + cbase;
+                    // the next 32-column chunk is in flight from TMEM while this one is folded into the accumulators
+                    uint32_t vv[2][32];
+                    if (ok) tc_ld32(tlane + buf * BN, vv[0]);
 #pragma unroll
                     for (int cc = 0; cc < 4; ++cc) {
                         if (!ok) break;
-                        uint32_t v[32];
-                        tc_ld32(tlane + buf * BN + cc * 32, v);
                         tc_wait_ld();
+                        if (cc + 1 < 4) tc_ld32(tlane + buf * BN + (cc + 1) * 32, vv[(cc + 1) & 1]);
+                        const uint32_t (&v)[32] = vv[cc & 1];
 #pragma unroll
                         for (int j = 0; j < 32; j += 2) {
                             const int col = cc * 32 + j;
@@ -419,11 +422,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             int i0 = (int)v[j], i1 = (int)v[j + 1];
                             if (A_UNSIGNED) { i0 = (i0 >> 8) - za * rs[col]; i1 = (i1 >> 8) - za * rs[col + 1]; }
                             const uint64_t p2 = mul2(sa2, pack2(sbp.x, sbp.y));
-                            // int -> float without the conversion unit: for |i| < 2^22 the pattern 0x4B400000 + i is the float
-                            // 1.5 * 2^23 + i, and subtracting 1.5 * 2^23 is exact (|256 * group sum| <= 2^21)
-                            const uint64_t f2 = add2(pack2(__uint_as_float(0x4B400000u + (uint32_t)i0), __uint_as_float(0x4B400000u + (uint32_t)i1)),
-                                                     pack2(-12582912.0f, -12582912.0f));
-                            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[col >> 1]) : "l"(f2), "l"(p2));
+                            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[col >> 1]) : "l"(pack2((float)i0, (float)i1)), "l"(p2));
                         }
                     }
                     tc_fence_before();
