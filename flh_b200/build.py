@@ -31,7 +31,7 @@ def _stale(target: str, deps) -> bool:
 
 def build(verbose: bool = False, force: bool = False) -> str:
     nvcc = os.environ.get("NVCC", "nvcc")
-    headers = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "token_common.cuh"), os.path.join(CSRC, "tc_common.cuh"), os.path.join(CSRC, "act_common.cuh"), os.path.join(HERE, "..", "include", "flh_b200.h")]
+    headers = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "token_common.cuh"), os.path.join(CSRC, "tc_common.cuh"), os.path.join(CSRC, "act_common.cuh"), os.path.join(CSRC, "tc_quant_common.cuh"), os.path.join(HERE, "..", "include", "flh_b200.h")]
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
     jobs = []

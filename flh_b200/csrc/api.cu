@@ -63,6 +63,7 @@ int launch_silu_mul(const void *, int, long, long, long, void *, cudaStream_t);
 int launch_silu_mul_quant_token_tc(const void *, int, long, long, long, int, const uint32_t *, float, uint8_t *, void *, void *, cudaStream_t);
 int launch_rope_kv(const void *, const float *, const float *, void *, void *, void *, int, int, int, int, int, int, int, cudaStream_t);
 int quant_token_tc_status(int *);
+
 int quant_token_tc_wait_profile(unsigned long long *);
 int quant_token_tc_status_clear();
 int gemm_i8_wait_profile(unsigned long long *);

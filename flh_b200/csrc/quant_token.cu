@@ -505,7 +505,8 @@ int launch_quant_token_asym(const void *x, int in_dtype, long M, long K, long ld
                             void *scale, void *zero, cudaStream_t stream) {
     if (hadamard == 1) {
         // default transform: the high part on the tensor cores, for every batch size (K = P * 64, P <= 256)
-        const int rc = launch_quant_token_tc(x, in_dtype, M, K, ld, kfac, sign_bits, clip, q, scale, zero, stream);
+        int rc;
+        rc = launch_quant_token_tc(x, in_dtype, M, K, ld, kfac, sign_bits, clip, q, scale, zero, stream);
         if (rc != -1000) return rc;
     }
     if ((!hadamard || kfac == 1) && (K == 4096 || K == 8192) && M >= token_warp_min_rows() &&

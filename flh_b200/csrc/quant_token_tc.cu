@@ -25,6 +25,7 @@
 #include "tc_common.cuh"
 #include "token_common.cuh"
 #include "act_common.cuh"
+#include "tc_quant_common.cuh"
 
 namespace flh {
 namespace {
@@ -52,22 +53,13 @@ struct TcQuantParams {
     int Kdim, Mtot;            // contraction length of the MMAs (multiple of 16), rows of A (128 or 256)
     int a_bytes, stage_bytes, stages;
     int bf16;
+    int dbg;                   // PROFILE only: bit 0 = the epilogue only loads and releases its accumulators (how fast TMA + MMA run alone)
     const uint8_t *gu;         // FUSE: merged gate/up matrix [M][2K] (gate = the first K columns), row stride gu_ld_bytes
     long gu_ld_bytes;
     float clip, c;
     uint8_t *q;
     __half *scale, *zero;
 };
-
-__device__ __forceinline__ uint64_t umma_desc_tc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
-}
 
 __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&v)[64]) {
     asm volatile(
@@ -106,17 +98,6 @@ __device__ __forceinline__ void bfly6_pairs(uint64_t (&p)[32]) {
     }
 }
 
-__device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
-    uint32_t r;
-    asm volatile("redux.sync.max.u32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(v));
-    return r;
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-
 // PROFILE: time every wait with %globaltimer and add the sums to g_wait_tc (flh_b200_quant_token_wait_profile).
 // FUSE: the rows are not read by TMA but MADE by the epilogue warps — SiLU(gate) * up of the merged gate/up GEMM output
 // (act_common.cuh), written into the stages in the layout TMA would have produced; the unit after the one whose
@@ -146,63 +127,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
     const uint64_t t_start = PROFILE ? gtimer() : 0;
 
     // ---- one-time set-up: A = G (or diag(G, G)) as a K-major operand with the 128-byte swizzle ----
-    // element (m, k): K atom kb = k / 64 at (kb * Mtot / 8 + m / 8) * 1024, row m % 8 of 128 bytes, 16-byte chunk ((k % 64) / 8) ^ (m % 8).
-    // G[p'][p] = S[a'][a] * (-1)^popc(b' & b) with p = a * B + b (B a power of two): per row the signs of the factor come as
-    // one bit row of the table (staged in shared memory first), the Sylvester part is a parity.
-    {
-        uint32_t *sgn = reinterpret_cast<uint32_t *>(sm + aux + 2048);      // kfac * words words (<= 172 * 6 * 4 bytes)
-        if (p.sign_bits)
-            for (int i = tid; i < p.kfac * p.words; i += kThreadsTc) sgn[i] = p.sign_bits[i];
-        __syncthreads();
-        const int katoms = (p.Kdim + 63) >> 6;
-        const int cpr = katoms * 8;                                         // 16-byte chunks per row of A
-        const int chunks = p.Mtot * cpr;
-        const int logB = 31 - __clz(p.B);
-        const uint32_t one = p.bf16 ? 0x3F80u : 0x3C00u;
-        for (int i = tid; i < chunks; i += kThreadsTc) {
-            const int m = i / cpr, kc = i - m * cpr;                        // row of A, 16-byte chunk along K
-            const int pr = R == 2 ? (m & 63) : m, blk_m = R == 2 ? (m >> 6) : 0;
-            uint32_t w[4] = {0u, 0u, 0u, 0u};
-            const int k0 = kc * 8;
-            const int pc0 = R == 2 ? (k0 & 63) : k0, blk_k = R == 2 ? (k0 >> 6) : 0;
-            if (pr < p.P && blk_k == blk_m && pc0 < p.P && k0 < p.Kdim) {
-                const int ar = pr >> logB, br = pr & (p.B - 1);
-                const uint32_t *row = sgn + ar * p.words;
-                uint32_t neg8;                                              // bit e: the sign of element pc0 + e
-                if (p.B >= 8) {
-                    // the eight columns share one column of the factor; their Sylvester bits are b0 .. b0 + 7 with b0 a multiple
-                    // of 8, so the parity splits into a common part and the 8-point Walsh row of br & 7
-                    const int ac = pc0 >> logB, bc0 = pc0 & (p.B - 1);
-                    uint32_t common = __popc((uint32_t)(br & bc0)) & 1u;
-                    if (p.sign_bits) common ^= (row[ac >> 5] >> (ac & 31)) & 1u;
-                    // Walsh rows of order 8 as bit masks: bit e of row r = parity(r & e)
-                    const uint32_t walsh8 = (0x00u) | (0xAAu << 8) | (0xCCu << 16) | (0x66u << 24);
-                    const uint32_t walsh8b = (0xF0u) | (0x5Au << 8) | (0x3Cu << 16) | (0x96u << 24);
-                    const int r7 = br & 7;
-                    const uint32_t wr = ((r7 < 4 ? walsh8 : walsh8b) >> (8 * (r7 & 3))) & 0xFFu;
-                    neg8 = wr ^ (common ? 0xFFu : 0u);
-                } else if (p.B == 1) {
-                    neg8 = p.sign_bits ? (row[pc0 >> 5] >> (pc0 & 31)) & 0xFFu : 0u;   // eight neighbouring bits of the factor's row
-                } else {
-                    neg8 = 0;
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const int pc = pc0 + e, ac = pc >> logB, bc = pc & (p.B - 1);
-                        uint32_t neg = __popc((uint32_t)(br & bc)) & 1u;
-                        if (p.sign_bits && ac < p.kfac) neg ^= (row[ac >> 5] >> (ac & 31)) & 1u;
-                        neg8 |= neg << e;
-                    }
-                }
-                const int nvalid = p.P - pc0 < 8 ? p.P - pc0 : 8;
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                    if (e < nvalid) w[e >> 1] |= (one | (((neg8 >> e) & 1u) << 15)) << (16 * (e & 1));
-            }
-            const int kb = kc >> 3, cc = kc & 7;
-            *reinterpret_cast<uint4 *>(sm + (kb * (p.Mtot >> 3) + (m >> 3)) * 1024 + (m & 7) * 128 + ((cc ^ (m & 7)) << 4)) =
-                make_uint4(w[0], w[1], w[2], w[3]);
-        }
-    }
+    build_sign_operand(sm, reinterpret_cast<uint32_t *>(sm + aux + 2048), p.sign_bits, p.kfac, p.words, p.P, p.B, R, p.Kdim, p.Mtot,
+                       p.bf16 != 0, tid, kThreadsTc);
     if (tid == 0) {
         for (int s = 0; s < kMaxStages; ++s) { mbar_init(stage_full(s), FUSE ? kEpiWarpsTc : 1); mbar_init(stage_empty(s), 1); }
         for (int u = 0; u < kSlots; ++u) { mbar_init(slot_full(u), 1); mbar_init(slot_empty(u), 4 * BPU); }
@@ -358,6 +284,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
             const int u = it & nu_mask;
             ok = __all_sync(0xffffffffu, ok && wait(slot_full(u), (uint32_t)((it >> nu_log) & 1), 34, w4));
             uint64_t v[32];
+            if (PROFILE && (p.dbg & 2)) {                            // experiment: no TMEM load either
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(slot_empty(u));
+                continue;
+            }
             if (ok) {
                 tc_fence_after();
                 uint32_t rawv[64];
@@ -372,6 +304,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(slot_empty(u));               // the accumulator is in registers: the slot is free
+            if (PROFILE && (p.dbg & 1)) {
+                if (v[0] == 0x123456789abcdefull) p.q[0] = 1;         // keep the load alive
+                continue;
+            }
             bfly6_pairs(v);
             // ---- row minimum (<= 0) and maximum (>= 0): the bit pattern of a non-negative binary32 orders like an
             //      unsigned integer, so |min| and max go through one redux.sync each ----
@@ -543,6 +479,7 @@ static int launch_tc(const void *x, const void *gu, int in_dtype, long M, long K
     // beside A (large stages keep more bytes in flight per barrier round trip than many small ones).
     int NB = 4 / p.T;
     while (!gu && NB > 1 && (M + (long)p.R * NB - 1) / ((long)p.R * NB) < kNumSMs) NB >>= 1;     // (the fused form works as one team)
+    { const char *e = getenv("FLH_B200_TC_NB"); if (e && !gu) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4) NB = v <= 4 / p.T ? v : NB; } }   // tuning aid
     int CK = p.R == 2 ? 64 : 16;
     if (p.R == 1) {
         for (int c = p.Kdim; c >= 16; c -= 16)
@@ -574,7 +511,8 @@ static int launch_tc(const void *x, const void *gu, int in_dtype, long M, long K
     const int smem = p.a_bytes + stages * p.stage_bytes + 7168 + 1024;
     // FLH_B200_TC_PROFILE=1 (read once): the variant that times its waits for flh_b200_quant_token_wait_profile
     static int profile = -1;
-    if (profile < 0) { const char *e = getenv("FLH_B200_TC_PROFILE"); profile = (e && atoi(e) != 0) ? 1 : 0; }
+    if (profile < 0) { const char *e = getenv("FLH_B200_TC_PROFILE"); profile = e ? atoi(e) : 0; }
+    p.dbg = profile > 1 ? profile >> 1 : 0;                      // FLH_B200_TC_PROFILE=3: profile + accumulators loaded and dropped
     using Kern = void (*)(const CUtensorMap, const TcQuantParams);
     const bool fuse = gu != nullptr;
     const Kern kern = fuse ? (profile ? quant_token_tc_kernel<true, true> : quant_token_tc_kernel<false, true>)

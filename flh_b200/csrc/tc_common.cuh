@@ -22,28 +22,35 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds instead of coming back at
+// once, so a waiting warp does not spend issue slots on a spin loop beside the warps that have work
+__device__ __forceinline__ bool mbar_try_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ uint64_t gtimer() {
     uint64_t t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: false when two seconds pass or another thread of the CTA already gave up.
+// Bounded wait: false when two seconds pass or another thread of the CTA already gave up.  Each try may sleep in hardware
+// for up to 20 us (suspend-time hint), so the loop turns a few times per wait instead of spinning.
 __device__ __forceinline__ bool mbar_wait_status(int *status, uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                                  int code, unsigned long long *waited = nullptr) {
     if (mbar_try(bar, parity)) return true;
     const uint64_t t0 = gtimer();
-    for (int it = 0;; ++it) {
-        if (mbar_try(bar, parity)) {
+    for (;;) {
+        if (mbar_try_hint(bar, parity, 20000u)) {
             if (waited) *waited += gtimer() - t0;
             return true;
         }
-        if ((it & 63) == 63) {
-            if (*abort_flag) return false;
-            if (gtimer() - t0 > 2000000000ull) {
-                *abort_flag = code;
-                if (atomicCAS(&status[0], 0, code) == 0) status[1] = blockIdx.x + 65536 * blockIdx.y;
-                return false;
-            }
+        if (*abort_flag) return false;
+        if (gtimer() - t0 > 2000000000ull) {
+            *abort_flag = code;
+            if (atomicCAS(&status[0], 0, code) == 0) status[1] = blockIdx.x + 65536 * blockIdx.y;
+            return false;
         }
     }
 }

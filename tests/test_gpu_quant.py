@@ -104,7 +104,9 @@ def test_token_asym_hadamard_bit_exact(cuda, m, k):
     assert np.array_equal(q.cpu().numpy(), qo)
 
 
-TC_SHAPES = TOKEN_SHAPES + [(64, 11008), (33, 14336), (1, 11008), (7, 11008), (301, 11008), (1001, 11008), (1, 14336), (16, 14336),
+# 2560 = 40 * 64, 3072 = 12 * 256 and 3584 = 28 * 128 have a factor with two to eight Sylvester bits beside it
+TC_SHAPES = TOKEN_SHAPES + [(3, 2560), (300, 2560), (700, 3584), (2000, 4096), (1187, 4096), (4, 3072), (1, 4096), (2, 4096), (3, 4096),
+                            (4, 4096), (5, 4096), (6, 4096), (7, 4096), (8, 4096), (64, 11008), (33, 14336), (1, 11008), (7, 11008), (301, 11008), (1001, 11008), (1, 14336), (16, 14336),
                             (256, 14336), (16, 11008), (256, 11008), (256, 4096), (131, 8192), (40, 7168), (9, 3584)]
 
 
@@ -123,7 +125,7 @@ def test_token_asym_default_transform_tolerance(cuda, m, k):
 def test_token_asym_default_transform_is_batch_independent(cuda):
     """A token row gets the same codes whatever batch it arrives in (the default transform takes one kernel, one
     summation order, for every M)."""
-    for k in (4096, 11008):
+    for k in (4096, 3584, 11008):
         x = activations(4300 + k, 300, k)
         xd = _dev(x)
         qa, sa, za = cuda.quant_token_asym_i4(xd, hadamard=True)
