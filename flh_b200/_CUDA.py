@@ -21,7 +21,7 @@ from .hadamard import get_hadK
 
 F16, BF16 = 0, 1
 GEMM_AUTO, GEMM_TCGEN05, GEMM_MMA_SYNC, GEMM_STREAM, GEMM_STREAM_SPLITK, GEMM_TCGEN05_DIRECT = 0, 1, 2, 3, 4, 5
-GEMM_TCGEN05_I8, GEMM_TCGEN05_I8_PAIR = 6, 7
+GEMM_TCGEN05_I8, GEMM_TCGEN05_I8_PAIR, GEMM_DECODE_TC = 6, 7, 8
 
 
 def _check(cond: bool, msg: str) -> None:

@@ -69,6 +69,14 @@ int quant_token_tc_status_clear();
 int gemm_i8_wait_profile(unsigned long long *);
 int gemm_i8_status_clear();
 
+size_t gemm_decode_tc_workspace_bytes(long M, long N, long K);
+bool gemm_decode_tc_supported(long M, long N, long K, long a_group);
+int launch_gemm_decode_tc(const uint8_t *, const uint8_t *, const void *, const void *, const void *,
+                          const int32_t *, const void *, void *, long, long, long, long, long, int, void *, cudaStream_t);
+int gemm_decode_tc_status(int *);
+int gemm_decode_tc_status_clear();
+int gemm_decode_tc_wait_profile(unsigned long long *);
+
 int gemm_tcgen05_status(int *);
 int gemm_tcgen05_wait_profile(unsigned long long *);
 int gemm_tcgen05_status_clear();
@@ -246,9 +254,20 @@ int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t
     return launch_weight_rowsum(B, N, K, group, rowsum, static_cast<cudaStream_t>(stream));
 }
 
+// Decode shapes where the tensor-core kernel beats the mma.sync streaming kernel (measured on B200): its set-up and
+// the hand-over of shared tiles cost ~9 us, its streaming rate is higher and does not drop with the token count.
+static bool decode_tc_pays(long M, long N, long K, long a_group) {
+    const double mib = (double)N * (double)K / 2.0 / (1 << 20);            // packed weight bytes
+    const double need = M > 32 ? 12.0 : (M > 16 ? 32.0 : 64.0);
+    return mib >= need && gemm_decode_tc_supported(M, N, K, a_group);
+}
+static int pick_stream(long M, long N, long K) {
+    return stream_splits(M, N, K) > 1 ? FLH_B200_GEMM_STREAM_SPLITK : FLH_B200_GEMM_STREAM;
+}
+
 int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group) {
     if ((a_group < b_group ? a_group : b_group) < 128) return FLH_B200_GEMM_MMA_SYNC;    // K-groups of 32 / 64
-    if (M <= 64) return stream_splits(M, N, K) > 1 ? FLH_B200_GEMM_STREAM_SPLITK : FLH_B200_GEMM_STREAM;
+    if (M <= 64) return decode_tc_pays(M, N, K, a_group) ? FLH_B200_GEMM_DECODE_TC : pick_stream(M, N, K);
     // large batches without group scales: expanding both operands to int8 first pays for itself
     if (a_group == K && b_group == K && M >= 1024)
         return N % 256 == 0 ? FLH_B200_GEMM_TCGEN05_I8_PAIR : FLH_B200_GEMM_TCGEN05_I8;
@@ -258,6 +277,7 @@ int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group) 
 size_t flh_b200_gemm_workspace_bytes(long M, long N, long K, long a_group, long b_group, int algo) {
     if (algo == FLH_B200_GEMM_AUTO) algo = flh_b200_gemm_pick_algo(M, N, K, a_group, b_group);
     if (algo == FLH_B200_GEMM_TCGEN05_I8 || algo == FLH_B200_GEMM_TCGEN05_I8_PAIR) return gemm_i8_workspace_bytes(M, N, K);
+    if (algo == FLH_B200_GEMM_DECODE_TC) return M <= 64 ? gemm_decode_tc_workspace_bytes(M, N, K) : 0;
     if (algo != FLH_B200_GEMM_STREAM_SPLITK || M > 64) return 0;
     return stream_scratch_bytes(M, N, stream_splits(M, N, K));
 }
@@ -289,6 +309,10 @@ int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_s
     }
     if (algo == FLH_B200_GEMM_AUTO) {
         algo = flh_b200_gemm_pick_algo(M, N, K, a_group, b_group);
+        // without (enough) scratch the tensor-core decode kernel gives way to the streaming kernels
+        if (algo == FLH_B200_GEMM_DECODE_TC &&
+            (!workspace || workspace_bytes < gemm_decode_tc_workspace_bytes(M, N, K) || (reinterpret_cast<uintptr_t>(workspace) & 255)))
+            algo = pick_stream(M, N, K);
         // without (enough) scratch the split-K form quietly gives way to the plain streaming kernel
         if (algo == FLH_B200_GEMM_STREAM_SPLITK &&
             (!workspace || workspace_bytes < stream_scratch_bytes(M, N, stream_splits(M, N, K))))
@@ -313,6 +337,16 @@ int flh_b200_gemm_i4_dequant(const uint8_t *A, const uint8_t *B, const void *a_s
                         "split-K needs %zu bytes of zero-initialised workspace (got %zu)", need, workspace_bytes);
             FLH_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, FLH_B200_EALIGN, "workspace must be 256-byte aligned");
             return launch_gemm_stream(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, splits, workspace, s);
+        }
+        case FLH_B200_GEMM_DECODE_TC: {
+            FLH_REQUIRE(M <= 64, FLH_B200_EINVAL, "the decode kernel serves M <= 64 (got %ld)", M);
+            FLH_REQUIRE(gemm_decode_tc_supported(M, N, K, a_group), FLH_B200_EUNSUPPORTED,
+                        "the decode kernel does not serve N=%ld K=%ld with this scale layout (too many tiles or token scales)", N, K);
+            const size_t need = gemm_decode_tc_workspace_bytes(M, N, K);
+            FLH_REQUIRE(workspace && workspace_bytes >= need, FLH_B200_EINVAL,
+                        "the decode kernel needs %zu bytes of zero-initialised workspace (got %zu)", need, workspace_bytes);
+            FLH_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, FLH_B200_EALIGN, "workspace must be 256-byte aligned");
+            return launch_gemm_decode_tc(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, workspace, s);
         }
         case FLH_B200_GEMM_MMA_SYNC:
             return launch_gemm_mma_tile(A, B, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, a_group, b_group, out_dtype, s);
@@ -397,7 +431,10 @@ int flh_b200_gemm_status(int *out) {
     if (out[0]) return quant_token_factor_status_clear();
     rc = quant_token_tc_status(out);
     if (rc) return rc;
-    return out[0] ? quant_token_tc_status_clear() : 0;
+    if (out[0]) return quant_token_tc_status_clear();
+    rc = gemm_decode_tc_status(out);
+    if (rc) return rc;
+    return out[0] ? gemm_decode_tc_status_clear() : 0;
 }
 
 int flh_b200_quant_token_wait_profile(unsigned long long *out) {
@@ -411,7 +448,11 @@ int flh_b200_gemm_wait_profile(unsigned long long *out) {
     if (rc) return rc;
     bool any = false;
     for (int i = 0; i < 8; ++i) any = any || out[i] != 0;
-    return any ? 0 : gemm_i8_wait_profile(out);        // nothing from the converting kernels: the int8-operand ones
+    if (any) return 0;
+    rc = gemm_i8_wait_profile(out);                    // nothing from the converting kernels: the int8-operand ones,
+    if (rc) return rc;
+    for (int i = 0; i < 8; ++i) any = any || out[i] != 0;
+    return any ? 0 : gemm_decode_tc_wait_profile(out); // then the decode kernel
 }
 
 void flhDenseLayerGEMM_i4_o16(const uint8_t *A, const uint8_t *B, const void *A_scale, const void *B_scale,

@@ -51,6 +51,8 @@ extern "C" {
                                      first, then TMA + tcgen05.mma on int8 tiles (no conversion inside the GEMM)  */
 #define FLH_B200_GEMM_TCGEN05_I8_PAIR 7 /* the same on two-CTA clusters (tcgen05 cta_group::2, 256 x 256 tiles);
                                           N % 256 == 0                                                         */
+#define FLH_B200_GEMM_DECODE_TC 8 /* M <= 64 on the tensor cores with the operands swapped (weights on the MMA's M side),
+                                    K-ranges balanced across CTAs; needs zero-initialised workspace like split-K */
 
 int flh_b200_version(void);
 const char *flh_b200_last_error(void);
@@ -188,13 +190,16 @@ int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t
  *   flh_gemm_i4_dequant_o16_kernel (flh/kernels/gemm_and_dequant_i4.cu:287-313, 315-469).
  *   N % 128 == 0 and K % 128 == 0 are required (as the reference kernel assumes), K <= 65536.
  *   algo: FLH_B200_GEMM_*.  workspace: device scratch of at least
- *   flh_b200_gemm_workspace_bytes(...) bytes, 256-byte aligned (may be NULL when that is 0).  Only the
- *   split-K streaming kernel uses it (decode shapes whose N alone cannot fill the GPU): its first 4 KB
- *   are arrival counters that must be ZERO before the first launch and are left zero by every launch;
- *   launches that share a workspace must not overlap on the GPU.  With AUTO and no (or too small a)
- *   workspace the plain streaming kernel (or, for large batches, the converting tcgen05 kernel) runs instead.  Split-K adds the per-split binary32 chains in
- *   split order, so with group scales its outputs can differ from the single chain in the last bit
- *   (<= 1e-3 relative); without group scales the partial sums are int32 and the result is identical.
+ *   flh_b200_gemm_workspace_bytes(...) bytes, 256-byte aligned (may be NULL when that is 0).  The two decode
+ *   kernels that share output tiles between CTAs use it: the split-K streaming kernel (decode shapes whose N
+ *   alone cannot fill the GPU) and the tensor-core decode kernel (DECODE_TC; AUTO picks it for M <= 64 when
+ *   the packed weights reach 64 MiB, 32 MiB above 16 tokens, 12 MiB above 32).  Its first 8 KB are arrival
+ *   counters that must be ZERO before the first launch and are left zero by every launch; launches that
+ *   share a workspace must not overlap on the GPU.  With AUTO and no (or too small a) workspace the plain
+ *   streaming kernel (or, for large batches, the converting tcgen05 kernel) runs instead.  Both kernels add
+ *   the binary32 chains of the CTAs that share a tile in K order, so with group scales their outputs can
+ *   differ from the single chain in the last bit (<= 1e-3 relative, the same bits on every run); without
+ *   group scales the partial sums are int32 and the result is identical.  STREAM and TCGEN05 never split a chain.
  *   The int8-operand kernels (TCGEN05_I8, TCGEN05_I8_PAIR; a_group = b_group = K only) write the expanded
  *   operands, (M + N) * K bytes, into the workspace; it needs no initial contents, results are bit-identical
  *   to the other kernels, and launches that share a workspace must not overlap on the GPU.

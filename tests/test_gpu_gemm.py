@@ -8,7 +8,7 @@ from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 
-STREAM, MMA, TC, SPLITK = 3, 2, 1, 4
+STREAM, MMA, TC, SPLITK, DECODE_TC = 3, 2, 1, 4, 8
 
 
 def _dev(a):
@@ -89,6 +89,64 @@ def test_stream_splitk(cuda, m, n, k):
     assert np.array_equal(d0.cpu().numpy().view(np.uint16), ref.view(np.uint16))
     err = (d1.float() - d0.float()).abs()
     assert bool((err <= 1e-3 * d0.float().abs() + 1e-3 * d0.float().abs().mean()).all()), err.max().item()
+
+
+def _close(d, ref16):
+    """Within 1e-3 of the single-chain result (relative, with a floor of 1e-3 of the mean magnitude)."""
+    got, ref = d.float().cpu().numpy(), ref16.astype(np.float32)
+    err = np.abs(got - ref)
+    return bool((err <= 1e-3 * np.abs(ref) + 1e-3 * np.abs(ref).mean()).all()), float(err.max())
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 32, 33, 64])
+def test_decode_tc_kernel(cuda, mode, m):
+    """The tensor-core decode kernel (weights on the MMA's M side, K-ranges balanced across CTAs).  Without group
+    scales the CTAs that share a tile hand over int32 sums: equal to the oracle bit for bit.  With group scales each
+    CTA keeps its own binary32 chain and the chains are added in K order: within 1e-3 of the oracle, the same bits
+    on every run."""
+    case = make_case(30 * m, m, 256, 1024, *mode, bias=(m == 17))
+    ap, bp, sa, sb, za, bi = case
+    if mode[0] == 0 and mode[1] == 0:
+        run_case(cuda, DECODE_TC, case, bf16=(m == 33))
+        return
+    k = ap.shape[1] * 2
+    rsum = None if za is None else cuda.weight_rowsum(_dev(bp), min(k // sa.shape[1], k // sb.shape[1]))
+    args = (_dev(ap), _dev(bp), _dev(sa), _dev(sb))
+    kw = dict(A_zero=None if za is None else _dev(za), B_rowsum=rsum, bias=None if bi is None else _dev(bi), algo=DECODE_TC)
+    d1, d2 = cuda.gemm_i4_dequant(*args, **kw), cuda.gemm_i4_dequant(*args, **kw)
+    assert torch.equal(d1.view(torch.int16), d2.view(torch.int16))
+    ok, worst = _close(d1, O.gemm_i4_dequant(ap, bp, sa, sb, a_zero=za, bias=bi))
+    assert ok, worst
+
+
+@pytest.mark.parametrize("m,n,k", [(4, 128, 512), (16, 128, 128), (40, 128, 384)])
+def test_decode_tc_whole_tiles(cuda, m, n, k):
+    """A tile whose K lies in one CTA keeps a single chain: bit-exact with group scales too."""
+    for mode in MODES:
+        run_case(cuda, DECODE_TC, make_case(m + k, m, n, k, *mode))
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 4096, 4096), (5, 1024, 11008), (64, 1152, 2304), (32, 8192, 3584)])
+def test_decode_tc_shapes(cuda, m, n, k):
+    run_case(cuda, DECODE_TC, make_case(m + n + k, m, n, k, 0, 0, True, bias=True))
+    run_case(cuda, DECODE_TC, make_case(m + n + k + 1, m, n, k, 0, 0, False), bf16=True)
+    ap, bp, sa, sb, _, _ = make_case(m + n + 2, m, n, k, 128, 128, False)
+    d = cuda.gemm_i4_dequant(_dev(ap), _dev(bp), _dev(sa), _dev(sb), algo=DECODE_TC)
+    ok, worst = _close(d, O.gemm_i4_dequant(ap, bp, sa, sb))
+    assert ok, worst
+    st = cuda.gemm_status()
+    assert st[0] == 0, st
+
+
+def test_auto_picks_decode_tc_for_large_decode_shapes(cuda):
+    pick = cuda._lib.load().flh_b200_gemm_pick_algo
+    assert pick(64, 8192, 8192, 128, 128) == DECODE_TC          # 32 MiB of weights, 64 tokens
+    assert pick(32, 8192, 8192, 8192, 8192) == DECODE_TC
+    assert pick(16, 28672, 8192, 128, 128) == DECODE_TC         # 112 MiB
+    assert pick(16, 22016, 4096, 128, 128) == STREAM            # 43 MiB at 16 tokens: the streaming kernel
+    assert pick(16, 4096, 4096, 128, 128) == SPLITK
+    assert pick(128, 8192, 8192, 128, 128) == TC
 
 
 def test_reference_script_case(cuda):
