@@ -576,20 +576,34 @@ def extras(C, device, peaks):
                 t = _time(lambda: C.gemm_i8w_dequant(A, B8, sa, sb, A_zero=za, B_rowsum=rs), iters=5, warm=2)
                 ex[f"gemm_M{m}_{k}to{n}_{tag}_prepacked_TOPS"] = 2.0 * m * n * k / t / 1e12
                 del B8
-    for (m, k, n) in ((1, 4096, 22016), (16, 4096, 22016), (16, 11008, 4096), (16, 4096, 4096)):
-        sets = [gemm_inputs(C, m, n, k, True, False, device, seed=s) for s in range(3)]
+    for (m, k, n) in ((1, 4096, 22016), (16, 4096, 22016), (64, 4096, 22016), (16, 11008, 4096), (16, 4096, 4096),
+                      (16, 8192, 28672), (64, 8192, 28672)):
+        # enough copies of the weights that successive launches cannot be served from the 126 MB L2
+        base = gemm_inputs(C, m, n, k, True, False, device, seed=0)
+        nsets = max(3, -(-320_000_000 // (n * k // 2)))
+        sets = [base] + [(base[0], base[1].clone()) + base[2:] for _ in range(nsets - 1)]
         it = [0]
 
         D = torch.empty((m, n), dtype=torch.float16, device=device)
 
         def f():
             it[0] += 1
-            A, B, sa, sb, za, rs = sets[it[0] % 3]
+            A, B, sa, sb, za, rs = sets[it[0] % nsets]
             C.gemm_i4_dequant(A, B, sa, sb, out=D)
 
-        t = _time(f, iters=12, graph=True)
+        t = _time(f, iters=max(12, nsets), graph=True)
         b = n * k // 2 + 2 * n * (k // 128) + m * k // 2 + 2 * m * n
         ex[f"gemm_decode_M{m}_{k}to{n}_g128_GBps"] = b / t / 1e9
+        if m == 16:
+            # what a plain streaming read of the same packed weights reaches at this size (the row-sum kernel): the
+            # practical ceiling of a launch this short, well under the large-copy HBM peak
+            def r():
+                it[0] += 1
+                C.weight_rowsum(sets[it[0] % nsets][1], k)
+
+            t = _time(r, iters=max(12, nsets), graph=True)
+            ex[f"read_ceiling_{k}to{n}_GBps"] = (n * k // 2) / t / 1e9
+        del sets
     a8 = torch.randint(-8, 8, (8192, 8192), device=device, dtype=torch.int8)
     b8 = torch.randint(-8, 8, (8192, 8192), device=device, dtype=torch.int8)
     t = _time(lambda: torch._int_mm(a8, b8), iters=5, warm=2)

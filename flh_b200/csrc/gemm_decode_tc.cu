@@ -5,7 +5,8 @@
 //   warp 0 (one thread)   TMA: 128 x 64 B of packed weights + TOK x 64 B of packed tokens per 128-K block -> smem ring
 //   warps 2-5             nibbles -> int8 (x16) in the K-major 128-byte-swizzled layout tcgen05 reads
 //   warp 1 (one thread)   four tcgen05.mma (K = 32 each) per block; D[channel][token] int32 in TMEM
-//   warps 6-9             thread = output channel: tcgen05.ld of the TOK sums of a block, dequantise
+//   warps 6-9 (6-13 for 64 tokens: two groups, 32 token columns each)
+//                         thread = output channel: tcgen05.ld of its token sums of a block, dequantise
 //                         (acc = fmaf(float(I_g), sa * sb, acc) per 128-K group, or once per channel), store D^T
 //
 // Work split ("stream-K"): the (tile, K-block) pairs are laid out in one line, tile-major, and cut into equal
@@ -25,8 +26,11 @@ namespace {
 
 constexpr int BR = 128;                 // output channels per tile = MMA M
 constexpr int BK = 128;                 // K per stage = one 128-byte swizzle row of int8
-constexpr int kThreads = 320;
-constexpr int kCounterBytes = 8192;     // one arrival counter per tile (N <= 262144)
+// One arrival counter per tile and epilogue group, in the first 4 KB of the workspace: the same 4 KB the split-K
+// streaming kernel keeps its slab counters in (both leave them zero, and everything after is scratch for both),
+// so one workspace can serve whichever of the two AUTO picks for a shape.
+constexpr int kMaxTiles = 512;          // N <= 65536
+constexpr int kCounterBytes = 2 * kMaxTiles * 4;
 
 __device__ int g_status[4];
 
@@ -61,6 +65,8 @@ struct DecPlan {
     static constexpr int SP = TOK == 16 ? 7 : (TOK == 32 ? 6 : 10);  // packed stages in flight (TMA)
     static constexpr int SE = kTwo ? 2 : 3;                 // expanded stages
     static constexpr int NBUF = GROUPED ? 4 : 2;            // TMEM accumulators
+    static constexpr int EG = TOK == 64 ? 2 : 1;            // epilogue groups of four warps, TOK / EG token columns each
+    static constexpr int kThreads = 192 + 128 * EG;
     static constexpr int kTmemCols = NBUF * TOK < 32 ? 32 : NBUF * TOK;
     static constexpr int kPkStage = (BR + TOK) * (BK / 2);
     static constexpr int kExStage = (BR + TOK) * BK;
@@ -85,11 +91,11 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[TOK])
 }
 
 template <int TOK, bool GROUPED, bool A_UNSIGNED>
-__global__ void __launch_bounds__(kThreads, TOK <= 32 ? 2 : 1)
+__global__ void __launch_bounds__((DecPlan<TOK, GROUPED>::kThreads), TOK <= 32 ? 2 : 1)
 gemm_decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       const DecParams p) {
     using Plan = DecPlan<TOK, GROUPED>;
-    constexpr int SP = Plan::SP, SE = Plan::SE, NBUF = Plan::NBUF;
+    constexpr int SP = Plan::SP, SE = Plan::SE, NBUF = Plan::NBUF, EG = Plan::EG, TE = TOK / EG;
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -122,9 +128,9 @@ gemm_decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     if (tid == 0) {
         for (int s = 0; s < SP; ++s) { mbar_init(pk_full(s), 1); mbar_init(pk_empty(s), 128); }
         for (int s = 0; s < SE; ++s) { mbar_init(ex_full(s), 128); mbar_init(ex_empty(s), 1); }
-        for (int b = 0; b < NBUF; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 128); }
+        for (int b = 0; b < NBUF; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 128 * EG); }
         *abort_flag = 0;
-        *s_last = 0;
+        s_last[0] = 0; s_last[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
@@ -237,17 +243,30 @@ gemm_decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         if (ct == 0) { atomicAdd(&g_wait_ns[4], w4); atomicAdd(&g_wait_ns[5], w5); }
     } else {
         // ------------------------------------------------------------ epilogue: thread = output channel
-        const int et = tid - 192;                        // 0..127
+        // 64 token columns are shared by two groups of four warps (32 columns each): the per-group work of a K-block
+        // is what bounds this role
+        const int eg = (tid - 192) >> 7;                 // epilogue group
+        const int et = (tid - 192) & 127;                // 0..127 within the group
+        const int j0 = eg * TE;                          // first token column of this group
         const int wq = warp & 3;                         // the TMEM lane quarter this warp may read
         const int r = wq * 32 + lane;                    // channel within the tile = TMEM lane
         const uint32_t tlane = tmem + ((uint32_t)(wq * 32) << 16);
         const int gbs = p.gb_cols > 1 ? 1 : 0, gas = p.ga_cols > 1 ? TOK : 0;
-        for (int i = et; i < sa_n; i += 128) {
-            const int g = i / TOK, j = i - g * TOK;
-            sa_s[i] = j < p.M ? __half2float(p.a_scale[(long)j * p.ga_cols + g]) : 0.0f;
-            if (A_UNSIGNED) za_s[i] = j < p.M ? (int)__half2float(p.a_zero[(long)j * p.ga_cols + g]) : 0;
+        if (p.ga_cols > 1) {
+            // only the K-groups this CTA multiplies; consecutive threads read consecutive groups of one token
+            const int ng = min(count, KB);
+            for (int i = tid - 192; i < ng * TOK; i += 128 * EG) {
+                const int j = i / ng, kb = (lin_begin + (i - j * ng)) % KB;
+                sa_s[kb * TOK + j] = j < p.M ? __half2float(p.a_scale[(long)j * KB + kb]) : 0.0f;
+                if (A_UNSIGNED) za_s[kb * TOK + j] = j < p.M ? (int)__half2float(p.a_zero[(long)j * KB + kb]) : 0;
+            }
+        } else {
+            for (int j = tid - 192; j < TOK; j += 128 * EG) {
+                sa_s[j] = j < p.M ? __half2float(p.a_scale[j]) : 0.0f;
+                if (A_UNSIGNED) za_s[j] = j < p.M ? (int)__half2float(p.a_zero[j]) : 0;
+            }
         }
-        bar_sync_named(1, 128);
+        bar_sync_named(1, 128 * EG);
         int u = 0;
         bool ok = true;
         unsigned long long w6 = 0, w7 = 0;
@@ -260,10 +279,10 @@ gemm_decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             const int kb1 = min(KB, kb0 + (lin_end - lin));
             const int n = tile * BR + r;
             const bool whole = kb0 == 0 && kb1 == KB;
-            uint64_t accf[TOK / 2];                       // binary32 chains, two tokens per register pair
-            int acci[TOK];                                // int32 sums (x256) without group scales
+            uint64_t accf[TE / 2];                       // binary32 chains, two tokens per register pair
+            int acci[TE];                                // int32 sums (x256) without group scales
 #pragma unroll
-            for (int j = 0; j < TOK / 2; ++j) accf[j] = 0ull;
+            for (int j = 0; j < TE / 2; ++j) accf[j] = 0ull;
 
             if (GROUPED) {
                 // 256 * sum arrives from the tensor core; without zero-points the 1/256 rides in the weight scale
@@ -280,16 +299,16 @@ gemm_decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     const int buf = u % NBUF;
                     ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full(buf), (u / NBUF) & 1, abort_flag, 6, &w6));
                     tc_fence_after();
-                    uint32_t v[TOK];
-                    if (ok) { tmem_ld_cols<TOK>(tlane + buf * TOK, v); tc_wait_ld(); }
+                    uint32_t v[TE];
+                    if (ok) { tmem_ld_cols<TE>(tlane + buf * TOK + j0, v); tc_wait_ld(); }
                     tc_fence_before();
                     mbar_arrive(acc_empty(buf));
                     if (ok) {
-                        const float *sa = sa_s + gas * kb;
-                        const int *za = za_s + gas * kb;
+                        const float *sa = sa_s + gas * kb + j0;
+                        const int *za = za_s + gas * kb + j0;
                         const uint64_t sb2 = pack2(sbv, sbv);
 #pragma unroll
-                        for (int j = 0; j < TOK; j += 2) {
+                        for (int j = 0; j < TE; j += 2) {
                             const float2 sap = *reinterpret_cast<const float2 *>(sa + j);
                             int i0 = (int)v[j], i1 = (int)v[j + 1];
                             if (A_UNSIGNED) { i0 = (i0 >> 8) - za[j] * rsv; i1 = (i1 >> 8) - za[j + 1] * rsv; }
@@ -303,13 +322,13 @@ gemm_decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 const int buf = u % NBUF;
                 ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full(buf), (u / NBUF) & 1, abort_flag, 7, &w6));
                 tc_fence_after();
-                uint32_t v[TOK];
-                if (ok) { tmem_ld_cols<TOK>(tlane + buf * TOK, v); tc_wait_ld(); }
+                uint32_t v[TE];
+                if (ok) { tmem_ld_cols<TE>(tlane + buf * TOK + j0, v); tc_wait_ld(); }
                 tc_fence_before();
                 mbar_arrive(acc_empty(buf));
                 ++u;
 #pragma unroll
-                for (int j = 0; j < TOK; ++j) acci[j] = ok ? (int)v[j] : 0;
+                for (int j = 0; j < TE; ++j) acci[j] = ok ? (int)v[j] : 0;
             }
 
             bool finish = whole;
@@ -317,10 +336,10 @@ gemm_decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 // this CTA holds only part of the tile's K: leave the partial sums, count the arrival
                 const int first_cta = (tile * KB) / p.per, last_cta = (tile * KB + KB - 1) / p.per;
                 const int slot = 2 * blockIdx.x + (lin_begin / KB == tile ? 0 : 1);
-                float *dst = p.partials + (size_t)slot * TOK * BR + r;
+                float *dst = p.partials + ((size_t)slot * TOK + j0) * BR + r;
                 if (ok) {
 #pragma unroll
-                    for (int j = 0; j < TOK; ++j) {
+                    for (int j = 0; j < TE; ++j) {
                         float lo, hi;
                         unpack2(accf[j >> 1], lo, hi);
                         dst[j * BR] = GROUPED ? ((j & 1) ? hi : lo) : __int_as_float(acci[j]);
@@ -328,38 +347,38 @@ gemm_decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 }
                 const uint64_t t7 = gtimer();
                 __threadfence();
-                bar_sync_named(1, 128);
-                if (et == 0) *s_last = atomicAdd(&p.counters[tile], 1) == last_cta - first_cta;
-                bar_sync_named(1, 128);
-                finish = *s_last != 0;
+                bar_sync_named(2 + eg, 128);
+                if (et == 0) s_last[eg] = atomicAdd(&p.counters[tile + eg * kMaxTiles], 1) == last_cta - first_cta;
+                bar_sync_named(2 + eg, 128);
+                finish = s_last[eg] != 0;
                 if (finish) {
                     __threadfence();
 #pragma unroll
-                    for (int j = 0; j < TOK / 2; ++j) accf[j] = 0ull;
+                    for (int j = 0; j < TE / 2; ++j) accf[j] = 0ull;
 #pragma unroll
-                    for (int j = 0; j < TOK; ++j) acci[j] = 0;
-                    constexpr int PF = TOK == 16 ? 4 : (TOK == 32 ? 2 : 1);     // parts whose loads are in flight together
+                    for (int j = 0; j < TE; ++j) acci[j] = 0;
+                    constexpr int PF = TE == 16 ? 4 : 2;     // parts whose loads are in flight together
                     for (int c0 = first_cta; c0 <= last_cta; c0 += PF) {
-                        float w[PF][TOK];
+                        float w[PF][TE];
 #pragma unroll
                         for (int q = 0; q < PF; ++q) {
                             const int c = min(c0 + q, last_cta);
                             const int sl = 2 * c + ((c * p.per) / KB == tile ? 0 : 1);
-                            const float *src = p.partials + (size_t)sl * TOK * BR + r;
+                            const float *src = p.partials + ((size_t)sl * TOK + j0) * BR + r;
 #pragma unroll
-                            for (int j = 0; j < TOK; ++j) w[q][j] = __ldcg(src + j * BR);
+                            for (int j = 0; j < TE; ++j) w[q][j] = __ldcg(src + j * BR);
                         }
 #pragma unroll
                         for (int q = 0; q < PF; ++q) {
                             if (c0 + q > last_cta) break;
 #pragma unroll
-                            for (int j = 0; j < TOK; j += 2) {
+                            for (int j = 0; j < TE; j += 2) {
                                 if (GROUPED) accf[j >> 1] = (c0 + q == first_cta) ? pack2(w[q][j], w[q][j + 1]) : add2(accf[j >> 1], pack2(w[q][j], w[q][j + 1]));
                                 else { acci[j] += __float_as_int(w[q][j]); acci[j + 1] += __float_as_int(w[q][j + 1]); }
                             }
                         }
                     }
-                    if (et == 0) p.counters[tile] = 0;     // ready for the next launch
+                    if (et == 0) p.counters[tile + eg * kMaxTiles] = 0;     // ready for the next launch
                 }
                 w7 += gtimer() - t7;
             }
@@ -373,24 +392,25 @@ gemm_decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                     rsc = A_UNSIGNED ? p.b_rowsum[n] : 0;
                 }
 #pragma unroll
-                for (int j = 0; j < TOK; ++j) {
+                for (int j = 0; j < TE; ++j) {
                     float lo, hi;
                     unpack2(accf[j >> 1], lo, hi);
                     float o = (j & 1) ? hi : lo;
+                    const int tok = j0 + j;
                     if (!GROUPED) {
-                        const int I = A_UNSIGNED ? acci[j] - ((za_s[j] * rsc) << 8) : acci[j];
-                        o = __fmaf_rn((float)I, __fmul_rn(sa_s[j], sbc), 0.0f);
+                        const int I = A_UNSIGNED ? acci[j] - ((za_s[tok] * rsc) << 8) : acci[j];
+                        o = __fmaf_rn((float)I, __fmul_rn(sa_s[tok], sbc), 0.0f);
                     }
                     if (p.bias) o = __fadd_rn(o, bias);
-                    if (j < p.M) {
-                        if (p.out_bf16) static_cast<__nv_bfloat16 *>(p.D)[(long)j * p.N + n] = __float2bfloat16_rn(o);
-                        else static_cast<__half *>(p.D)[(long)j * p.N + n] = __float2half_rn(o);
+                    if (tok < p.M) {
+                        if (p.out_bf16) static_cast<__nv_bfloat16 *>(p.D)[(long)tok * p.N + n] = __float2bfloat16_rn(o);
+                        else static_cast<__half *>(p.D)[(long)tok * p.N + n] = __float2half_rn(o);
                     }
                 }
             }
             lin += kb1 - kb0;
         }
-        if (et == 0) { atomicAdd(&g_wait_ns[6], w6); atomicAdd(&g_wait_ns[7], w7); }
+        if (et == 0 && eg == 0) { atomicAdd(&g_wait_ns[6], w6); atomicAdd(&g_wait_ns[7], w7); }
     }
 
     __syncthreads();
@@ -483,7 +503,7 @@ int launch_t(const CUtensorMap &mw, const CUtensorMap &mx, const DecParams &p, i
     if (smem > 227 * 1024) return fail(FLH_B200_EUNSUPPORTED, "K = %d needs %d bytes of shared memory for the token scales", p.K, smem);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_status(e, "gemm_decode_tc attribute");
-    kern<<<grid, kThreads, smem, stream>>>(mw, mx, p);
+    kern<<<grid, Plan::kThreads, smem, stream>>>(mw, mx, p);
     return cuda_status(cudaGetLastError(), "gemm_decode_tc launch");
 }
 
@@ -495,10 +515,10 @@ int launch_tok(const CUtensorMap &mw, const CUtensorMap &mx, const DecParams &p,
 
 }  // namespace
 
-// Shapes the kernel serves: M <= 64, at most 2048 tiles of 128 channels, and token scales of the whole K that fit
+// Shapes the kernel serves: M <= 64, at most 512 tiles of 128 channels, and token scales of the whole K that fit
 // beside the stage rings in shared memory (group scales on the token side are the large case).
 bool gemm_decode_tc_supported(long M, long N, long K, long a_group) {
-    if (M < 1 || M > 64 || N % BR || K % BK || N / BR > kCounterBytes / 4) return false;
+    if (M < 1 || M > 64 || N % BR || K % BK || N / BR > kMaxTiles) return false;
     const int tok = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const long aux = (a_group < K ? (K / BK) * tok : tok) * 8;      // with zero-points
     const long fixed = tok == 16 ? DecPlan<16, true>::kAuxOff : (tok == 32 ? DecPlan<32, true>::kAuxOff : DecPlan<64, true>::kAuxOff);
@@ -515,7 +535,7 @@ int launch_gemm_decode_tc(const uint8_t *A, const uint8_t *B, const void *a_scal
                           const void *b_scale, const int32_t *b_rowsum, const void *bias, void *D, long M,
                           long N, long K, long a_group, long b_group, int out_dtype, void *workspace,
                           cudaStream_t stream) {
-    if (N / BR > kCounterBytes / 4) return fail(FLH_B200_EUNSUPPORTED, "N = %ld is more than the %d tiles the counters cover", N, kCounterBytes / 4);
+    if (N / BR > kMaxTiles) return fail(FLH_B200_EUNSUPPORTED, "N = %ld is more than the %d tiles the counters cover", N, kMaxTiles);
     DecParams p;
     p.a_scale = static_cast<const __half *>(a_scale);
     p.a_zero = static_cast<const __half *>(a_zero);

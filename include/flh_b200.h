@@ -193,7 +193,7 @@ int flh_b200_weight_rowsum(const uint8_t *B, long N, long K, long group, int32_t
  *   flh_b200_gemm_workspace_bytes(...) bytes, 256-byte aligned (may be NULL when that is 0).  The two decode
  *   kernels that share output tiles between CTAs use it: the split-K streaming kernel (decode shapes whose N
  *   alone cannot fill the GPU) and the tensor-core decode kernel (DECODE_TC; AUTO picks it for M <= 64 when
- *   the packed weights reach 64 MiB, 32 MiB above 16 tokens, 12 MiB above 32).  Its first 8 KB are arrival
+ *   the packed weights reach 64 MiB, 32 MiB above 16 tokens, 12 MiB above 32).  Its first 4 KB are arrival
  *   counters that must be ZERO before the first launch and are left zero by every launch; launches that
  *   share a workspace must not overlap on the GPU.  With AUTO and no (or too small a) workspace the plain
  *   streaming kernel (or, for large batches, the converting tcgen05 kernel) runs instead.  Both kernels add

@@ -139,11 +139,26 @@ def test_decode_tc_shapes(cuda, m, n, k):
     assert st[0] == 0, st
 
 
+def test_decode_kernels_share_one_workspace(cuda):
+    """Split-K and the tensor-core decode kernel alternate on one stream's workspace: each leaves the arrival counters
+    zero and treats the rest as scratch, so results do not depend on what ran before."""
+    big = make_case(77, 64, 8192, 2048, 0, 0, True)
+    small = make_case(78, 16, 1024, 4096, 128, 128, False)
+    for _ in range(2):
+        run_case(cuda, DECODE_TC, big)
+        ap, bp, sa, sb, _, _ = small
+        d = cuda.gemm_i4_dequant(_dev(ap), _dev(bp), _dev(sa), _dev(sb), algo=SPLITK)
+        ok, worst = _close(d, O.gemm_i4_dequant(ap, bp, sa, sb))
+        assert ok, worst
+    run_case(cuda, DECODE_TC, make_case(79, 40, 1024, 4096, 0, 0, False))
+
+
 def test_auto_picks_decode_tc_for_large_decode_shapes(cuda):
     pick = cuda._lib.load().flh_b200_gemm_pick_algo
     assert pick(64, 8192, 8192, 128, 128) == DECODE_TC          # 32 MiB of weights, 64 tokens
     assert pick(32, 8192, 8192, 8192, 8192) == DECODE_TC
     assert pick(16, 28672, 8192, 128, 128) == DECODE_TC         # 112 MiB
+    assert pick(16, 152064, 4096, 4096, 4096) == STREAM         # more tiles than the counters cover
     assert pick(16, 22016, 4096, 128, 128) == STREAM            # 43 MiB at 16 tokens: the streaming kernel
     assert pick(16, 4096, 4096, 128, 128) == SPLITK
     assert pick(128, 8192, 8192, 128, 128) == TC
