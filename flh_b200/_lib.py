@@ -28,6 +28,8 @@ SIGNATURES = {
                                                       c_void_p, c_void_p, c_void_p, c_void_p]),
     "flh_b200_rope_kv_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_int, c_void_p]),
+    "flh_b200_gptq_block": (c_int, [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
+                                    c_float, c_void_p, c_long, c_void_p, c_void_p]),
     "flh_b200_sign_table_bytes": (c_size_t, [c_int]),
     "flh_b200_pack_signs": (c_int, [c_void_p, c_int, c_void_p]),
     "flh_b200_weight_rowsum": (c_int, [c_void_p, c_long, c_long, c_long, c_void_p, c_void_p]),

@@ -63,6 +63,8 @@ int launch_silu_mul(const void *, int, long, long, long, void *, cudaStream_t);
 int launch_silu_mul_quant_token_tc(const void *, int, long, long, long, int, const uint32_t *, float, uint8_t *, void *, void *, cudaStream_t);
 int launch_rope_kv(const void *, const float *, const float *, void *, void *, void *, int, int, int, int, int, int, int, cudaStream_t);
 int quant_token_tc_status(int *);
+int launch_gptq_block(const float *, long, const float *, long, const float *, const float *, long, const int *, long, int, int, int,
+                      float, float *, long, float *, cudaStream_t);
 
 int quant_token_tc_wait_profile(unsigned long long *);
 int quant_token_tc_status_clear();
@@ -416,6 +418,20 @@ int flh_b200_gemm_i8w_dequant(const uint8_t *A, const uint8_t *B8, const void *a
     FLH_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, FLH_B200_EALIGN, "workspace must be 256-byte aligned");
     return launch_gemm_i8(A, nullptr, B8, a_scale, a_zero, b_scale, b_rowsum, bias, D, M, N, K, out_dtype,
                           N % 256 == 0, workspace, static_cast<cudaStream_t>(stream));
+}
+
+int flh_b200_gptq_block(const float *W, long ldw, const float *Hinv, long ldh, const float *scale, const float *zero,
+                        long lds, const int *group_of_col, long rows, int count, int maxq, int sym, float clip_ratio,
+                        float *Q, long ldq, float *Err, void *stream) {
+    FLH_REQUIRE(rows >= 0 && count >= 1 && count <= 128, FLH_B200_EINVAL, "bad shape rows=%ld count=%d (count must be 1..128)", rows, count);
+    FLH_REQUIRE(ldw >= count && ldh >= count && ldq >= count && lds >= 1, FLH_B200_EINVAL, "leading dimensions must cover the block");
+    FLH_REQUIRE(maxq >= 1 && maxq <= 255, FLH_B200_EINVAL, "maxq must be 1..255 (got %d)", maxq);
+    FLH_REQUIRE(clip_ratio > 0.0f, FLH_B200_EINVAL, "clip_ratio must be positive");
+    if (rows == 0) return 0;
+    FLH_REQUIRE(W && Hinv && scale && group_of_col && Q && Err, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(sym || zero, FLH_B200_EINVAL, "asymmetric quantisation needs zero-points");
+    return launch_gptq_block(W, ldw, Hinv, ldh, scale, zero, lds, group_of_col, rows, count, maxq, sym != 0, clip_ratio, Q, ldq, Err,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int flh_b200_gemm_status(int *out) {

@@ -229,6 +229,21 @@ int flh_b200_gemm_i8w_dequant(const uint8_t *A, const uint8_t *B8, const void *a
                               long M, long N, long K, int out_dtype, void *workspace,
                               size_t workspace_bytes, void *stream);
 
+/* One column block of GPTQ's quantise-and-compensate sweep: the inner loop of FLHGPTQ.fasterquant
+ * (flh/nn/gptq.py:198-232) for `count` <= 128 consecutive columns of all `rows` weight rows, in one launch.
+ *   W     f32, rows x ldw   the block's columns as they stand before the sweep (read only)
+ *   Hinv  f32, count x ldh  the block of the upper Cholesky factor of the inverse Hessian (its diagonal block)
+ *   scale / zero  f32, rows x lds; column c of the block uses entry group_of_col[c] (zero may be NULL when sym)
+ *   Q     f32, rows x ldq   the dequantised columns;  Err  f32, rows x count  the errors (w - q) / Hinv[c][c]
+ * For each column c in order:  q = scale * clamp(rint(x / scale), -(maxq + 1), maxq)  (sym; x = w clamped to
+ * +-scale * maxq * clip_ratio when clip_ratio < 1),  or  scale * (clamp(rint(x / scale + zero), 0, maxq) - zero),
+ * err = (w - q) / Hinv[c][c],  and  w_j = w_j - err * Hinv[c][j]  for the columns j > c of the block; binary32
+ * throughout, each product and difference rounded as the reference's torch code rounds them.  The caller applies
+ * W[:, after the block] -= Err @ Hinv[block rows, after the block]  (a plain GEMM) before the next block. */
+int flh_b200_gptq_block(const float *W, long ldw, const float *Hinv, long ldh, const float *scale, const float *zero,
+                        long lds, const int *group_of_col, long rows, int count, int maxq, int sym, float clip_ratio,
+                        float *Q, long ldq, float *Err, void *stream);
+
 /* Which algorithm FLH_B200_GEMM_AUTO resolves to for this shape (one of FLH_B200_GEMM_*). */
 int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group);
 
