@@ -337,6 +337,8 @@ def run_ours(args, world, rank, local, dist):
     elif args.workload in ("gemm_prefill", "gemm_decode"):
         prefill = args.workload == "gemm_prefill"
         M, K, N = (2048, 4096, 12288) if prefill else (16, 4096, 22016)
+        if args.m:
+            M = args.m                                   # e.g. --m 64: a decode batch the tensor-core decode kernel serves
         asym = args.act_mode == "token_asym"          # per-token asymmetric x per-channel weights, else group-128 symmetric
         sets = [gemm_inputs(C, M, N, K, not asym, asym, device, seed=s + 10 * rank) for s in range(3 if not prefill else 1)]
         D = torch.empty((M, N), dtype=torch.float16, device=device)
@@ -673,6 +675,7 @@ def main():
     ap.add_argument("--act-mode", default="group_sym", choices=["group_sym", "token_asym"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count of the llama workloads")
     ap.add_argument("--rows", type=int, default=16384, help="had_quant: token rows per GPU (default: the headline 16384)")
+    ap.add_argument("--m", type=int, default=0, help="gemm_prefill / gemm_decode: token rows M (default 2048 / 16)")
     ap.add_argument("--k", type=int, default=4096, help="had_quant: hidden size K (default: the headline 4096)")
     ap.add_argument("--prepack", action="store_true",
                     help="gemm_prefill / llama*_prefill with token_asym: keep an int8 copy of the weights (expanded once, outside the timed region)")
