@@ -130,8 +130,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
     build_sign_operand(sm, reinterpret_cast<uint32_t *>(sm + aux + 2048), p.sign_bits, p.kfac, p.words, p.P, p.B, R, p.Kdim, p.Mtot,
                        p.bf16 != 0, tid, kThreadsTc);
     if (tid == 0) {
-        for (int s = 0; s < kMaxStages; ++s) { mbar_init(stage_full(s), FUSE ? kEpiWarpsTc : 1); mbar_init(stage_empty(s), 1); }
-        for (int u = 0; u < kSlots; ++u) { mbar_init(slot_full(u), 1); mbar_init(slot_empty(u), 4 * BPU); }
+        // with two accumulator tiles per row (T = 2) each tile has its own MMA issuer thread: both free a stage, both fill a slot
+        for (int s = 0; s < kMaxStages; ++s) { mbar_init(stage_full(s), FUSE ? kEpiWarpsTc : 1); mbar_init(stage_empty(s), T); }
+        for (int u = 0; u < kSlots; ++u) { mbar_init(slot_full(u), T); mbar_init(slot_empty(u), 4 * BPU); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -169,8 +170,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
                 }
             }
             if (PROFILE) atomicAdd(&g_wait_tc[1], w1);
-        } else if (warp == kEpiWarpsTc + 1 && lane == 0) {
-            // ============================================================= MMA issuer
+        } else if (warp > kEpiWarpsTc && warp - kEpiWarpsTc - 1 < T && lane == 0) {
+            // ============================================================= MMA issuers
+            // One tcgen05.mma costs its issuing thread a few hundred cycles whatever its size, and for P > 128 that thread
+            // is the kernel's limit: the two accumulator tiles of a row are independent, so each gets its own issuer.
+            const int ti = warp - kEpiWarpsTc - 1;
             const uint32_t fmt = p.bf16 ? 1u : 0u;
             // D binary32, A / B format, B N-major (bit 16), N = 64 NB, M = 128
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)((64 * NB) >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -187,7 +191,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
                     if (!wait(stage_full(s), (uint32_t)((sc / S) & 1), 32, w2)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t bst = st_base + s * p.stage_bytes;
-                    for (int t = 0; t < T; ++t) {
+                    {
+                        const int t = ti;
                         const uint32_t d = tmem + (uint32_t)((u * BPU + t * NB) * 64);
                         for (int ks = 0; ks < ksteps; ++ks) {
                             const int kg = c * ksteps + ks;            // K step within the whole contraction
@@ -206,7 +211,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
                 }
                 if (ok) tc_commit(slot_full(u));
             }
-            if (PROFILE) { atomicAdd(&g_wait_tc[2], w2); atomicAdd(&g_wait_tc[3], w3); }
+            if (PROFILE && ti == 0) { atomicAdd(&g_wait_tc[2], w2); atomicAdd(&g_wait_tc[3], w3); }
         }
     } else {
         // ================================================================= epilogue
