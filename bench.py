@@ -9,7 +9,10 @@ Workloads (synthetic, seeded; shapes from the reference's benchmark configuratio
                 (bytes = M * (2K + K/2 + 4)).  One step = one launch over one batch.
   norm_quant    fused RMS-norm + per-token asymmetric int4 (the decoder's hidden-state step); --rows / --k.
   gemm_prefill  int4 GEMM + dequant, M = 2048, 4096 -> 12288, group-128 scales; metric = TOPS (2MNK).
-  gemm_decode   int4 GEMM + dequant, M = 16, 4096 -> 22016; metric = GB/s on packed-weight bytes.
+  gemm_decode   int4 GEMM + dequant, M = 16 (--m), 4096 -> 22016; metric = GB/s on packed-weight bytes.
+  grid          every point of the two measurement grids (quantisers: M x K x mode; GEMM: M x layer shape x scale mode)
+                as tables under "extra", each with its fraction of the measured and of the nominal peak.
+  llama7b_prefill | llama7b_decode | llama70b_prefill | llama70b_decode   the Llama-shaped W4A4 decoder (tok/s).
 The default run also measures the other kernels briefly and reports them under "extra".
 
 One JSON line on stdout (rank 0).  Multi-GPU: token batches are independent, so every rank runs
@@ -334,6 +337,10 @@ def run_ours(args, world, rank, local, dist):
                    clocks=cs.summary(), gpu_launches=steps,
                    roofline={"kernel": "quant_group_sym_kernel<7,true>", "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"],
                              "peak_src": peaks["src"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None})
+    elif args.workload == "grid":
+        out.update(grid_tables(C, device, peaks))
+        out.update(metric="grid", unit="see extra", value=0.0, ms_per_step=0.0, dtype="int4 codes", gpu_launches=0,
+                   config={"workload": "the measurement grids of the quantisers (M x K x mode) and of the GEMM (M x shape x scale mode)"})
     elif args.workload in ("gemm_prefill", "gemm_decode"):
         prefill = args.workload == "gemm_prefill"
         M, K, N = (2048, 4096, 12288) if prefill else (16, 4096, 22016)
@@ -546,6 +553,72 @@ def _time(fn, iters=10, warm=3, graph=False):
         e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) * 1e-3 / iters
+
+
+NOMINAL_HBM_GBS, NOMINAL_INT8_TOPS = 7700.0, 4500.0      # data-sheet figures, for the "fraction of nominal" columns
+
+
+def grid_tables(C, device, peaks):
+    """Every point of the two measurement grids: fused transform + quantiser + pack for M in {1, 16, 256, 4096, 16384} x
+    K in {4096, 11008, 14336} x both modes (GB/s on the algorithmic bytes), and the GEMM for M in {1, 8, 32, 512, 2048,
+    8192} x four layer shapes x both scale modes (GB/s on the decode bytes up to 32 rows, TOPS above).  Short launches are
+    timed as CUDA-graph replays; inputs rotate over enough copies to exceed L2 where one copy does not."""
+    hbm, tops = peaks["hbm_gbs"], 2 * peaks["bf16_tflops"]
+    quant, gemm = [], []
+    for k in (4096, 11008, 14336):
+        for m in (1, 16, 256, 4096, 16384):
+            nset = 3 if m * k * 2 > 40_000_000 else 1
+            xs = [synth_activations(m, k, 31 + i, device) for i in range(nset)]
+            it = [0]
+
+            def tok():
+                it[0] += 1
+                C.quant_token_asym_i4(xs[it[0] % nset], hadamard=True)
+
+            def grp():
+                it[0] += 1
+                C.hadamard_and_quantize_i4(xs[it[0] % nset].view(-1, 128))
+
+            for name, fn, sbytes in (("token_asym", tok, 4), ("group128_sym", grp, 2 * k // 128)):
+                t = _time(fn, iters=12, warm=5, graph=True)
+                gbs = m * (2 * k + k // 2 + sbytes) / t / 1e9
+                quant.append({"M": m, "K": k, "mode": name, "us": round(t * 1e6, 2), "GBps": round(gbs, 1),
+                              "frac_measured": round(gbs / hbm, 3), "frac_nominal": round(gbs / NOMINAL_HBM_GBS, 3)})
+            del xs
+    for (k, n) in ((4096, 12288), (4096, 4096), (4096, 22016), (11008, 4096)):
+        for m in (1, 8, 32, 512, 2048, 8192):
+            for grouped, asym, tag in ((True, False, "group128_sym"), (False, True, "token_asym_channel")):
+                base = gemm_inputs(C, m, n, k, grouped, asym, device, seed=3)
+                nset = max(1, -(-320_000_000 // (n * k // 2))) if m <= 32 else 1
+                sets = [base] + [(base[0], base[1].clone()) + base[2:] for _ in range(nset - 1)]
+                D = torch.empty((m, n), dtype=torch.float16, device=device)
+                it = [0]
+
+                def f():
+                    it[0] += 1
+                    A, B, sa, sb, za, rs = sets[it[0] % nset]
+                    C.gemm_i4_dequant(A, B, sa, sb, A_zero=za, B_rowsum=rs, out=D)
+
+                t = _time(f, iters=max(8, nset) if m <= 32 else 5, warm=3, graph=m <= 512)
+                row = {"M": m, "K": k, "N": n, "scales": tag, "us": round(t * 1e6, 2),
+                       "algo": int(_algo(m, n, k, 128 if grouped else k))}
+                if m <= 32:
+                    gc = k // 128 if grouped else 1
+                    b = n * k // 2 + 2 * n * gc + m * k // 2 + 2 * m * n
+                    row.update(GBps=round(b / t / 1e9, 1), frac_measured=round(b / t / 1e9 / hbm, 3), frac_nominal=round(b / t / 1e9 / NOMINAL_HBM_GBS, 3))
+                else:
+                    ops = 2.0 * m * n * k / t / 1e12
+                    row.update(TOPS=round(ops, 1), frac_measured=round(ops / tops, 3), frac_nominal=round(ops / NOMINAL_INT8_TOPS, 3))
+                gemm.append(row)
+                del sets, base
+    return {"extra": {"grid_quant": quant, "grid_gemm": gemm,
+                      "peaks": {"hbm_gbs_measured": hbm, "hbm_gbs_nominal": NOMINAL_HBM_GBS, "int8_tops_2x_measured_bf16": tops,
+                                "int8_tops_nominal": NOMINAL_INT8_TOPS}}}
+
+
+def _algo(m, n, k, group):
+    from flh_b200 import _lib
+    return _lib.load().flh_b200_gemm_pick_algo(m, n, k, group, group)
 
 
 def extras(C, device, peaks):
