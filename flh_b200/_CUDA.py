@@ -215,15 +215,19 @@ def silu_mul(gu):
     return out
 
 
-def silu_mul_quant_token_asym_i4(gu, hadamard: bool = True, clip: float = 1.0, exact: bool = False):
-    """SiLU(gate) * up of gu [M, 2F], then (optionally the full-width transform and) the per-token asymmetric quantiser:
-    one kernel when the tensor-core quantiser takes the width (hadamard=True, exact=False, F = P * 64 with P <= 256), else
-    silu_mul followed by quant_token_asym_i4 — the same result either way.  -> (q u8[M, F/2], scale f16[M], zero f16[M])."""
+def silu_mul_quant_token_asym_i4(gu, hadamard: bool = True, clip: float = 1.0, exact: bool = False, fused: bool = False):
+    """SiLU(gate) * up of gu [M, 2F], then (optionally the full-width transform and) the per-token asymmetric quantiser.
+    -> (q u8[M, F/2], scale f16[M], zero f16[M]).
+
+    Default: silu_mul followed by quant_token_asym_i4 (two launches).  `fused=True` runs the single-kernel form when the
+    tensor-core quantiser takes the width (hadamard=True, exact=False, F = P * 64 with P <= 256): the same bits, but measured
+    SLOWER than the pair at every batch size on B200 (F = 11008: 18.6 vs 11.1 us at 16 rows, 171 vs 113 us at 4096 rows) —
+    its epilogue warps, already the limit of the quantiser, also have to make the SiLU rows — so nothing uses it by default."""
     _check(gu.is_cuda and gu.dtype in (torch.float16, torch.bfloat16), "gu must be a CUDA float16 or bfloat16 tensor")
     _check(gu.dim() == 2 and gu.stride(1) == 1 and gu.shape[1] % 2 == 0, "gu must be [M, 2F] with unit inner stride")
     M, F = gu.shape[0], gu.shape[1] // 2
     lib = _lib.load()
-    if hadamard and not exact and M > 0:
+    if fused and hadamard and not exact and M > 0:
         kfac, bits = _sign_bits(F, gu.device)
         if lib.flh_b200_quant_token_kernel(M, F, 1, kfac) == b"quant_token_tc_kernel":
             q = torch.empty((M, F // 2), dtype=torch.uint8, device=gu.device)

@@ -176,7 +176,8 @@ class DecoderLayer(torch.nn.Module):
             s, z, q = self._norm_quant(self.norm2, self.q_mlp, x)
         gu = self.gate_up(q, s, z)
         if cfg.fuse_glue and cfg.act_mode == "token_asym":
-            # SiLU(gate) * up, the online transform and the quantiser in one kernel (two for widths it does not take)
+            # SiLU(gate) * up, then the online transform and the quantiser (two launches: measured faster than the one-kernel
+            # form, whose epilogue warps would have to make the SiLU rows on top of the quantiser's work)
             with timing.region("quant"):
                 lead = gu.shape[:-1]
                 q, s, z = _CUDA.silu_mul_quant_token_asym_i4(gu.view(-1, gu.shape[-1]), hadamard=self.q_down.use_hadamard,

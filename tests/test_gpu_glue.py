@@ -44,7 +44,7 @@ def test_silu_mul_quant_fused_equals_the_two_steps(cuda, m, f):
     kernel: the entry point then runs the two steps itself."""
     gu = _gate_up(70 + m, m, f)
     gud = torch.from_numpy(gu).cuda()
-    q, s, z = cuda.silu_mul_quant_token_asym_i4(gud, hadamard=True)
+    q, s, z = cuda.silu_mul_quant_token_asym_i4(gud, hadamard=True, fused=True)
     a = cuda.silu_mul(gud)
     q2, s2, z2 = cuda.quant_token_asym_i4(a, hadamard=True)
     assert torch.equal(q, q2) and torch.equal(s, s2) and torch.equal(z, z2)
@@ -59,7 +59,7 @@ def test_silu_mul_quant_bf16_and_clip(cuda):
     gu = _gate_up(91, m, f, bf16=True)
     wide = torch.zeros((m, 2 * f + 64), dtype=torch.bfloat16, device="cuda")
     wide[:, :2 * f] = torch.from_numpy(gu.view(np.int16)).cuda().view(torch.bfloat16)
-    q, s, z = cuda.silu_mul_quant_token_asym_i4(wide[:, :2 * f], hadamard=True, clip=0.9)
+    q, s, z = cuda.silu_mul_quant_token_asym_i4(wide[:, :2 * f], hadamard=True, clip=0.9, fused=True)
     q2, s2, z2 = cuda.quant_token_asym_i4(cuda.silu_mul(wide[:, :2 * f]), hadamard=True, clip=0.9)
     assert torch.equal(q, q2) and torch.equal(s, s2) and torch.equal(z, z2)
     assert_token_tolerance(q, s, z, *O.quant_token_asym(O.silu_mul16(gu, bf16=True), True, clip=0.9, bf16=True))
