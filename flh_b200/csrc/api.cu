@@ -270,8 +270,9 @@ static int pick_stream(long M, long N, long K) {
 int flh_b200_gemm_pick_algo(long M, long N, long K, long a_group, long b_group) {
     if ((a_group < b_group ? a_group : b_group) < 128) return FLH_B200_GEMM_MMA_SYNC;    // K-groups of 32 / 64
     if (M <= 64) return decode_tc_pays(M, N, K, a_group) ? FLH_B200_GEMM_DECODE_TC : pick_stream(M, N, K);
-    // large batches without group scales: expanding both operands to int8 first pays for itself
-    if (a_group == K && b_group == K && M >= 1024)
+    // large batches without group scales: expanding both operands to int8 first pays for itself — from 1,536 rows, or from
+    // 1,024 when the output is wide enough to fill the GPU with 256 x 256 tiles (measured crossovers on B200)
+    if (a_group == K && b_group == K && (M >= 1536 || (M >= 1024 && N >= 8192)))
         return N % 256 == 0 ? FLH_B200_GEMM_TCGEN05_I8_PAIR : FLH_B200_GEMM_TCGEN05_I8;
     return FLH_B200_GEMM_TCGEN05;
 }
