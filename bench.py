@@ -492,14 +492,41 @@ def tp_extras(C, dist, world, rank, device, layers=8):
         model = Decoder(cfg, device, seed=0, group=None, with_head=True)
         if mode == "token_asym":
             model.prepack_int8()
-        ids = torch.randint(100, 200, (4, 2048), device=device)
+        ids = torch.randint(100, 200, (4, 2048), generator=torch.Generator().manual_seed(99)).to(device)   # the same on every rank
+        model.cfg.seq_parallel = False                   # first the all-reduce form (activations replicated on every rank)
         t = timed_loop(lambda i: model(ids), 3, 3, dist, device)
         ex[f"llama70b_{layers}L_prefill_tok_per_s_{mode}"] = 4 * 2048 * 3 / t
         with timing.collect() as tc:
             model(ids)
         ex[f"llama70b_{layers}L_prefill_breakdown_ms_{mode}"] = {k_: round(v, 3) for k_, v in tc.summary().items()}
+        # the same step with the residual stream sharded by tokens (reduce-scatter + all-gather of int4 codes)
+        model.cfg.seq_parallel = True
+        t = timed_loop(lambda i: model(ids), 3, 3, dist, device)
+        ex[f"llama70b_{layers}L_prefill_seqpar_tok_per_s_{mode}"] = 4 * 2048 * 3 / t
+        with timing.collect() as tc:
+            y_sp = model(ids)
+        ex[f"llama70b_{layers}L_prefill_seqpar_breakdown_ms_{mode}"] = {k_: round(v, 3) for k_, v in tc.summary().items()}
+        model.cfg.seq_parallel = False
+        y_ar = model(ids)
+        ex[f"llama70b_{layers}L_prefill_seqpar_vs_allreduce_max_rel_{mode}"] = float(
+            ((y_sp.float() - y_ar.float()).abs().max() / y_ar.float().abs().max()).item())
+        del y_sp, y_ar
+        # the same comparison on ONE layer (the difference before the following layers amplify it: f16 sums in another order)
+        with torch.no_grad():
+            x0 = model.embed(ids)
+            pos = torch.arange(0, 2048, device=device)
+            one_ar = model.layers[0](x0, pos)
+            t_loc = 4 * 2048 // world
+            one_sp = model.layers[0](x0.view(4 * 2048, -1)[rank * t_loc:(rank + 1) * t_loc].contiguous(), pos, shape=(4, 2048))
+            ref = one_ar.view(4 * 2048, -1)[rank * t_loc:(rank + 1) * t_loc]
+            rel = ((one_sp.float() - ref.float()).abs().max() / ref.float().abs().max()).reshape(1)
+            dist.all_reduce(rel, op=dist.ReduceOp.MAX)
+            ex[f"seqpar_vs_allreduce_one_layer_max_rel_{mode}"] = float(rel.item())
+            del x0, one_ar, one_sp
+        model.cfg.seq_parallel = True
         if mode == "token_asym":
-            ex["llama70b_%dL_prefill_tok_per_s" % layers] = ex[f"llama70b_{layers}L_prefill_tok_per_s_{mode}"]
+            ex["llama70b_%dL_prefill_tok_per_s" % layers] = max(ex[f"llama70b_{layers}L_prefill_tok_per_s_{mode}"],
+                                                                ex[f"llama70b_{layers}L_prefill_seqpar_tok_per_s_{mode}"])
             B, ctx = 64, 1024
             cache = model.new_cache(B, ctx + 8)
             for c in cache:

@@ -25,7 +25,7 @@ import torch.nn.functional as F
 
 from . import _CUDA, timing
 from .nn import ActQuantizer, LinearFLH
-from .tp import ColumnParallelLinearFLH, RowParallelLinearFLH
+from .tp import gather_quantised, ColumnParallelLinearFLH, RowParallelLinearFLH
 
 
 @dataclass
@@ -43,6 +43,9 @@ class DecoderConfig:
     fuse_norm: bool = True               # RMS-norm fused into the per-token quantiser where the kernel exists
     fuse_glue: bool = True               # rotary embedding + KV-cache write, and SiLU(gate) * up (+ transform + quantiser), as
                                          # kernels of this library instead of PyTorch tensor operations
+    seq_parallel: bool = True            # tensor-parallel prefill with the residual stream sharded by tokens: row-parallel
+                                         # outputs are reduce-scattered, norm + quantiser run on T / tp rows, and the all-gather
+                                         # carries int4 codes (a quarter of the f16 bytes)
 
     @property
     def head_dim(self):
@@ -126,14 +129,23 @@ class DecoderLayer(torch.nn.Module):
             return s.view(lead + (cfg.hidden // 128,)), None, q.view(lead + (cfg.hidden // 2,))
         return quant(norm(x))
 
-    def forward(self, x, pos, cache=None, tables=None):
-        """x [B, S, hidden] f16; pos [S] absolute positions; cache = (k, v) [B, nkv, T, D] with a write
-        cursor `cache[2]`, or None for a cache-less prefill; tables = rope_tables(pos, ...) shared by the layers."""
+    def forward(self, x, pos, cache=None, tables=None, shape=None):
+        """x [B, S, hidden] f16 (or, sequence-parallel, this rank's [B S / tp, hidden] slice with shape = (B, S)); pos [S]
+        absolute positions; cache = (k, v) [B, nkv, T, D] with a write cursor `cache[2]`, or None for a cache-less prefill;
+        tables = rope_tables(pos, ...) shared by the layers."""
         cfg = self.cfg
-        B, S, _ = x.shape
+        sp = x.dim() == 2                                # sequence-parallel: x is this rank's [T / tp, hidden] slice of the B * S rows
+        if sp:
+            B, S = shape
+        else:
+            B, S, _ = x.shape
         hd = cfg.head_dim
         with timing.region("quant"):
             s, z, q = self._norm_quant(self.norm1, self.q_in, x)
+        if sp:
+            q, s, z = gather_quantised(q, s, z, self.qkv.group)
+            q, s = q.view(B, S, -1), s.view(B, S, -1)
+            z = None if z is None else z.view(B, S, -1)
         qkv = self.qkv(q, s, z)
         with timing.region("glue"):
             mask, causal = None, S > 1
@@ -169,11 +181,13 @@ class DecoderLayer(torch.nn.Module):
             att = att.transpose(1, 2).reshape(B, S, self.nh * hd)
         with timing.region("quant"):
             s, z, q = self.q_attn(att)
-        y = self.o(q, s, z)
+        y = self.o.forward_scatter(q, s, z) if sp else self.o(q, s, z)
         with timing.region("glue"):
             x = x + y
         with timing.region("quant"):
             s, z, q = self._norm_quant(self.norm2, self.q_mlp, x)
+        if sp:
+            q, s, z = gather_quantised(q, s, z, self.gate_up.group)
         gu = self.gate_up(q, s, z)
         if cfg.fuse_glue and cfg.act_mode == "token_asym":
             # SiLU(gate) * up, then the online transform and the quantiser (two launches: measured faster than the one-kernel
@@ -192,7 +206,7 @@ class DecoderLayer(torch.nn.Module):
                     a = F.silu(g) * u
             with timing.region("quant"):
                 s, z, q = self.q_down(a)
-        y = self.down(q, s, z)
+        y = self.down.forward_scatter(q, s, z) if sp else self.down(q, s, z)
         with timing.region("glue"):
             return x + y
 
@@ -205,9 +219,15 @@ class Decoder(torch.nn.Module):
         self.cfg, self.device = cfg, device
         gen = torch.Generator(device=device).manual_seed(seed + (dist.get_rank() if dist.is_initialized() else 0))
         self.embed = torch.nn.Embedding(cfg.vocab, cfg.hidden, device=device, dtype=torch.float16)
+        # replicated parameters are the same on every rank (the shards above differ by rank): the sequence-parallel form
+        # hands rows of the residual stream from rank to rank
+        rep = torch.Generator(device=device).manual_seed(seed + 7919)
+        self.embed.weight.data.copy_(torch.randn(cfg.vocab, cfg.hidden, device=device, generator=rep).half())
         self.layers = torch.nn.ModuleList(DecoderLayer(cfg, device, gen, group) for _ in range(cfg.n_layers))
         self.norm = RMSNorm(cfg.hidden, cfg.eps).to(device)
         self.head = torch.nn.Linear(cfg.hidden, cfg.vocab, bias=False, device=device, dtype=torch.float16) if with_head else None
+        if self.head is not None:
+            self.head.weight.data.copy_((torch.randn(cfg.vocab, cfg.hidden, device=device, generator=rep) * cfg.hidden ** -0.5).half())
 
     def prepack_int8(self):
         """Prefill-heavy serving: every W4 linear with per-channel scales keeps an int8 copy of its weights too."""
@@ -229,9 +249,18 @@ class Decoder(torch.nn.Module):
         x = self.embed(ids)
         pos = torch.arange(start, start + S, device=ids.device)
         tables = rope_tables(pos, self.cfg.head_dim, self.cfg.rope_theta) if self.cfg.fuse_glue else None
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        sp = self.cfg.seq_parallel and self.cfg.tp > 1 and world == self.cfg.tp and S > 1 and (B * S) % world == 0
+        if sp:                                           # this rank's contiguous slice of the B * S token rows
+            t = B * S // world
+            x = x.view(B * S, -1)[dist.get_rank() * t:(dist.get_rank() + 1) * t].contiguous()
         for i, layer in enumerate(self.layers):
             if cache is not None:
                 cache[i][2] = start
-            x = layer(x, pos, None if cache is None else cache[i], tables)
+            x = layer(x, pos, None if cache is None else cache[i], tables, shape=(B, S) if sp else None)
+        if sp:
+            full = torch.empty((B * S, x.shape[-1]), dtype=x.dtype, device=x.device)
+            dist.all_gather_into_tensor(full, x.contiguous())
+            x = full.view(B, S, -1)
         x = self.norm(x)
         return x if self.head is None else self.head(x[:, -1:])

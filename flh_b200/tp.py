@@ -126,3 +126,34 @@ class RowParallelLinearFLH(torch.nn.Module):
             with timing.region("allreduce"):
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         return y
+
+    def forward_scatter(self, x, a_scale=None, a_zero=None, **kw):
+        """Sequence-parallel form: this rank's K-slice of the GEMM over ALL token rows, then a reduce-scatter — rank r
+        receives the summed rows [r T / tp, (r + 1) T / tp) only (half the bytes of the all-reduce; the other half, the
+        all-gather, is done later on the QUANTISED activations, 4x smaller, see gather_quantised)."""
+        M = x.numel() // x.shape[-1]
+        world = dist.get_world_size(self.group)
+        with timing.region("gemm"):
+            y = self.shard(x.reshape(M, -1), a_scale.reshape(M, -1), None if a_zero is None else a_zero.reshape(M, -1), **kw)
+        out = torch.empty((M // world, y.shape[-1]), dtype=y.dtype, device=y.device)
+        with timing.region("allreduce"):
+            dist.reduce_scatter_tensor(out, y, op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+
+def gather_quantised(q, s, z, group=None):
+    """All-gather of quantised token rows (codes u8 [t, K/2], scales [t, g], zero-points [t, g] or None) along the token
+    dimension: [t, ..] on every rank -> [t * tp, ..], rank order.  The int4 codes are a quarter of the f16 activations an
+    all-reduce would have carried."""
+    world = dist.get_world_size(group)
+    outs = []
+    with timing.region("allreduce"):
+        for t in (q, s, z):
+            if t is None:
+                outs.append(None)
+                continue
+            t = t.contiguous()
+            o = torch.empty((t.shape[0] * world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+            dist.all_gather_into_tensor(o, t, group=group)
+            outs.append(o)
+    return outs

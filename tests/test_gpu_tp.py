@@ -52,6 +52,23 @@ def _worker(rank, world, port, tmp):
             if sym:     # group-128 quantisation is unchanged by the K split: only the f16 summation differs
                 rel = (y_row.float() - y_full.float()).abs().max() / y_full.float().abs().max()
                 assert rel < 2e-3, rel
+        # sequence-parallel prefill (residual stream sharded by tokens: reduce-scatter + all-gather of int4 codes) against the
+        # all-reduce form, whole decoder, both activation modes: with two ranks both sums are a + b, so the logits are equal
+        from flh_b200.model import Decoder, DecoderConfig
+        for mode in ("token_asym", "group_sym"):
+            cfg = DecoderConfig(hidden=4096, n_heads=32, n_kv_heads=8, ffn=14336, n_layers=2, vocab=1000, act_mode=mode, tp=world)
+            model = Decoder(cfg, dev, seed=4)
+            ids = torch.randint(10, 900, (2, 96), generator=torch.Generator().manual_seed(1)).to(dev)
+            cfg.seq_parallel = True
+            y_sp = model(ids)
+            cfg.seq_parallel = False
+            y_ar = model(ids)
+            rel = (y_sp.float() - y_ar.float()).abs().max() / y_ar.float().abs().max()
+            assert rel < 1e-3, (mode, float(rel))
+            # a batch whose rows do not divide by the ranks falls back to the all-reduce form
+            cfg.seq_parallel = True
+            odd = model(ids[:, :95][:1])
+            assert odd.shape == (1, 1, 1000)
         if rank == 0:
             open(os.path.join(tmp, "ok"), "w").write("ok")
     finally:

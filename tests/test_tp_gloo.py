@@ -35,6 +35,16 @@ def _oracle_backend():
     return gemm, rowsum
 
 
+def args_full_rows(x, asym, O):
+    """(codes, scales, zero-points) of all rows of x, full width, as the linears take them."""
+    M, K = x.shape
+    if asym:
+        q, s, z = O.quant_token_asym(x, False)
+        return torch.from_numpy(q), torch.from_numpy(s).view(M, 1), torch.from_numpy(z).view(M, 1)
+    q, s = O.quant_group_sym(x.reshape(-1, 128), False)
+    return torch.from_numpy(q.reshape(M, K // 2)), torch.from_numpy(s.reshape(M, K // 128)), None
+
+
 def _worker(rank, world, port, tmp):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -86,6 +96,26 @@ def _worker(rank, world, port, tmp):
             if not asym:    # same quantised activations as the full layer: only the summation order differs
                 err = (y_row.float() - y_full.float()).abs().max() / y_full.float().abs().max()
                 assert err < 2e-3, f"row-parallel vs single device: {err}"
+            # sequence-parallel form: the reduce-scatter hands rank r the summed rows of its token slice — the same bits as
+            # the all-reduced rows — and the all-gather of per-rank quantised rows rebuilds the full quantised batch
+            M2 = 6                                           # rows divisible by the two ranks
+            x2 = torch.randn(M2, K, generator=g).half().numpy()
+            kk = K // world
+            if asym:
+                a2 = tuple(torch.from_numpy(a).view(M2, -1) for a in O.quant_token_asym(np.ascontiguousarray(x2[:, rank * kk:(rank + 1) * kk]), False))
+            else:
+                q2, s2 = O.quant_group_sym(np.ascontiguousarray(x2[:, rank * kk:(rank + 1) * kk]).reshape(-1, 128), False)
+                a2 = (torch.from_numpy(q2.reshape(M2, kk // 2)), torch.from_numpy(s2.reshape(M2, kk // 128)), None)
+            y_all = row(*a2)
+            y_mine = row.forward_scatter(*a2)
+            t = M2 // world
+            assert torch.equal(y_mine.view(torch.int16), y_all[rank * t:(rank + 1) * t].contiguous().view(torch.int16)), "reduce-scatter"
+            from flh_b200.tp import gather_quantised
+            mine = tuple(None if a is None else a[rank * t:(rank + 1) * t].contiguous() for a in args_full_rows(x2, asym, O))
+            whole_rows = args_full_rows(x2, asym, O)
+            got = gather_quantised(*mine)
+            for a, b in zip(got, whole_rows):
+                assert (a is None and b is None) or torch.equal(a, b), "all-gather of quantised rows"
         # row-parallel with the online full-width transform (the down_proj of the per-token mode): every rank rotates
         # its own K / tp activations, so the weight is rotated per block of K / tp = 3584 = 28 * 128; the summed output
         # must approximate the float layer x @ W^T as well as the single-device layer does
