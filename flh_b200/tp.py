@@ -146,14 +146,17 @@ def gather_quantised(q, s, z, group=None):
     dimension: [t, ..] on every rank -> [t * tp, ..], rank order.  The int4 codes are a quarter of the f16 activations an
     all-reduce would have carried."""
     world = dist.get_world_size(group)
-    outs = []
+    outs, works = [], []
     with timing.region("allreduce"):
+        # the three exchanges are issued together and waited for once: the two small ones ride behind the codes
         for t in (q, s, z):
             if t is None:
                 outs.append(None)
                 continue
             t = t.contiguous()
             o = torch.empty((t.shape[0] * world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
-            dist.all_gather_into_tensor(o, t, group=group)
+            works.append(dist.all_gather_into_tensor(o, t, group=group, async_op=True))
             outs.append(o)
+        for w in works:
+            w.wait()
     return outs
