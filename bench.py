@@ -503,6 +503,11 @@ def tp_extras(C, dist, world, rank, device, layers=8):
         model.cfg.seq_parallel = True
         t = timed_loop(lambda i: model(ids), 3, 3, dist, device)
         ex[f"llama70b_{layers}L_prefill_seqpar_tok_per_s_{mode}"] = 4 * 2048 * 3 / t
+        try:        # the same step recorded once into a CUDA graph (collectives included) and replayed: no launch gaps
+            tg = timed_loop(lambda i: model(ids), 3, 3, dist, device, graph=True)
+            ex[f"llama70b_{layers}L_prefill_seqpar_graph_tok_per_s_{mode}"] = 4 * 2048 * 3 / tg
+        except Exception as e:
+            sys.stderr.write(f"prefill graph capture failed ({e})\n")
         with timing.collect() as tc:
             y_sp = model(ids)
         ex[f"llama70b_{layers}L_prefill_seqpar_breakdown_ms_{mode}"] = {k_: round(v, 3) for k_, v in tc.summary().items()}
