@@ -521,9 +521,10 @@ def tp_extras(C, dist, world, rank, device, layers=8):
             x0 = model.embed(ids)
             pos = torch.arange(0, 2048, device=device)
             one_ar = model.layers[0](x0, pos)
-            t_loc = 4 * 2048 // world
-            one_sp = model.layers[0](x0.view(4 * 2048, -1)[rank * t_loc:(rank + 1) * t_loc].contiguous(), pos, shape=(4, 2048))
-            ref = one_ar.view(4 * 2048, -1)[rank * t_loc:(rank + 1) * t_loc]
+            from flh_b200.tp import local_rows
+            nblk = model.cfg.sp_blocks
+            one_sp = model.layers[0](local_rows(x0.view(4 * 2048, -1), rank, world, nblk).contiguous(), pos, shape=(4, 2048, nblk))
+            ref = local_rows(one_ar.view(4 * 2048, -1), rank, world, nblk)
             rel = ((one_sp.float() - ref.float()).abs().max() / ref.float().abs().max()).reshape(1)
             dist.all_reduce(rel, op=dist.ReduceOp.MAX)
             ex[f"seqpar_vs_allreduce_one_layer_max_rel_{mode}"] = float(rel.item())

@@ -25,7 +25,7 @@ import torch.nn.functional as F
 
 from . import _CUDA, timing
 from .nn import ActQuantizer, LinearFLH
-from .tp import gather_quantised, ColumnParallelLinearFLH, RowParallelLinearFLH
+from .tp import ColumnParallelLinearFLH, RowParallelLinearFLH, gather_quantised, gather_rows, local_rows
 
 
 @dataclass
@@ -43,6 +43,9 @@ class DecoderConfig:
     fuse_norm: bool = True               # RMS-norm fused into the per-token quantiser where the kernel exists
     fuse_glue: bool = True               # rotary embedding + KV-cache write, and SiLU(gate) * up (+ transform + quantiser), as
                                          # kernels of this library instead of PyTorch tensor operations
+    sp_blocks: int = 1                   # sequence-parallel: row blocks per row-parallel GEMM; with 2 the reduce-scatter of one block
+                                         # runs beside the GEMM of the next (from 2,048 rows per block).  Measured slower at 8 GPUs
+                                         # (NCCL's kernels take SMs from the GEMM, two exchanges cost two latencies): off
     seq_parallel: bool = True            # tensor-parallel prefill with the residual stream sharded by tokens: row-parallel
                                          # outputs are reduce-scattered, norm + quantiser run on T / tp rows, and the all-gather
                                          # carries int4 codes (a quarter of the f16 bytes)
@@ -130,20 +133,20 @@ class DecoderLayer(torch.nn.Module):
         return quant(norm(x))
 
     def forward(self, x, pos, cache=None, tables=None, shape=None):
-        """x [B, S, hidden] f16 (or, sequence-parallel, this rank's [B S / tp, hidden] slice with shape = (B, S)); pos [S]
+        """x [B, S, hidden] f16 (or, sequence-parallel, this rank's B S / tp rows with shape = (B, S, blocks)); pos [S]
         absolute positions; cache = (k, v) [B, nkv, T, D] with a write cursor `cache[2]`, or None for a cache-less prefill;
         tables = rope_tables(pos, ...) shared by the layers."""
         cfg = self.cfg
-        sp = x.dim() == 2                                # sequence-parallel: x is this rank's [T / tp, hidden] slice of the B * S rows
+        sp = x.dim() == 2                                # sequence-parallel: x holds this rank's T / tp of the B * S rows (tp.local_rows)
         if sp:
-            B, S = shape
+            B, S, blocks = shape
         else:
             B, S, _ = x.shape
         hd = cfg.head_dim
         with timing.region("quant"):
             s, z, q = self._norm_quant(self.norm1, self.q_in, x)
         if sp:
-            q, s, z = gather_quantised(q, s, z, self.qkv.group)
+            q, s, z = gather_quantised(q, s, z, self.qkv.group, blocks)
             q, s = q.view(B, S, -1), s.view(B, S, -1)
             z = None if z is None else z.view(B, S, -1)
         qkv = self.qkv(q, s, z)
@@ -181,13 +184,13 @@ class DecoderLayer(torch.nn.Module):
             att = att.transpose(1, 2).reshape(B, S, self.nh * hd)
         with timing.region("quant"):
             s, z, q = self.q_attn(att)
-        y = self.o.forward_scatter(q, s, z) if sp else self.o(q, s, z)
+        y = self.o.forward_scatter(q, s, z, blocks=blocks) if sp else self.o(q, s, z)
         with timing.region("glue"):
             x = x + y
         with timing.region("quant"):
             s, z, q = self._norm_quant(self.norm2, self.q_mlp, x)
         if sp:
-            q, s, z = gather_quantised(q, s, z, self.gate_up.group)
+            q, s, z = gather_quantised(q, s, z, self.gate_up.group, blocks)
         gu = self.gate_up(q, s, z)
         if cfg.fuse_glue and cfg.act_mode == "token_asym":
             # SiLU(gate) * up, then the online transform and the quantiser (two launches: measured faster than the one-kernel
@@ -206,7 +209,7 @@ class DecoderLayer(torch.nn.Module):
                     a = F.silu(g) * u
             with timing.region("quant"):
                 s, z, q = self.q_down(a)
-        y = self.down.forward_scatter(q, s, z) if sp else self.down(q, s, z)
+        y = self.down.forward_scatter(q, s, z, blocks=blocks) if sp else self.down(q, s, z)
         with timing.region("glue"):
             return x + y
 
@@ -251,16 +254,14 @@ class Decoder(torch.nn.Module):
         tables = rope_tables(pos, self.cfg.head_dim, self.cfg.rope_theta) if self.cfg.fuse_glue else None
         world = dist.get_world_size() if dist.is_initialized() else 1
         sp = self.cfg.seq_parallel and self.cfg.tp > 1 and world == self.cfg.tp and S > 1 and (B * S) % world == 0
-        if sp:                                           # this rank's contiguous slice of the B * S token rows
-            t = B * S // world
-            x = x.view(B * S, -1)[dist.get_rank() * t:(dist.get_rank() + 1) * t].contiguous()
+        if sp:                                           # this rank's rows of the B * S token rows (tp.local_rows)
+            blocks = self.cfg.sp_blocks if (B * S) % (world * self.cfg.sp_blocks) == 0 and B * S // self.cfg.sp_blocks >= 2048 else 1
+            x = local_rows(x.view(B * S, -1), dist.get_rank(), world, blocks).contiguous()
         for i, layer in enumerate(self.layers):
             if cache is not None:
                 cache[i][2] = start
-            x = layer(x, pos, None if cache is None else cache[i], tables, shape=(B, S) if sp else None)
+            x = layer(x, pos, None if cache is None else cache[i], tables, shape=(B, S, blocks) if sp else None)
         if sp:
-            full = torch.empty((B * S, x.shape[-1]), dtype=x.dtype, device=x.device)
-            dist.all_gather_into_tensor(full, x.contiguous())
-            x = full.view(B, S, -1)
+            x = gather_rows(x, None, blocks).view(B, S, -1)
         x = self.norm(x)
         return x if self.head is None else self.head(x[:, -1:])

@@ -127,36 +127,78 @@ class RowParallelLinearFLH(torch.nn.Module):
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         return y
 
-    def forward_scatter(self, x, a_scale=None, a_zero=None, **kw):
-        """Sequence-parallel form: this rank's K-slice of the GEMM over ALL token rows, then a reduce-scatter — rank r
-        receives the summed rows [r T / tp, (r + 1) T / tp) only (half the bytes of the all-reduce; the other half, the
-        all-gather, is done later on the QUANTISED activations, 4x smaller, see gather_quantised)."""
+    def forward_scatter(self, x, a_scale=None, a_zero=None, blocks: int = 1, **kw):
+        """Sequence-parallel form: this rank's K-slice of the GEMM over ALL token rows, then a reduce-scatter — every rank
+        receives only the summed rows it owns (half the bytes of the all-reduce; the other half, the all-gather, is done
+        later on the QUANTISED activations, 4x smaller, see gather_quantised).
+
+        blocks > 1: the rows are cut into `blocks` equal blocks; the reduce-scatter of block b runs on NCCL's stream while the
+        GEMM of block b + 1 runs on the compute stream.  Rank r then owns rows [r T/(tp blocks), (r + 1) T/(tp blocks)) OF
+        EVERY BLOCK (block-cyclic ownership, `local_rows`), and its output holds them block after block."""
         M = x.numel() // x.shape[-1]
         world = dist.get_world_size(self.group)
-        with timing.region("gemm"):
-            y = self.shard(x.reshape(M, -1), a_scale.reshape(M, -1), None if a_zero is None else a_zero.reshape(M, -1), **kw)
-        out = torch.empty((M // world, y.shape[-1]), dtype=y.dtype, device=y.device)
-        with timing.region("allreduce"):
-            dist.reduce_scatter_tensor(out, y, op=dist.ReduceOp.SUM, group=self.group)
+        xs, ss = x.reshape(M, -1), a_scale.reshape(M, -1)
+        zs = None if a_zero is None else a_zero.reshape(M, -1)
+        N = self.shard.out_features
+        out = torch.empty((M // world, N), dtype=kw.get("out_dtype") or self.shard.w_scale.dtype, device=x.device)
+        assert blocks >= 1 and M % (world * blocks) == 0, "rows must divide by ranks x blocks"
+        mb, tb = M // blocks, M // blocks // world
+        y = torch.empty((M, N), dtype=out.dtype, device=x.device)
+        works = []
+        for b in range(blocks):
+            r0, r1 = b * mb, (b + 1) * mb
+            with timing.region("gemm"):
+                self.shard(xs[r0:r1], ss[r0:r1], None if zs is None else zs[r0:r1], out=y[r0:r1], **kw)
+            works.append(dist.reduce_scatter_tensor(out[b * tb:(b + 1) * tb], y[r0:r1], op=dist.ReduceOp.SUM, group=self.group,
+                                                    async_op=True))
+        with timing.region("allreduce"):              # what is left of the exchange after the last GEMM block
+            for w in works:
+                w.wait()
         return out
 
 
-def gather_quantised(q, s, z, group=None):
-    """All-gather of quantised token rows (codes u8 [t, K/2], scales [t, g], zero-points [t, g] or None) along the token
-    dimension: [t, ..] on every rank -> [t * tp, ..], rank order.  The int4 codes are a quarter of the f16 activations an
-    all-reduce would have carried."""
+def local_rows(x, rank: int, world: int, blocks: int = 1):
+    """This rank's rows of x [T, ..] under the ownership forward_scatter(blocks=...) produces: rows
+    [r T/(tp blocks), (r + 1) T/(tp blocks)) of every block, block after block (blocks = 1: one contiguous slice)."""
+    T = x.shape[0]
+    tb = T // blocks // world
+    return x.view(blocks, world, tb, *x.shape[1:])[:, rank].reshape(blocks * tb, *x.shape[1:])
+
+
+def _natural_order(o, world: int, blocks: int):
+    """[rank][block][rows] (what an all-gather of local rows returns) -> [block][rank][rows] = natural row order."""
+    if blocks <= 1:
+        return o
+    tb = o.shape[0] // world // blocks
+    return o.view(world, blocks, tb, *o.shape[1:]).transpose(0, 1).reshape(o.shape)
+
+
+def gather_rows(x, group=None, blocks: int = 1):
+    """All-gather of local rows (see local_rows) back into natural row order."""
     world = dist.get_world_size(group)
-    outs, works = [], []
+    x = x.contiguous()
+    o = torch.empty((x.shape[0] * world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(o, x, group=group)
+    return _natural_order(o, world, blocks)
+
+
+def gather_quantised(q, s, z, group=None, blocks: int = 1):
+    """All-gather of quantised token rows (codes u8 [t, K/2], scales [t, g], zero-points [t, g] or None) along the token
+    dimension: the local rows of every rank -> all T rows in natural order.  The int4 codes are a quarter of the f16
+    activations an all-reduce would have carried; scales and zero-points travel as one tensor."""
+    world = dist.get_world_size(group)
     with timing.region("allreduce"):
-        # the three exchanges are issued together and waited for once: the two small ones ride behind the codes
-        for t in (q, s, z):
-            if t is None:
-                outs.append(None)
-                continue
+        sz = s if z is None else torch.cat((s, z), dim=-1)           # one small exchange instead of two
+        outs, works = [], []
+        for t in (q, sz):
             t = t.contiguous()
             o = torch.empty((t.shape[0] * world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
             works.append(dist.all_gather_into_tensor(o, t, group=group, async_op=True))
             outs.append(o)
         for w in works:
             w.wait()
-    return outs
+        qf, szf = _natural_order(outs[0], world, blocks), _natural_order(outs[1], world, blocks)
+    if z is None:
+        return [qf, szf, None]
+    g = s.shape[-1]
+    return [qf, szf[..., :g].contiguous(), szf[..., g:].contiguous()]

@@ -58,13 +58,15 @@ def _worker(rank, world, port, tmp):
         for mode in ("token_asym", "group_sym"):
             cfg = DecoderConfig(hidden=4096, n_heads=32, n_kv_heads=8, ffn=14336, n_layers=2, vocab=1000, act_mode=mode, tp=world)
             model = Decoder(cfg, dev, seed=4)
+            for shape in ((2, 96), (2, 2048)):               # 4,096 rows: two blocks of 2,048, block-cyclic ownership
+                ids = torch.randint(10, 900, shape, generator=torch.Generator().manual_seed(1)).to(dev)
+                cfg.seq_parallel, cfg.sp_blocks = True, 2 if shape[1] == 2048 else 1
+                y_sp = model(ids)
+                cfg.seq_parallel, cfg.sp_blocks = False, 1
+                y_ar = model(ids)
+                rel = (y_sp.float() - y_ar.float()).abs().max() / y_ar.float().abs().max()
+                assert rel < 1e-3, (mode, shape, float(rel))
             ids = torch.randint(10, 900, (2, 96), generator=torch.Generator().manual_seed(1)).to(dev)
-            cfg.seq_parallel = True
-            y_sp = model(ids)
-            cfg.seq_parallel = False
-            y_ar = model(ids)
-            rel = (y_sp.float() - y_ar.float()).abs().max() / y_ar.float().abs().max()
-            assert rel < 1e-3, (mode, float(rel))
             # a batch whose rows do not divide by the ranks falls back to the all-reduce form
             cfg.seq_parallel = True
             odd = model(ids[:, :95][:1])

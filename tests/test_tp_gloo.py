@@ -27,7 +27,11 @@ def _oracle_backend():
         d = O.gemm_i4_dequant(A.numpy(), B.numpy(), A_scale.numpy(), B_scale.numpy(),
                               a_zero=None if A_zero is None else A_zero.numpy(),
                               bias=None if bias is None else bias.numpy())
-        return torch.from_numpy(d.copy())
+        d = torch.from_numpy(d.copy())
+        if out is not None:
+            out.copy_(d)
+            return out
+        return d
 
     def rowsum(B, group):
         return torch.from_numpy(O.weight_rowsum(B.numpy(), group))
@@ -98,7 +102,7 @@ def _worker(rank, world, port, tmp):
                 assert err < 2e-3, f"row-parallel vs single device: {err}"
             # sequence-parallel form: the reduce-scatter hands rank r the summed rows of its token slice — the same bits as
             # the all-reduced rows — and the all-gather of per-rank quantised rows rebuilds the full quantised batch
-            M2 = 6                                           # rows divisible by the two ranks
+            M2 = 8                                           # rows divisible by ranks x blocks
             x2 = torch.randn(M2, K, generator=g).half().numpy()
             kk = K // world
             if asym:
@@ -107,15 +111,16 @@ def _worker(rank, world, port, tmp):
                 q2, s2 = O.quant_group_sym(np.ascontiguousarray(x2[:, rank * kk:(rank + 1) * kk]).reshape(-1, 128), False)
                 a2 = (torch.from_numpy(q2.reshape(M2, kk // 2)), torch.from_numpy(s2.reshape(M2, kk // 128)), None)
             y_all = row(*a2)
-            y_mine = row.forward_scatter(*a2)
-            t = M2 // world
-            assert torch.equal(y_mine.view(torch.int16), y_all[rank * t:(rank + 1) * t].contiguous().view(torch.int16)), "reduce-scatter"
-            from flh_b200.tp import gather_quantised
-            mine = tuple(None if a is None else a[rank * t:(rank + 1) * t].contiguous() for a in args_full_rows(x2, asym, O))
+            from flh_b200.tp import gather_quantised, gather_rows, local_rows
             whole_rows = args_full_rows(x2, asym, O)
-            got = gather_quantised(*mine)
-            for a, b in zip(got, whole_rows):
-                assert (a is None and b is None) or torch.equal(a, b), "all-gather of quantised rows"
+            for blocks in (1, 2):                            # M2 = 8 rows: 4 or 2 x 2 per rank
+                y_mine = row.forward_scatter(*a2, blocks=blocks)
+                assert torch.equal(y_mine.view(torch.int16), local_rows(y_all, rank, world, blocks).contiguous().view(torch.int16)), "reduce-scatter"
+                assert torch.equal(gather_rows(y_mine, None, blocks).view(torch.int16), y_all.view(torch.int16)), "gather of local rows"
+                mine = tuple(None if a is None else local_rows(a, rank, world, blocks).contiguous() for a in whole_rows)
+                got = gather_quantised(*mine, blocks=blocks)
+                for a, b in zip(got, whole_rows):
+                    assert (a is None and b is None) or torch.equal(a, b), "all-gather of quantised rows"
         # row-parallel with the online full-width transform (the down_proj of the per-token mode): every rank rotates
         # its own K / tp activations, so the weight is rotated per block of K / tp = 3584 = 28 * 128; the summed output
         # must approximate the float layer x @ W^T as well as the single-device layer does
