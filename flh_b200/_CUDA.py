@@ -176,7 +176,7 @@ def quant_token_asym_i4(x, hadamard: bool = True, clip: float = 1.0, exact: bool
     hadamard=True applies the full-width transform of matmul_hadU (flh/functional/hadamard.py:92-113)
     before the per-token asymmetric quantiser of fake_quant/quant_utils.py:94-128.  By default the high part
     of the transform (the kfac x kfac factor and the butterfly bits above 64) is summed by the tensor cores
-    (K = P * 64, P <= 256): same values up to the order of binary32 additions, the same order for every
+    (K = P * 64, P <= 512): same values up to the order of binary32 additions, the same order for every
     batch size.  exact=True keeps the sequential order of the reference (bit-exact with the CPU oracle,
     slower).  out=(q, scale, zero) writes into caller tensors instead of allocating."""
     if exact_factor is not None:        # earlier name of `exact`
@@ -229,7 +229,8 @@ def silu_mul_quant_token_asym_i4(gu, hadamard: bool = True, clip: float = 1.0, e
     lib = _lib.load()
     if fused and hadamard and not exact and M > 0:
         kfac, bits = _sign_bits(F, gu.device)
-        if lib.flh_b200_quant_token_kernel(M, F, 1, kfac) == b"quant_token_tc_kernel":
+        # the fused form makes whole rows in shared memory: widths up to P = 256 only (wider rows are read as two halves)
+        if F // 64 <= 256 and lib.flh_b200_quant_token_kernel(M, F, 1, kfac) == b"quant_token_tc_kernel":
             q = torch.empty((M, F // 2), dtype=torch.uint8, device=gu.device)
             s = torch.empty((M,), dtype=torch.float16, device=gu.device)
             z = torch.empty((M,), dtype=torch.float16, device=gu.device)

@@ -205,7 +205,7 @@ int flh_b200_silu_mul_quant_token_asym_i4(const void *gu, int in_dtype, long M, 
     FLH_REQUIRE(gu && q && scale && zero, FLH_B200_EINVAL, "null pointer");
     FLH_REQUIRE(aligned16(gu) && aligned16(q), FLH_B200_EALIGN, "gu and q must be 16-byte aligned");
     const int rc = launch_silu_mul_quant_token_tc(gu, in_dtype, M, F, ld, kfac, sign_bits, clip, q, scale, zero, static_cast<cudaStream_t>(stream));
-    if (rc == -1000) return fail(FLH_B200_EUNSUPPORTED, "F=%ld is not a width the tensor-core quantiser takes (F = P * 64, P <= 256); run the two steps separately", F);
+    if (rc == -1000) return fail(FLH_B200_EUNSUPPORTED, "F=%ld is not a width the fused form takes (F = P * 64, P <= 256); run the two steps separately", F);
     return rc;
 }
 

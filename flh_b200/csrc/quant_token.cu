@@ -504,7 +504,7 @@ int launch_quant_token_asym(const void *x, int in_dtype, long M, long K, long ld
                             int kfac, const uint32_t *sign_bits, float clip, uint8_t *q,
                             void *scale, void *zero, cudaStream_t stream) {
     if (hadamard == 1) {
-        // default transform: the high part on the tensor cores, for every batch size (K = P * 64, P <= 256)
+        // default transform: the high part on the tensor cores, for every batch size (K = P * 64, P <= 512)
         int rc;
         rc = launch_quant_token_tc(x, in_dtype, M, K, ld, kfac, sign_bits, clip, q, scale, zero, stream);
         if (rc != -1000) return rc;

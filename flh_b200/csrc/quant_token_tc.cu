@@ -17,7 +17,11 @@
 // order does not depend on the batch: every M takes this kernel.
 //
 // Shapes: P <= 64: two rows per MMA (A = diag(G, G), 128 x 128); 64 < P <= 128: one row per MMA (M = 128);
-// 128 < P <= 256: one row on two MMAs (M = 256 as two tiles).  Roles of the persistent CTA: 16 epilogue warps (four
+// 128 < P <= 256: one row on two MMAs (M = 256 as two tiles).  256 < P <= 512 (K = 28672, 32768): G = H_2 (x) G' with G' of
+// order P / 2 <= 256; the row is read as its two halves X_0, X_1 of the top Sylvester bit (a 5-D TMA box picks every other
+// block of chunks), and the accumulator tiles of out_0 = G' X_0 + G' X_1 and out_1 = G' X_0 - G' X_1 are filled by the same
+// instructions with the negate-A bit of the instruction descriptor set for the one minus sign: four tiles per row, the
+// operand in shared memory stays G'.  Roles of the persistent CTA: 16 epilogue warps (four
 // groups of four, one group per 128-lane accumulator tile), one TMA thread, one MMA thread.  Rings: shared-memory stages
 // (TMA -> MMA), 64-column TMEM slots (MMA -> epilogue).  All mbarrier waits are bounded; a wait that runs out sets a status word,
 // the warps keep walking their loops without touching the tensor core so that every named barrier is still reached.
@@ -31,7 +35,7 @@ namespace flh {
 namespace {
 
 constexpr int kEpiWarpsTc = 16;
-constexpr int kThreadsTc = kEpiWarpsTc * 32 + 128;       // + one warpgroup holding the TMA warp and the MMA warp
+constexpr int kThreadsTc = kEpiWarpsTc * 32 + 128;       // + one warpgroup: the TMA thread (warp 16) and up to three MMA issuer threads (warps 17-19)
 constexpr int kSlots = 8;                                // 64-column accumulator slots in TMEM (512 columns)
 constexpr int kMaxStages = 8;
 __device__ int g_status_tc[4];
@@ -46,7 +50,9 @@ struct TcQuantParams {
     int kfac, B;               // P = kfac * B, B a power of two
     int words;                 // 32-bit words per row of the sign-bit table
     const uint32_t *sign_bits; // kfac rows of bits (1 = negative), or null for kfac = 1
-    int R, T;                  // rows per 128-lane accumulator block (2 when P <= 64), tiles per row (2 when P > 128)
+    int R, T;                  // rows per 128-lane accumulator block (2 when P <= 64), tiles of G per row (2 when PG > 128)
+    int H;                     // halves of the top Sylvester bit handled by signed accumulation (2 when P > 256, else 1)
+    int PG, BG;                // order of the operand G (P / H) and its Sylvester part (B / H)
     int NB;                    // 64-column blocks per MMA: N = 64 * NB, i.e. R * NB rows per unit
     int CK, nchunks;           // a stage holds CK rows of the contraction (the K dimension of the MMAs) of every row of the unit;
                                // a unit is nchunks stages (1 when R = 2)
@@ -99,17 +105,20 @@ __device__ __forceinline__ void bfly6_pairs(uint64_t (&p)[32]) {
 }
 
 // PROFILE: time every wait with %globaltimer and add the sums to g_wait_tc (flh_b200_quant_token_wait_profile).
+// HALVES: the two-half form for 256 < P <= 512 (below).
 // FUSE: the rows are not read by TMA but MADE by the epilogue warps — SiLU(gate) * up of the merged gate/up GEMM output
 // (act_common.cuh), written into the stages in the layout TMA would have produced; the unit after the one whose
 // accumulators are being turned into codes is made first, so the tensor core always has a unit to work on.
-template <bool PROFILE, bool FUSE>
+template <bool PROFILE, bool FUSE, bool HALVES>
 __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __grid_constant__ CUtensorMap map_x, const TcQuantParams p) {
     extern __shared__ uint8_t smem_dyn[];
     const uint32_t raw = smem_u32(smem_dyn);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *sm = smem_dyn + (base - raw);
     const int S = p.stages, T = p.T, R = p.R, NB = p.NB;
-    const int BPU = T * NB;                              // 128-lane x 64-column accumulator blocks per unit (1, 2 or 4)
+    constexpr int H = HALVES ? 2 : 1;                    // halves of the top Sylvester bit (HALVES: P > 256)
+    const int TT = T * H;                                // accumulator tiles per row
+    const int BPU = TT * NB;                             // 128-lane x 64-column accumulator blocks per unit (1, 2 or 4)
     const int NU = kSlots / BPU;                         // units whose accumulators fit TMEM
     const int NT = 4 / BPU;                              // epilogue teams (each takes every NT-th unit)
     const uint32_t a_base = base, st_base = base + p.a_bytes;
@@ -127,12 +136,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
     const uint64_t t_start = PROFILE ? gtimer() : 0;
 
     // ---- one-time set-up: A = G (or diag(G, G)) as a K-major operand with the 128-byte swizzle ----
-    build_sign_operand(sm, reinterpret_cast<uint32_t *>(sm + aux + 2048), p.sign_bits, p.kfac, p.words, p.P, p.B, R, p.Kdim, p.Mtot,
+    build_sign_operand(sm, reinterpret_cast<uint32_t *>(sm + aux + 2048), p.sign_bits, p.kfac, p.words, p.PG, p.BG, R, p.Kdim, p.Mtot,
                        p.bf16 != 0, tid, kThreadsTc);
     if (tid == 0) {
-        // with two accumulator tiles per row (T = 2) each tile has its own MMA issuer thread: both free a stage, both fill a slot
-        for (int s = 0; s < kMaxStages; ++s) { mbar_init(stage_full(s), FUSE ? kEpiWarpsTc : 1); mbar_init(stage_empty(s), T); }
-        for (int u = 0; u < kSlots; ++u) { mbar_init(slot_full(u), T); mbar_init(slot_empty(u), 4 * BPU); }
+        // every accumulator tile of a row has its own MMA issuer thread: all of them free a stage, all of them fill a slot
+        for (int s = 0; s < kMaxStages; ++s) { mbar_init(stage_full(s), FUSE ? kEpiWarpsTc : 1); mbar_init(stage_empty(s), TT); }
+        for (int u = 0; u < kSlots; ++u) { mbar_init(slot_full(u), TT); mbar_init(slot_empty(u), 4 * BPU); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -156,75 +165,181 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
     };
 
     if (warp >= kEpiWarpsTc) {
-        if (!FUSE && warp == kEpiWarpsTc && lane == 0) {
-            // ============================================================= TMA producer
-            long it = 0;                                 // stages issued so far
-            unsigned long long w1 = 0;
-            bool ok = true;
-            for (long unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
-                for (int c = 0; c < p.nchunks; ++c, ++it) {
-                    const int s = (int)(it % S);
-                    if (!wait(stage_empty(s), (uint32_t)(((it / S) & 1) ^ 1), 31, w1)) { ok = false; break; }
-                    mbar_expect_tx(stage_full(s), (uint32_t)p.stage_bytes);
-                    tma_load_3d(st_base + s * p.stage_bytes, &map_x, 0, c * p.CK, (int)(unit * R * NB), stage_full(s));
+        if constexpr (!HALVES) {
+            if (!FUSE && warp == kEpiWarpsTc && lane == 0) {
+                // ============================================================= TMA producer
+                long it = 0;                                 // stages issued so far
+                unsigned long long w1 = 0;
+                bool ok = true;
+                for (long unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+                    for (int c = 0; c < p.nchunks; ++c, ++it) {
+                        const int s = (int)(it % S);
+                        if (!wait(stage_empty(s), (uint32_t)(((it / S) & 1) ^ 1), 31, w1)) { ok = false; break; }
+                        mbar_expect_tx(stage_full(s), (uint32_t)p.stage_bytes);
+                        tma_load_3d(st_base + s * p.stage_bytes, &map_x, 0, c * p.CK, (int)(unit * R * NB), stage_full(s));
+                    }
                 }
+                if (PROFILE) atomicAdd(&g_wait_tc[1], w1);
+            } else if (warp > kEpiWarpsTc && warp - kEpiWarpsTc - 1 < T && lane == 0) {
+                // ============================================================= MMA issuers
+                // One tcgen05.mma costs its issuing thread a few hundred cycles whatever its size, and for P > 128 that thread
+                // is the kernel's limit: the two accumulator tiles of a row are independent, so each gets its own issuer.
+                const int ti = warp - kEpiWarpsTc - 1;
+                const uint32_t fmt = p.bf16 ? 1u : 0u;
+                // D binary32, A / B format, B N-major (bit 16), N = 64 NB, M = 128
+                const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)((64 * NB) >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+                const uint32_t nblk = (uint32_t)p.stage_bytes / (uint32_t)NB;          // bytes between the 64-column blocks of B (one block = R rows)
+                const int ksteps = (R == 2 ? p.Kdim : p.CK) >> 4;          // K steps of 16 per stage
+                long it = 0, sc = 0;                                       // units, stages consumed so far
+                unsigned long long w2 = 0, w3 = 0;
+                bool ok = true;
+                for (long unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ++it) {
+                    const int u = (int)(it % NU);
+                    if (!wait(slot_empty(u), (uint32_t)(((it / NU) & 1) ^ 1), 33, w3)) break;
+                    for (int c = 0; c < p.nchunks; ++c, ++sc) {
+                        const int s = (int)(sc % S);
+                        if (!wait(stage_full(s), (uint32_t)((sc / S) & 1), 32, w2)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t bst = st_base + s * p.stage_bytes;
+                        {
+                            const int t = ti;
+                            const uint32_t d = tmem + (uint32_t)((u * BPU + t * NB) * 64);
+                            for (int ks = 0; ks < ksteps; ++ks) {
+                                const int kg = c * ksteps + ks;            // K step within the whole contraction
+                                // A: K-major, 8-row groups 1024 bytes apart; K step of 16 = 32 bytes inside the 128-byte row, next atom after 4
+                                const uint64_t ad = umma_desc_tc(a_base + ((kg >> 2) * (p.Mtot >> 3) + t * 16) * 1024 + (kg & 3) * 32, 16, 1024);
+                                // B: N-major (64 values of j = one 128-byte row per p), 8-row groups 1024 bytes apart (SBO), 16 rows per
+                                // K step; the NB blocks of 64 columns (different token rows) lie nblk bytes apart (LBO)
+                                const uint64_t bd = umma_desc_tc(bst + ks * 2048, nblk, 1024);
+                                const uint32_t acc = kg ? 1u : 0u;
+                                asm volatile("{\n\t.reg .pred pp;\n\tsetp.ne.b32 pp, %4, 0;\n\t"
+                                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pp;\n\t}"
+                                             ::"r"(d), "l"(ad), "l"(bd), "r"(idesc), "r"(acc) : "memory");
+                            }
+                        }
+                        tc_commit(stage_empty(s));
+                    }
+                    if (ok) tc_commit(slot_full(u));
+                }
+                if (PROFILE && ti == 0) { atomicAdd(&g_wait_tc[2], w2); atomicAdd(&g_wait_tc[3], w3); }
             }
-            if (PROFILE) atomicAdd(&g_wait_tc[1], w1);
-        } else if (warp > kEpiWarpsTc && warp - kEpiWarpsTc - 1 < T && lane == 0) {
-            // ============================================================= MMA issuers
-            // One tcgen05.mma costs its issuing thread a few hundred cycles whatever its size, and for P > 128 that thread
-            // is the kernel's limit: the two accumulator tiles of a row are independent, so each gets its own issuer.
-            const int ti = warp - kEpiWarpsTc - 1;
+        } else {
+            // One tcgen05.mma costs its issuing thread a few hundred cycles whatever its size, and for P > 128 that is the kernel's
+            // limit: the accumulator tiles of a row are independent, so each has its own issuer thread — warps 17, 18, 19 for tiles
+            // 0, 1, 2, and the TMA thread of warp 16 for a fourth tile (two halves x two tiles of G).
             const uint32_t fmt = p.bf16 ? 1u : 0u;
-            // D binary32, A / B format, B N-major (bit 16), N = 64 NB, M = 128
+            // D binary32, A / B format, B N-major (bit 16), N = 64 NB, M = 128; bit 13 negates A (the minus sign of out_1 = G' X_0 - G' X_1)
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)((64 * NB) >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
             const uint32_t nblk = (uint32_t)p.stage_bytes / (uint32_t)NB;          // bytes between the 64-column blocks of B (one block = R rows)
             const int ksteps = (R == 2 ? p.Kdim : p.CK) >> 4;          // K steps of 16 per stage
-            long it = 0, sc = 0;                                       // units, stages consumed so far
-            unsigned long long w2 = 0, w3 = 0;
-            bool ok = true;
-            for (long unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ++it) {
-                const int u = (int)(it % NU);
-                if (!wait(slot_empty(u), (uint32_t)(((it / NU) & 1) ^ 1), 33, w3)) break;
-                for (int c = 0; c < p.nchunks; ++c, ++sc) {
-                    const int s = (int)(sc % S);
-                    if (!wait(stage_full(s), (uint32_t)((sc / S) & 1), 32, w2)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t bst = st_base + s * p.stage_bytes;
-                    {
-                        const int t = ti;
-                        const uint32_t d = tmem + (uint32_t)((u * BPU + t * NB) * 64);
-                        for (int ks = 0; ks < ksteps; ++ks) {
-                            const int kg = c * ksteps + ks;            // K step within the whole contraction
-                            // A: K-major, 8-row groups 1024 bytes apart; K step of 16 = 32 bytes inside the 128-byte row, next atom after 4
-                            const uint64_t ad = umma_desc_tc(a_base + ((kg >> 2) * (p.Mtot >> 3) + t * 16) * 1024 + (kg & 3) * 32, 16, 1024);
-                            // B: N-major (64 values of j = one 128-byte row per p), 8-row groups 1024 bytes apart (SBO), 16 rows per
-                            // K step; the NB blocks of 64 columns (different token rows) lie nblk bytes apart (LBO)
-                            const uint64_t bd = umma_desc_tc(bst + ks * 2048, nblk, 1024);
-                            const uint32_t acc = kg ? 1u : 0u;
-                            asm volatile("{\n\t.reg .pred pp;\n\tsetp.ne.b32 pp, %4, 0;\n\t"
-                                         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pp;\n\t}"
-                                         ::"r"(d), "l"(ad), "l"(bd), "r"(idesc), "r"(acc) : "memory");
-                        }
-                    }
-                    tc_commit(stage_empty(s));
+            const int SPU = H * p.nchunks;                             // stages per unit: the chunks of half 0, then of half 1
+            // the K steps of stage s (chunk c of half h) into accumulator tile ti of TMEM slot u
+            auto mma_stage = [&](int ti, int u, int h, int c, int s) {
+                const int t = HALVES ? ti % T : ti, hp = HALVES ? ti / T : 0;                     // tile of G, half h' of the output
+                const uint32_t bst = st_base + s * p.stage_bytes;
+                const uint32_t d = tmem + (uint32_t)((u * BPU + ti * NB) * 64);
+                const uint32_t idv = (hp == 1 && h == 1) ? (idesc | (1u << 13)) : idesc;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    const int kg = c * ksteps + ks;                    // K step within the whole contraction
+                    // A: K-major, 8-row groups 1024 bytes apart; K step of 16 = 32 bytes inside the 128-byte row, next atom after 4
+                    const uint64_t ad = umma_desc_tc(a_base + ((kg >> 2) * (p.Mtot >> 3) + t * 16) * 1024 + (kg & 3) * 32, 16, 1024);
+                    // B: N-major (64 values of j = one 128-byte row per p), 8-row groups 1024 bytes apart (SBO), 16 rows per
+                    // K step; the NB blocks of 64 columns (different token rows) lie nblk bytes apart (LBO)
+                    const uint64_t bd = umma_desc_tc(bst + ks * 2048, nblk, 1024);
+                    const uint32_t acc = (kg | h) ? 1u : 0u;
+                    asm volatile("{\n\t.reg .pred pp;\n\tsetp.ne.b32 pp, %4, 0;\n\t"
+                                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pp;\n\t}"
+                                 ::"r"(d), "l"(ad), "l"(bd), "r"(idv), "r"(acc) : "memory");
                 }
-                if (ok) tc_commit(slot_full(u));
+            };
+            // stage number `ld` of this CTA (unit ld / SPU of its list): the TMA load
+            auto issue_load = [&](long ld) {
+                const long iu = ld / SPU;
+                const int hc = (int)(ld - iu * SPU), h = hc / p.nchunks, c = hc - h * p.nchunks;
+                const long unit = blockIdx.x + iu * gridDim.x;
+                const int s = (int)(ld % S);
+                mbar_expect_tx(stage_full(s), (uint32_t)p.stage_bytes);
+                if (H == 1) {
+                    tma_load_3d(st_base + s * p.stage_bytes, &map_x, 0, c * p.CK, (int)(unit * R * NB), stage_full(s));
+                } else {
+                    // chunk rows [c CK, (c + 1) CK) of half h, in the order of G': (a, b') with b' < BG
+                    const int r0 = c * p.CK;
+                    tma_load_5d(st_base + s * p.stage_bytes, &map_x, 0, p.kfac > 1 ? 0 : r0, h, p.kfac > 1 ? r0 / p.BG : 0,
+                                (int)(unit * R * NB), stage_full(s));
+                }
+            };
+            const long my_units = (long)blockIdx.x < n_units ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            if (!FUSE && warp == kEpiWarpsTc && lane == 0 && TT < 4) {
+                // ============================================================= TMA producer
+                unsigned long long w1 = 0;
+                for (long ld = 0; ld < my_units * SPU; ++ld) {
+                    if (!wait(stage_empty((int)(ld % S)), (uint32_t)(((ld / S) & 1) ^ 1), 31, w1)) break;
+                    issue_load(ld);
+                }
+                if (PROFILE) atomicAdd(&g_wait_tc[1], w1);
+            } else if (!FUSE && warp == kEpiWarpsTc && lane == 0) {
+                // ============================================================= TMA producer that also issues the fourth tile's MMAs:
+                // before it waits for a stage it makes sure that stage is on its way, then issues as many further loads as free
+                // stages allow without waiting
+                unsigned long long w1 = 0, w2 = 0, w3 = 0;
+                const long total = my_units * SPU;
+                long loads = 0;
+                bool ok = true;
+                for (long it = 0; it < my_units && ok; ++it) {
+                    const int u = (int)(it % NU);
+                    if (!wait(slot_empty(u), (uint32_t)(((it / NU) & 1) ^ 1), 33, w3)) break;
+                    for (int hc = 0; hc < SPU; ++hc) {
+                        const long sc = it * SPU + hc;
+                        while (loads <= sc && ok) {
+                            ok = wait(stage_empty((int)(loads % S)), (uint32_t)(((loads / S) & 1) ^ 1), 31, w1);
+                            if (ok) issue_load(loads++);
+                        }
+                        if (!ok) break;
+                        while (loads < total && loads < sc + S && mbar_try(stage_empty((int)(loads % S)), (uint32_t)(((loads / S) & 1) ^ 1))) issue_load(loads++);
+                        const int s = (int)(sc % S);
+                        if (!wait(stage_full(s), (uint32_t)((sc / S) & 1), 32, w2)) { ok = false; break; }
+                        tc_fence_after();
+                        mma_stage(3, u, hc / p.nchunks, hc % p.nchunks, s);
+                        tc_commit(stage_empty(s));
+                    }
+                    if (ok) tc_commit(slot_full(u));
+                }
+                if (PROFILE) atomicAdd(&g_wait_tc[1], w1);
+            } else if (warp > kEpiWarpsTc && warp - kEpiWarpsTc - 1 < TT && lane == 0) {
+                // ============================================================= MMA issuers
+                const int ti = warp - kEpiWarpsTc - 1;
+                unsigned long long w2 = 0, w3 = 0;
+                bool ok = true;
+                for (long it = 0; it < my_units && ok; ++it) {
+                    const int u = (int)(it % NU);
+                    if (!wait(slot_empty(u), (uint32_t)(((it / NU) & 1) ^ 1), 33, w3)) break;
+                    for (int hc = 0; hc < SPU; ++hc) {
+                        const long sc = it * SPU + hc;
+                        const int s = (int)(sc % S);
+                        if (!wait(stage_full(s), (uint32_t)((sc / S) & 1), 32, w2)) { ok = false; break; }
+                        tc_fence_after();
+                        mma_stage(ti, u, hc / p.nchunks, hc % p.nchunks, s);
+                        tc_commit(stage_empty(s));
+                    }
+                    if (ok) tc_commit(slot_full(u));
+                }
+                if (PROFILE && ti == 0) { atomicAdd(&g_wait_tc[2], w2); atomicAdd(&g_wait_tc[3], w3); }
             }
-            if (PROFILE && ti == 0) { atomicAdd(&g_wait_tc[2], w2); atomicAdd(&g_wait_tc[3], w3); }
         }
     } else {
         // ================================================================= epilogue
         const int g = warp >> 2, quarter = warp & 3;
         const int team = g / BPU, b = g - team * BPU;                // this group's block of the unit
-        const int tile = b / NB, nb = b - tile * NB;                 // accumulator tile of the row, 64-column block of the MMA
-        const int wpr = R == 2 ? 2 : 4 * T;                          // warps that share one row
+        const int tile = b / NB, nb = b - tile * NB;                 // accumulator tile of the row (h' T + tile of G), 64-column block of the MMA
+        const int wpr = R == 2 ? 2 : 4 * TT;                         // warps that share one row
         const int m = quarter * 32 + lane;                           // TMEM lane = row of the accumulator tile
         const int riu = R == 2 ? nb * 2 + (m >> 6) : nb;             // row of the unit
-        const int pp = R == 2 ? (m & 63) : tile * 128 + m;           // p' of this thread
+        const int pg = R == 2 ? (m & 63) : (HALVES ? tile % T : tile) * 128 + m;     // row of G this thread holds
+        // its p' in the full transform: with two halves the top Sylvester bit h' sits between the factor index and the rest
+        const int pp = !HALVES ? pg : (pg / p.BG) * (2 * p.BG) + (tile / T) * p.BG + (pg % p.BG);
         const int rslot = R == 2 ? (quarter & 1) : tile * 4 + quarter;   // this warp among the warps of its row
         const int rt = team * R * NB + riu;                          // row in flight: named barrier 1 + rt (at most 8)
-        const bool live = pp < p.P;
+        const bool live = pg < p.PG;
         const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * 64);
         uint8_t *qbase = p.q + pp * 32;
         const long qld = (long)(p.K >> 1);
@@ -327,7 +442,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
             }
             const uint32_t wmin = warp_max_u32(__float_as_uint(fminf(mn0, mn1)) & 0x7fffffffu);
             const uint32_t wmax = warp_max_u32(__float_as_uint(fmaxf(mx0, mx1)) & 0x7fffffffu);
-            uint32_t *rd_ = red + (n & 1) * 128 + rt * 16;
+            uint32_t *rd_ = red + (n & 1) * 128 + rt * (HALVES && wpr > 8 ? 32 : 16);    // sixteen warps per row only with one row in flight
             if (lane == 0) *reinterpret_cast<uint2 *>(rd_ + rslot * 2) = make_uint2(wmin, wmax);
             bar_sync_named(1 + rt, 32 * wpr);
             uint32_t umin, umax;
@@ -341,6 +456,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) quant_token_tc_kernel(const __g
                 if (wpr > 4) {
                     const uint4 e2 = *reinterpret_cast<const uint4 *>(rd_ + 8), e3 = *reinterpret_cast<const uint4 *>(rd_ + 12);
                     umin = max(umin, max(max(e2.x, e2.z), max(e3.x, e3.z))); umax = max(umax, max(max(e2.y, e2.w), max(e3.y, e3.w)));
+                }
+                if (HALVES && wpr > 8) {
+#pragma unroll
+                    for (int e = 16; e < 32; e += 4) {
+                        const uint4 ee = *reinterpret_cast<const uint4 *>(rd_ + e);
+                        umin = max(umin, max(ee.x, ee.z)); umax = max(umax, max(ee.y, ee.w));
+                    }
                 }
             }
             const TokenRowParams rp = token_row_params(__uint_as_float(umin | 0x80000000u), __uint_as_float(umax), p.clip, p.c);
@@ -417,7 +539,10 @@ EncodeTiledFnTc encode_fn_tc() {
 // host thread, so that a serving loop that re-uses its buffers encodes each map once.
 struct MapKey {
     const void *x; long M, ld; int P, boxP, R;          // boxP: contraction rows per TMA box, R: token rows per box
-    bool operator==(const MapKey &o) const { return x == o.x && M == o.M && ld == o.ld && P == o.P && boxP == o.boxP && R == o.R; }
+    int H, BG, kfac;                                    // two-half mode: 5-D map over (j, b', h, a, row)
+    bool operator==(const MapKey &o) const {
+        return x == o.x && M == o.M && ld == o.ld && P == o.P && boxP == o.boxP && R == o.R && H == o.H && BG == o.BG && kfac == o.kfac;
+    }
 };
 struct MapCache { MapKey key[8]; CUtensorMap map[8]; int used = 0, next = 0; };
 
@@ -434,9 +559,22 @@ int get_map(const MapKey &k, CUtensorMap *out) {
     cuuint32_t box[3] = {64u, (cuuint32_t)k.boxP, (cuuint32_t)k.R};
     cuuint32_t estr[3] = {1u, 1u, 1u};
     CUtensorMap m;
-    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(k.x), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r;
+    if (k.H == 1) {
+        r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void *>(k.x), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        // chunk index p = a * (2 BG) + h * BG + b': dimension 1 = b' (128 bytes apart), 2 = h (BG chunks apart), 3 = a (2 BG chunks
+        // apart), 4 = row; a box takes boxP chunks of one half in (a, b') order — whole a-blocks, or part of the only one
+        cuuint64_t d5[5] = {64u, (cuuint64_t)k.BG, 2u, (cuuint64_t)k.kfac, (cuuint64_t)k.M};
+        cuuint64_t s5[4] = {128u, (cuuint64_t)k.BG * 128u, (cuuint64_t)k.BG * 256u, (cuuint64_t)k.ld * 2u};
+        cuuint32_t b5[5] = {64u, (cuuint32_t)(k.kfac > 1 ? k.BG : k.boxP), 1u, (cuuint32_t)(k.kfac > 1 ? k.boxP / k.BG : 1), (cuuint32_t)k.R};
+        cuuint32_t e5[5] = {1u, 1u, 1u, 1u, 1u};
+        r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 5, const_cast<void *>(k.x), d5, s5, b5, e5,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) return fail(FLH_B200_EINVAL, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     const int slot = cache.used < 8 ? cache.used++ : (cache.next++ & 7);
     cache.key[slot] = k;
@@ -447,13 +585,15 @@ int get_map(const MapKey &k, CUtensorMap *out) {
 
 }  // namespace
 
-// Shapes this kernel takes: K = P * 64 with P = kfac * 2^a <= 256.
+// Shapes this kernel takes: K = P * 64 with P = kfac * 2^a <= 512 (above 256 the Sylvester part must be at least 2: the top
+// bit is then handled by signed accumulation of the two halves of the row).
 bool quant_token_tc_takes(long K, int kfac) {
     if (K % 64 != 0 || kfac < 1) return false;
     const long P = K / 64;
-    if (P > 256 || P % kfac != 0) return false;
+    if (P > 512 || P % kfac != 0) return false;
     const long B = P / kfac;
-    return (B & (B - 1)) == 0;
+    if ((B & (B - 1)) != 0) return false;
+    return P <= 256 || (B >= 2 && kfac <= 256);
 }
 
 // Full-width transform + per-token asymmetric int4 for K = P * 64, P = kfac * 2^a <= 256.  x: the rows to quantise, or
@@ -471,9 +611,12 @@ static int launch_tc(const void *x, const void *gu, int in_dtype, long M, long K
     p.M = M; p.K = (int)K; p.P = P; p.kfac = kfac; p.B = B;
     p.words = (kfac + 31) / 32;
     p.sign_bits = kfac > 1 ? sign_bits : nullptr;
-    p.R = P <= 64 ? 2 : 1;
-    p.T = P > 128 ? 2 : 1;
-    const int boxP = p.R == 2 ? 64 : (P + 15) / 16 * 16;
+    p.H = P > 256 ? 2 : 1;
+    if (p.H == 2 && gu) return -1000;                            // the fused form makes whole rows: not written for two halves
+    p.PG = P / p.H; p.BG = B / p.H;
+    p.R = p.PG <= 64 ? 2 : 1;
+    p.T = p.PG > 128 ? 2 : 1;
+    const int boxP = p.R == 2 ? 64 : (p.PG + 15) / 16 * 16;
     p.Kdim = p.R == 2 ? 128 : boxP;
     p.Mtot = 128 * p.T;
     p.a_bytes = ((p.Kdim + 63) / 64) * p.Mtot * 128;
@@ -482,13 +625,20 @@ static int launch_tc(const void *x, const void *gu, int in_dtype, long M, long K
     // for any N); small batches take narrower ones so that the rows spread over more SMs.  A stage holds CK of the Kdim
     // contraction rows of every row of the unit: the largest divisor of Kdim (in steps of 16) of which two stages fit
     // beside A (large stages keep more bytes in flight per barrier round trip than many small ones).
-    int NB = 4 / p.T;
+    int NB = 4 / (p.T * p.H);
+    if (NB < 1) return -1000;
     while (!gu && NB > 1 && (M + (long)p.R * NB - 1) / ((long)p.R * NB) < kNumSMs) NB >>= 1;     // (the fused form works as one team)
-    { const char *e = getenv("FLH_B200_TC_NB"); if (e && !gu) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4) NB = v <= 4 / p.T ? v : NB; } }   // tuning aid
+    { const char *e = getenv("FLH_B200_TC_NB"); if (e && !gu) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4) NB = v <= 4 / (p.T * p.H) ? v : NB; } }   // tuning aid
     int CK = p.R == 2 ? 64 : 16;
     if (p.R == 1) {
-        for (int c = p.Kdim; c >= 16; c -= 16)
-            if (p.Kdim % c == 0 && 2 * NB * c * 128 <= budget) { CK = c; break; }
+        for (int c = p.Kdim; c >= 16; c -= 16) {
+            if (p.Kdim % c != 0 || 2 * NB * c * 128 > budget) continue;
+            // two halves: a TMA box is whole blocks of BG chunks (or a part of the only block) and at most 256 of anything
+            if (p.H == 2 && (kfac > 1 ? (c % p.BG != 0 || c / p.BG > 256) : (p.BG % c != 0 || c > 256))) continue;
+            CK = c;
+            break;
+        }
+        if (p.H == 2 && (kfac > 1 ? CK % p.BG != 0 : p.BG % CK != 0)) return -1000;
     }
     p.NB = NB;
     p.CK = CK;
@@ -509,7 +659,7 @@ static int launch_tc(const void *x, const void *gu, int in_dtype, long M, long K
     CUtensorMap map;
     memset(&map, 0, sizeof(map));
     if (!gu) {
-        MapKey key{x, M, ld, P, CK, p.R * NB};
+        MapKey key{x, M, ld, P, CK, p.R * NB, p.H, p.BG, kfac};
         const int rc = get_map(key, &map);
         if (rc) return rc;
     }
@@ -520,15 +670,17 @@ static int launch_tc(const void *x, const void *gu, int in_dtype, long M, long K
     p.dbg = profile > 1 ? profile >> 1 : 0;                      // FLH_B200_TC_PROFILE=3: profile + accumulators loaded and dropped
     using Kern = void (*)(const CUtensorMap, const TcQuantParams);
     const bool fuse = gu != nullptr;
-    const Kern kern = fuse ? (profile ? quant_token_tc_kernel<true, true> : quant_token_tc_kernel<false, true>)
-                           : (profile ? quant_token_tc_kernel<true, false> : quant_token_tc_kernel<false, false>);
-    static bool attr_done[2][64] = {};
+    const Kern kern = p.H == 2 ? (profile ? quant_token_tc_kernel<true, false, true> : quant_token_tc_kernel<false, false, true>)
+                      : fuse   ? (profile ? quant_token_tc_kernel<true, true, false> : quant_token_tc_kernel<false, true, false>)
+                               : (profile ? quant_token_tc_kernel<true, false, false> : quant_token_tc_kernel<false, false, false>);
+    static bool attr_done[3][64] = {};
+    const int variant = p.H == 2 ? 2 : fuse ? 1 : 0;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
-    if (dev < 0 || !attr_done[fuse][dev]) {
+    if (dev < 0 || !attr_done[variant][dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return cuda_status(e, "quant_token_tc smem attribute");
-        if (dev >= 0) attr_done[fuse][dev] = true;
+        if (dev >= 0) attr_done[variant][dev] = true;
     }
     const long n_units = (M + (long)p.R * NB - 1) / ((long)p.R * NB);
     const long grid = n_units < kNumSMs ? n_units : kNumSMs;

@@ -87,14 +87,15 @@ int flh_b200_hadamard_f16_inplace(void *x, long rows, int n, void *stream);
  * by flh_b200_pack_signs (copied to the device, 16-byte aligned); 1/sqrt(K) is folded into the scale.
  *   hadamard = 2: binary32 butterflies in the order of matmul_hadU (flh/functional/hadamard.py:92-113), the
  *     kfac x kfac factor summed k' ascending: bit-exact with the CPU oracle for every K.
- *   hadamard = 1 (default of the Python layer): for K = P * 64 with P <= 256 (4096, 8192, 11008, 14336, 16384 and the
- *     tensor-parallel shards 7168 / 3584 ...) the part of the transform above the lowest six bits — a P x P matrix of
+ *   hadamard = 1 (default of the Python layer): for K = P * 64 with P <= 512 (4096, 8192, 11008, 14336, 16384, 28672, 32768
+ *     and the tensor-parallel shards 7168 / 3584 ...) the part of the transform above the lowest six bits — a P x P matrix of
  *     +-1 — is applied first, to the raw 16-bit inputs, by tcgen05.mma (products exact, binary32 accumulation in the
  *     tensor core's order); the lowest six bits follow as binary32 butterflies.  Same values up to the order of the
  *     binary32 additions (the reference's own matmul has no fixed order either); measured against the oracle: at most
  *     0.1 % of all codes differ, by one step, scales within one f16 ulp.  Every M takes the same kernel, so a row's
- *     codes do not depend on the batch it arrives in.  Other K (28672, 32768): as hadamard = 2, except that factors of
- *     order >= 64 are summed by mma.sync.
+ *     codes do not depend on the batch it arrives in.  Above P = 256 the row is read as the two halves of its top
+ *     Sylvester bit and the +-1 matrix of order P / 2 is applied to both, added and subtracted in the accumulators.
+ *     Other K: as hadamard = 2, except that factors of order >= 64 are summed by mma.sync.
  * Quantiser: ActQuantizer.find_params / asym_quant (fake_quant/quant_utils.py:94-128, 17-21)
  * with the scale rounded to f16 before use.  q [M, K/2] codes 0..15; scale, zero [M] f16.
  * clip = the quantiser's clip_ratio in (0, 1]. */

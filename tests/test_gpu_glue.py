@@ -40,8 +40,8 @@ def test_silu_mul_bit_exact(cuda, m, f, bf16):
 @pytest.mark.parametrize("m,f", [(1, 11008), (9, 11008), (300, 11008), (2100, 11008), (260, 4096), (70, 14336), (40, 7168), (5, 3584), (3, 28672)])
 def test_silu_mul_quant_fused_equals_the_two_steps(cuda, m, f):
     """One kernel (SiLU * up made in shared memory, transform, quantiser) against the separate kernels, bit for bit; and
-    against the oracle chain within the stated tolerance of the default transform.  F = 28672 is not taken by the fused
-    kernel: the entry point then runs the two steps itself."""
+    against the oracle chain within the stated tolerance of the default transform.  F = 28672 is wider than the fused
+    kernel takes: the entry point then runs the two steps itself."""
     gu = _gate_up(70 + m, m, f)
     gud = torch.from_numpy(gu).cuda()
     q, s, z = cuda.silu_mul_quant_token_asym_i4(gud, hadamard=True, fused=True)

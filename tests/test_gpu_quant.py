@@ -107,7 +107,9 @@ def test_token_asym_hadamard_bit_exact(cuda, m, k):
 # 2560 = 40 * 64, 3072 = 12 * 256 and 3584 = 28 * 128 have a factor with two to eight Sylvester bits beside it
 TC_SHAPES = TOKEN_SHAPES + [(3, 2560), (300, 2560), (700, 3584), (2000, 4096), (1187, 4096), (4, 3072), (1, 4096), (2, 4096), (3, 4096),
                             (4, 4096), (5, 4096), (6, 4096), (7, 4096), (8, 4096), (64, 11008), (33, 14336), (1, 11008), (7, 11008), (301, 11008), (1001, 11008), (1, 14336), (16, 14336),
-                            (256, 14336), (16, 11008), (256, 11008), (256, 4096), (131, 8192), (40, 7168), (9, 3584)]
+                            (256, 14336), (16, 11008), (256, 11008), (256, 4096), (131, 8192), (40, 7168), (9, 3584),
+                            # 256 < P <= 512: the two-half form (28672 = 28 * 1024, 20480 = 20 * 1024, 24576 = 12 * 2048, 32768)
+                            (1, 28672), (70, 28672), (301, 28672), (130, 32768), (3, 20480), (150, 20480), (3, 24576), (149, 24576)]
 
 
 @pytest.mark.parametrize("m,k", TC_SHAPES)
@@ -125,7 +127,7 @@ def test_token_asym_default_transform_tolerance(cuda, m, k):
 def test_token_asym_default_transform_is_batch_independent(cuda):
     """A token row gets the same codes whatever batch it arrives in (the default transform takes one kernel, one
     summation order, for every M)."""
-    for k in (4096, 3584, 11008):
+    for k in (4096, 3584, 11008, 28672):
         x = activations(4300 + k, 300, k)
         xd = _dev(x)
         qa, sa, za = cuda.quant_token_asym_i4(xd, hadamard=True)
@@ -137,7 +139,7 @@ def test_token_asym_default_transform_is_batch_independent(cuda):
 def test_token_asym_default_transform_bf16_strided(cuda):
     """The default transform on bfloat16 input with a padded row stride and a clip ratio (K = 11008, prefill-size batch,
     and K = 4096 with edge rows): same stated tolerance as the binary16 case."""
-    for m, k in ((515, 11008), (300, 4096)):
+    for m, k in ((515, 11008), (300, 4096), (37, 28672)):
         xf = activations(4200 + k, m, k).astype(np.float32)
         xf[5] = 0.0
         xf[6] = np.abs(xf[6])
