@@ -486,6 +486,48 @@ def tp_extras(C, dist, world, rank, device, layers=8):
         else:
             ex["allreduce_1MB_us"] = t * 1e6
         del buf
+    # ---- (2b) the library's one-launch all-reduce over peer-mapped buffers against NCCL at decode message sizes ----
+    from flh_b200 import tp as tpmod
+    one_shot = None
+    try:
+        one_shot = tpmod.enable_one_shot(max_bytes=2 << 20)
+    except Exception as e:
+        ex["allreduce_oneshot_unavailable"] = str(e)[:200]
+    if one_shot is not None:
+        for name, numel in (("16KB", 8192), ("128KB", 8 * 8192), ("1MB", 64 * 8192)):
+            src = (torch.randn(numel, device=device) * (rank + 1)).half()
+            a, b = src.clone(), src.clone()
+            one_shot.reduce(a)
+            dist.all_reduce(b)
+            rel = ((a.float() - b.float()).abs().max() / b.float().abs().max()).reshape(1)
+            dist.all_reduce(rel, op=dist.ReduceOp.MAX)
+            ex[f"allreduce_oneshot_vs_nccl_max_rel_{name}"] = float(rel.item())
+            for kind, fn in (("oneshot", lambda: one_shot.reduce(a)), ("nccl", lambda: dist.all_reduce(b))):
+                t = timed_loop(lambda i: fn(), 50, 5, dist, device)
+                ex[f"allreduce_{kind}_{name}_us"] = t / 50 * 1e6
+                try:
+                    t = timed_loop(lambda i: fn(), 50, 5, dist, device, graph=True)
+                    ex[f"allreduce_{kind}_{name}_graph_us"] = t / 50 * 1e6
+                except Exception as e:
+                    sys.stderr.write(f"all-reduce graph capture failed ({e})\n")
+        # behind a row-parallel linear (decode batch 64, 8192 -> 8192): the result IS the binary32 sum of the f16 partial
+        # outputs in rank order, rounded once — compared bit for bit
+        full = LinearFLH(K, N, dtype=torch.float16, device=device, group_size=-1, in_group_size=128)
+        full.w_packed.copy_(torch.randint(0, 256, full.w_packed.shape, dtype=torch.uint8, generator=g).to(device))
+        full.w_scale.copy_((torch.rand(full.w_scale.shape, generator=g) * 0.015 + 0.005).half().to(device))
+        x = torch.randn(64, K, generator=g).half().to(device)
+        aq = ActQuantizer(bits=4, group_size=-1, sym=False, use_hadamard=False, packed_output=True)
+        kk = K // world
+        acc = torch.zeros(64, N, dtype=torch.float32, device=device)
+        for r in range(world):
+            acc = acc + shard_row(full, r, world)(*_reorder(aq(x[:, r * kk:(r + 1) * kk].contiguous()))).float()
+        y = RowParallelLinearFLH(shard_row(full, rank, world))(*_reorder(aq(x[:, rank * kk:(rank + 1) * kk].contiguous())))
+        same = torch.tensor([1 if torch.equal(y.view(torch.int16), acc.half().view(torch.int16)) else 0], device=device)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        ex["tp_oneshot_row_parallel_equals_binary32_sum"] = bool(same.item())
+        del full, acc
+        ex["allreduce_oneshot_status"] = one_shot.status()
+        tpmod.disable_one_shot()
     # ---- (3) the 70B-shaped decoder, `layers` layers, TP = world: tok/s and where the device time goes ----
     for mode in ("token_asym", "group_sym"):
         cfg = DecoderConfig(**dict(LLAMA3_70B, n_layers=layers), vocab=32000, act_mode=mode, tp=world)
@@ -550,6 +592,31 @@ def tp_extras(C, dist, world, rank, device, layers=8):
             with timing.collect() as tc:
                 fn(0)
             ex[f"llama70b_{layers}L_decode_breakdown_ms_eager"] = {k_: round(v, 3) for k_, v in tc.summary().items()}
+            if one_shot is not None:      # the same step with the 1 MB all-reduces as the library's one-launch form
+                def one_layer():          # logits after ONE layer: the f16 sums differ in order from NCCL's above two ranks, and
+                    saved = model.layers  # eight layers of random weights with int4 activations amplify any last-bit difference
+                    model.layers = saved[:1]
+                    try:
+                        return fn(0).float()
+                    finally:
+                        model.layers = saved
+                ref = one_layer()
+                tpmod.enable_one_shot(max_bytes=2 << 20)
+                got = one_layer()
+                rel = ((got - ref).abs().max() / ref.abs().max()).reshape(1)
+                dist.all_reduce(rel, op=dist.ReduceOp.MAX)
+                ex["decode_oneshot_vs_nccl_one_layer_max_rel"] = float(rel.item())
+                try:
+                    t1 = timed_loop(fn, 10, 3, dist, device, graph=True)
+                except Exception as e:
+                    sys.stderr.write(f"decode graph capture failed ({e}); timing plain launches\n")
+                    t1 = timed_loop(fn, 10, 3, dist, device)
+                ex["llama70b_%dL_decode_oneshot_tok_per_s" % layers] = B * 10 / t1
+                with timing.collect() as tc:
+                    fn(0)
+                ex[f"llama70b_{layers}L_decode_oneshot_breakdown_ms_eager"] = {k_: round(v, 3) for k_, v in tc.summary().items()}
+                ex["allreduce_oneshot_status_after_decode"] = tpmod._ONE_SHOT[None].status()
+                tpmod.disable_one_shot()
             del cache
         del model
         torch.cuda.empty_cache()

@@ -48,6 +48,14 @@ SIGNATURES = {
     "flh_b200_gemm_status": (c_int, [c_void_p]),
     "flh_b200_gemm_wait_profile": (c_int, [c_void_p]),
     "flh_b200_quant_token_wait_profile": (c_int, [c_void_p]),
+    "flh_b200_ar_create": (c_int, [c_int, c_int, c_size_t, c_void_p]),
+    "flh_b200_ar_export": (c_int, [c_void_p, c_void_p]),
+    "flh_b200_ar_import": (c_int, [c_void_p, c_int, c_void_p]),
+    "flh_b200_ar_attach": (c_int, [c_void_p, c_int, c_void_p]),
+    "flh_b200_allreduce": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p]),
+    "flh_b200_allreduce_ranks": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_void_p]),
+    "flh_b200_ar_status": (c_int, [c_void_p, c_void_p]),
+    "flh_b200_ar_destroy": (c_int, [c_void_p]),
     "flhDenseLayerGEMM_i4_o16": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]),
 }
 

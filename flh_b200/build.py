@@ -14,7 +14,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["api.cu", "quant_group.cu", "quant_token.cu", "quant_token_warp.cu", "quant_token_factor.cu", "quant_token_tc.cu", "act.cu", "gemm_mma.cu", "gemm_tcgen05.cu", "gemm_i8.cu", "gemm_decode_tc.cu", "gptq.cu"]
+SOURCES = ["api.cu", "quant_group.cu", "quant_token.cu", "quant_token_warp.cu", "quant_token_factor.cu", "quant_token_tc.cu", "act.cu", "gemm_mma.cu", "gemm_tcgen05.cu", "gemm_i8.cu", "gemm_decode_tc.cu", "gptq.cu", "allreduce.cu"]
 LIB = os.path.join(HERE, "libflh_b200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",

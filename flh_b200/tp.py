@@ -10,14 +10,89 @@ flh/nn/linear.py:20-30) so that a shard is a slice of the single-GPU tensors:
                                     scale / zero-point; a full-width Hadamard becomes block-diagonal per
                                     shard), runs the GEMM and the f16 partial outputs are summed with one
                                     all-reduce — the only collective of the path.
+
+The all-reduce is NCCL's, except for the small messages of decode once `enable_one_shot()` was called: those go
+through the library's own one-launch all-reduce over peer-mapped buffers (include/flh_b200.h: flh_b200_allreduce).
 """
 from __future__ import annotations
 
 import torch
 import torch.distributed as dist
 
-from . import timing
+import ctypes
+
+from . import _lib, timing
 from .nn import LinearFLH
+
+
+class OneShotAllReduce:
+    """The library's one-launch all-reduce (include/flh_b200.h: flh_b200_ar_*) for one process group: each rank
+    allocates its buffer, the 64-byte IPC handles travel through the group's object all-gather, every rank maps the
+    others.  `reduce(y)` sums y (f16 / bf16, contiguous, numel a multiple of 8, at most max_bytes) in place on the
+    current stream; every rank gets the same bits (slots are summed in rank order in binary32)."""
+
+    def __init__(self, group=None, max_bytes: int = 2 << 20, device=None):
+        self.group, self.max_bytes = group, int(max_bytes)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        lib = _lib.load()
+        self._h = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.flh_b200_ar_create(self.world, self.rank, self.max_bytes, ctypes.byref(self._h)), "ar_create")
+            mine = ctypes.create_string_buffer(64)
+            _lib.check(lib.flh_b200_ar_export(self._h, mine), "ar_export")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(mine.raw), group=group)
+            for r, hb in enumerate(handles):
+                if r != self.rank:
+                    _lib.check(lib.flh_b200_ar_import(self._h, r, ctypes.create_string_buffer(hb, 64)), "ar_import")
+        dist.barrier(group=group)          # nobody launches before everybody has mapped everybody
+
+    def takes(self, y) -> bool:
+        return (y.is_cuda and y.dtype in (torch.float16, torch.bfloat16) and y.is_contiguous() and y.numel() % 8 == 0
+                and 0 < y.numel() * 2 <= self.max_bytes and y.data_ptr() % 16 == 0)
+
+    def reduce(self, y):
+        _lib.check(_lib.load().flh_b200_allreduce(self._h, y.data_ptr(), y.data_ptr(), y.numel(),
+                                                  1 if y.dtype == torch.bfloat16 else 0,
+                                                  torch.cuda.current_stream(y.device).cuda_stream), "allreduce")
+        return y
+
+    def status(self):
+        out = (ctypes.c_int * 4)()
+        _lib.check(_lib.load().flh_b200_ar_status(self._h, out), "ar_status")
+        return list(out)
+
+    def close(self):
+        if self._h:
+            dist.barrier(group=self.group)  # no peer still reads or writes this buffer
+            _lib.check(_lib.load().flh_b200_ar_destroy(self._h), "ar_destroy")
+            self._h = ctypes.c_void_p()
+
+
+_ONE_SHOT = {}       # process group -> OneShotAllReduce
+
+
+def enable_one_shot(group=None, max_bytes: int = 2 << 20):
+    """From now on row-parallel linears of `group` sum messages of up to max_bytes with the one-launch all-reduce."""
+    if group not in _ONE_SHOT:
+        _ONE_SHOT[group] = OneShotAllReduce(group, max_bytes)
+    return _ONE_SHOT[group]
+
+
+def disable_one_shot(group=None):
+    ar = _ONE_SHOT.pop(group, None)
+    if ar is not None:
+        ar.close()
+
+
+def all_reduce_sum(y, group=None):
+    """Sum y over the ranks of `group`, in place: the one-launch form for small messages when enabled, else NCCL."""
+    ar = _ONE_SHOT.get(group)
+    if ar is not None and ar.takes(y):
+        return ar.reduce(y)
+    dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
+    return y
 
 
 def _clone_meta(lin: LinearFLH, in_features: int, out_features: int) -> LinearFLH:
@@ -124,7 +199,7 @@ class RowParallelLinearFLH(torch.nn.Module):
             y = self.shard(x, a_scale, a_zero, **kw)
         if multi:
             with timing.region("allreduce"):
-                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+                all_reduce_sum(y, self.group)
         return y
 
     def forward_scatter(self, x, a_scale=None, a_zero=None, blocks: int = 1, **kw):

@@ -289,6 +289,35 @@ int flh_b200_gemm_wait_profile(unsigned long long *out);
  * over warps), out[5] set-up.  Reads and clears; SYNCHRONISES the device.  out: 8 x unsigned long long in HOST memory. */
 int flh_b200_quant_token_wait_profile(unsigned long long *out);
 
+/* One-shot all-reduce (sum) of small f16 / bf16 messages between the GPUs of one node: the partial outputs of a
+ * row-parallel linear in tensor-parallel decode, where an all-reduce costs latency, not bandwidth.  No counterpart in FLH
+ * (it has no multi-GPU code).  One process per GPU (or one process for several), at most 8 ranks.
+ *   flh_b200_ar_create    allocates this rank's buffer on the current device: a control block, arrival flags and two
+ *                         sets of `world` receive slots of max_bytes each (max_bytes a multiple of 16, <= 64 MiB).
+ *   flh_b200_ar_export    writes the 64-byte CUDA IPC handle of that buffer; send it to the other processes.
+ *   flh_b200_ar_import    maps rank `peer`'s buffer from its IPC handle (another process);
+ *   flh_b200_ar_attach    the same for a rank that lives in this process (enables peer access if it is on another device).
+ *   flh_b200_allreduce    out = sum over ranks of x, n elements (a multiple of 8, n * 2 <= max_bytes), x and out 16-byte
+ *                         aligned, out may be x.  One kernel launch on `stream`, no other CUDA call: every rank pushes
+ *                         its message into every peer's slot with plain stores, raises a flag there, waits for the
+ *                         peers' flags and sums the slots in rank order in binary32 — all ranks get the same bits.
+ *                         Every rank must make the same sequence of calls (same n).  May be recorded into a CUDA graph.
+ *                         A wait that lasts 2 s ends with the status word set; the launch still completes.
+ *   flh_b200_allreduce_ranks  all `world` ranks in ONE cooperative launch, for ranks whose buffers live on one device
+ *                         (tests on a single GPU: launches that wait on one another must not share a GPU).
+ *   flh_b200_ar_status    out4 (HOST) = {0 or 1 = a wait ran out, the peer waited for, the CTA, the call number}; synchronises.
+ *   flh_b200_ar_destroy   unmaps the peers and frees the buffer (after all ranks are done with it). */
+typedef struct flh_b200_ar flh_b200_ar;
+int flh_b200_ar_create(int world, int rank, size_t max_bytes, flh_b200_ar **out);
+int flh_b200_ar_export(flh_b200_ar *h, void *ipc64);
+int flh_b200_ar_import(flh_b200_ar *h, int peer, const void *ipc64);
+int flh_b200_ar_attach(flh_b200_ar *h, int peer, flh_b200_ar *other);
+int flh_b200_allreduce(flh_b200_ar *h, const void *x, void *out, long n, int dtype, void *stream);
+int flh_b200_allreduce_ranks(flh_b200_ar *const *hs, int world, const void *const *xs, void *const *outs, long n,
+                             int dtype, void *stream);
+int flh_b200_ar_status(flh_b200_ar *h, int *out4);
+int flh_b200_ar_destroy(flh_b200_ar *h);
+
 /* The reference's one true C symbol, same signature and meaning
  * (flh/kernels/gemm_and_dequant_i4.cu:471-480): group-128 symmetric scales, f16 output,
  * legacy default stream, no status (errors are kept for flh_b200_last_error). */

@@ -71,6 +71,43 @@ def _worker(rank, world, port, tmp):
             cfg.seq_parallel = True
             odd = model(ids[:, :95][:1])
             assert odd.shape == (1, 1, 1000)
+        # the library's one-launch all-reduce over IPC-mapped buffers: same bits on every rank, equal to the binary32 sum in
+        # rank order; eager calls and a CUDA-graph replay (the call number lives on the device); then behind a row-parallel linear
+        from flh_b200 import tp
+        ar = tp.enable_one_shot(max_bytes=1 << 20)
+        gen = torch.Generator().manual_seed(77)
+        for n in (8, 8192, 8 * 777, 64 * 8192):
+            parts = [torch.randn(n, generator=gen).half() for _ in range(world)]
+            ref = parts[0].float()
+            for q in parts[1:]:
+                ref = ref + q.float()
+            y = parts[rank].to(dev)
+            assert ar.takes(y)
+            tp.all_reduce_sum(y)
+            assert torch.equal(y.cpu().view(torch.int16), ref.half().view(torch.int16)), n
+        y = torch.full((8192,), float(rank + 1), dtype=torch.float16, device=dev)
+        buf = y.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                buf.copy_(y)
+                ar.reduce(buf)
+            for _ in range(5):
+                graph.replay()
+        side.synchronize()
+        assert torch.all(buf == float(sum(range(1, world + 1))))
+        assert ar.status()[0] == 0
+        big = torch.ones(2 << 20, dtype=torch.float16, device=dev)           # 4 MiB: over the slot size, goes to NCCL
+        assert not ar.takes(big)
+        tp.all_reduce_sum(big)
+        assert torch.all(big == float(world))
+        y_nccl = row(q2, s2, z2)                                             # 96 x 1024 f16: the one-launch form now
+        tp.disable_one_shot()
+        y_ref = row(q2, s2, z2)
+        rel = (y_nccl.float() - y_ref.float()).abs().max() / y_ref.float().abs().max()
+        assert rel < 1e-3, rel
         if rank == 0:
             open(os.path.join(tmp, "ok"), "w").write("ok")
     finally:
