@@ -592,7 +592,8 @@ def tp_extras(C, dist, world, rank, device, layers=8):
             with timing.collect() as tc:
                 fn(0)
             ex[f"llama70b_{layers}L_decode_breakdown_ms_eager"] = {k_: round(v, 3) for k_, v in tc.summary().items()}
-            if one_shot is not None:      # the same step with the 1 MB all-reduces as the library's one-launch form
+            if one_shot is not None:      # the same step with the 1 MB all-reduces as the library's one-launch form, fused with the
+                                          # residual add, the RMS-norm and the next quantiser (flh_b200_allreduce_add_rmsnorm_quant_token_asym_i4)
                 def one_layer():          # logits after ONE layer: the f16 sums differ in order from NCCL's above two ranks, and
                     saved = model.layers  # eight layers of random weights with int4 activations amplify any last-bit difference
                     model.layers = saved[:1]

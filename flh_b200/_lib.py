@@ -54,6 +54,10 @@ SIGNATURES = {
     "flh_b200_ar_attach": (c_int, [c_void_p, c_int, c_void_p]),
     "flh_b200_allreduce": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p]),
     "flh_b200_allreduce_ranks": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_void_p]),
+    "flh_b200_allreduce_add_rmsnorm_quant_token_asym_i4": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_float, c_float,
+                                                                   c_void_p, c_void_p, c_void_p, c_void_p]),
+    "flh_b200_allreduce_add_rmsnorm_quant_token_asym_i4_ranks": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_long, c_long, c_int, c_float,
+                                                                         c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
     "flh_b200_ar_status": (c_int, [c_void_p, c_void_p]),
     "flh_b200_ar_destroy": (c_int, [c_void_p]),
     "flhDenseLayerGEMM_i4_o16": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t]),

@@ -22,7 +22,7 @@
 #include <stddef.h>
 #include <string.h>
 
-#include "common.cuh"
+#include "token_common.cuh"
 
 struct flh_b200_ar {
     int world, rank, device;
@@ -47,7 +47,9 @@ struct ArCtrl { uint32_t epoch, done; int status[4]; };
 struct ArRank {
     uint8_t *peer[kArMaxWorld];
     const void *x;
-    void *out;
+    void *out;                     // plain all-reduce: the sum; fused form: the residual stream (read, then residual + sum)
+    uint8_t *q;                    // fused form: codes, scales, zero-points of the normalised rows
+    __half *scale, *zero;
     int rank;
 };
 struct ArParams {
@@ -55,6 +57,8 @@ struct ArParams {
     long nvec;                     // 16-byte pieces of the message
     size_t max_bytes;
     int world;
+    int K;                         // fused form: row length (4096 or 8192)
+    float eps, clip;
 };
 
 __device__ __forceinline__ uint32_t *ar_flag(uint8_t *base, int parity, int src, int cta) {
@@ -162,6 +166,163 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArP
         for (int src = 0; src < world; ++src)
             acc8<BF16>(a, src == rank ? x[v] : ld_cg_v4(ar_slot(base, p.max_bytes, world, parity, src) + v));
         out[v] = round8<BF16>(a);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(&ctrl->done, 1u) == gridDim.x - 1) {
+            ctrl->done = 0;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t *>(&ctrl->epoch) = epoch;
+        }
+    }
+}
+
+template <bool BF16> __device__ __forceinline__ float cvt16(uint16_t h) {
+    return BF16 ? __uint_as_float((uint32_t)h << 16) : __half2float(__ushort_as_half(h));
+}
+template <bool BF16> __device__ __forceinline__ uint16_t rnd16(float f) {
+    if (BF16) { const __nv_bfloat16 b = __float2bfloat16_rn(f); return *reinterpret_cast<const uint16_t *>(&b); }
+    return __half_as_ushort(__float2half_rn(f));
+}
+
+// The all-reduce above FUSED with what follows a row-parallel linear in the decoder (modeling_llama.py: o_proj /
+// down_proj -> residual add -> RMS-norm -> per-token asymmetric int4 quantiser of the next linear's input):
+// CTA c owns token row c, so after step 3 it holds the whole row and goes on without another launch:
+//   sum16 = round16(sum of the partial outputs, rank order, binary32);  x = round16(residual + sum16)  -> residual stream
+//   y = round16(x * c),  c = 1 / sqrt(mean(x^2) + eps)   (norm weight 1)                                 -> not stored
+//   scale, zero-point, codes of y as flh_b200_rmsnorm_quant_token_asym_i4 makes them                      -> q, scale, zero
+// Bit for bit the chain all-reduce -> f16 add -> flh_b200_rmsnorm_quant_token_asym_i4: the sum of squares is taken the way
+// that kernel takes it (K / 128 chains of 128 consecutive elements by fma, joined by xor-shuffles 16 .. 1 inside a warp,
+// then warp 0 + warp 1), everything after it is element-wise or a min / max.
+template <bool BF16>
+__global__ void __launch_bounds__(kArThreads) allreduce_norm_quant_kernel(const ArParams p) {
+    __shared__ __align__(16) uint16_t rowbuf[8192];
+    __shared__ float red_sq[2], red_mm[2][kArThreads / 32], bc[3];
+    const ArRank &me = p.r[blockIdx.y];
+    const int rank = me.rank, world = p.world, cta = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint8_t *base = me.peer[rank];
+    ArCtrl *ctrl = reinterpret_cast<ArCtrl *>(base);
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(&ctrl->epoch) + 1;
+    const int parity = (int)(epoch & 1u);
+    const int K = p.K, rv = K / 8;                       // 16-byte pieces per row
+    const long v0 = (long)cta * rv;
+    const uint4 *x = reinterpret_cast<const uint4 *>(me.x);
+
+    for (int i = tid; i < rv; i += kArThreads) {
+        const uint4 val = x[v0 + i];
+        for (int d = 1; d < world; ++d) {
+            const int dst = (rank + d) % world;
+            ar_slot(me.peer[dst], p.max_bytes, world, parity, rank)[v0 + i] = val;
+        }
+    }
+    __syncthreads();
+    if (tid < world && tid != rank) {
+        st_release_sys(ar_flag(me.peer[tid], parity, rank, cta), epoch);
+        const uint32_t *f = ar_flag(base, parity, tid, cta);
+        const unsigned long long t0 = ar_timer();
+        uint32_t spins = 0;
+        while ((int)(ld_relaxed_sys(f) - epoch) < 0) {
+            if ((++spins & 1023u) == 0 && ar_timer() - t0 > kArWaitNs) {
+                if (atomicCAS(&ctrl->status[0], 0, 1) == 0) { ctrl->status[1] = tid; ctrl->status[2] = cta; ctrl->status[3] = (int)epoch; }
+                break;
+            }
+        }
+        (void)ld_acquire_sys(f);
+    }
+    __syncthreads();
+    // the row: sum, residual add, into the residual stream and into shared memory
+    uint4 *res = reinterpret_cast<uint4 *>(me.out);
+    for (int i = tid; i < rv; i += kArThreads) {
+        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int src = 0; src < world; ++src)
+            acc8<BF16>(a, src == rank ? x[v0 + i] : ld_cg_v4(ar_slot(base, p.max_bytes, world, parity, src) + v0 + i));
+        const uint4 s16 = round8<BF16>(a);
+        const uint4 r = res[v0 + i];
+        const uint32_t sw[4] = {s16.x, s16.y, s16.z, s16.w}, rw[4] = {r.x, r.y, r.z, r.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint16_t lo = rnd16<BF16>(__fadd_rn(cvt16<BF16>((uint16_t)rw[k]), cvt16<BF16>((uint16_t)sw[k])));
+            const uint16_t hi = rnd16<BF16>(__fadd_rn(cvt16<BF16>((uint16_t)(rw[k] >> 16)), cvt16<BF16>((uint16_t)(sw[k] >> 16))));
+            o[k] = (uint32_t)lo | ((uint32_t)hi << 16);
+        }
+        const uint4 xn = make_uint4(o[0], o[1], o[2], o[3]);
+        res[v0 + i] = xn;
+        reinterpret_cast<uint4 *>(rowbuf)[i ^ ((i >> 4) & 7)] = xn;      // piece i of chain i / 16, swizzled: the chains' reads below do not collide
+    }
+    __syncthreads();
+    // sum of squares: chain t adds elements [128 t, 128 t + 128) in order
+    const int chains = K / 128;                          // 32 or 64: whole warps
+    if (tid < chains) {
+        float ssq = 0.0f;
+#pragma unroll 4
+        for (int cc = 0; cc < 16; ++cc) {
+            const uint4 w4 = reinterpret_cast<const uint4 *>(rowbuf)[(tid * 16 + cc) ^ (tid & 7)];
+            const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float a = cvt16<BF16>((uint16_t)w[k]), b = cvt16<BF16>((uint16_t)(w[k] >> 16));
+                ssq = __fmaf_rn(a, a, ssq);
+                ssq = __fmaf_rn(b, b, ssq);
+            }
+        }
+#pragma unroll
+        for (int sft = 16; sft > 0; sft >>= 1) ssq = __fadd_rn(ssq, __shfl_xor_sync(0xffffffffu, ssq, sft));
+        if (lane == 0) red_sq[warp] = ssq;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const float ssq = chains == 64 ? __fadd_rn(red_sq[0], red_sq[1]) : red_sq[0];
+        bc[0] = __frcp_rn(__fsqrt_rn(__fadd_rn(__fmul_rn(ssq, 1.0f / (float)K), p.eps)));
+    }
+    __syncthreads();
+    const float c = bc[0];
+    // y = round16(x c) for this thread's elements (at most two pieces of eight), row minimum and maximum
+    float y[16];
+    float vmin = 0.0f, vmax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = tid + j * kArThreads;
+        if (i < rv) {
+            const uint4 w4 = reinterpret_cast<const uint4 *>(rowbuf)[i ^ ((i >> 4) & 7)];
+            const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const uint16_t h = (uint16_t)(w[e >> 1] >> ((e & 1) * 16));
+                const float v = cvt16<BF16>(rnd16<BF16>(__fmul_rn(cvt16<BF16>(h), c)));
+                y[j * 8 + e] = v;
+                vmin = fminf(vmin, v); vmax = fmaxf(vmax, v);
+            }
+        }
+    }
+    vmin = warp_min(vmin); vmax = warp_max(vmax);
+    if (lane == 0) { red_mm[0][warp] = vmin; red_mm[1][warp] = vmax; }
+    __syncthreads();
+    if (tid == 0) {
+        float a = red_mm[0][0], b = red_mm[1][0];
+        for (int w = 1; w < kArThreads / 32; ++w) { a = fminf(a, red_mm[0][w]); b = fmaxf(b, red_mm[1][w]); }
+        bc[1] = a; bc[2] = b;
+    }
+    __syncthreads();
+    const TokenRowParams rp = token_row_params(bc[1], bc[2], p.clip, 1.0f);
+    if (tid == 0) { me.scale[cta] = rp.scale; me.zero[cta] = __float2half_rn(rp.zero); }
+    const float lo = -rp.zero, hi = 15.0f - rp.zero;
+    const int zi = (int)rp.zero;
+    uint32_t *qrow = reinterpret_cast<uint32_t *>(me.q + (long)cta * (K / 2));
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = tid + j * kArThreads;
+        if (i < rv) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int e = 7; e >= 0; --e) {
+                float r = __fmul_rn(y[j * 8 + e], rp.rd);
+                if (rp.clamp) r = fmaxf(fminf(r, hi), lo);
+                w = w * 16u + (uint32_t)((int)rintf(r) + zi);
+            }
+            qrow[i] = w;
+        }
     }
     __syncthreads();
     if (tid == 0) {
@@ -287,6 +448,55 @@ int flh_b200_allreduce_ranks(flh_b200_ar *const *hs, int world, const void *cons
     const void *fn = dtype == FLH_B200_BF16 ? reinterpret_cast<const void *>(allreduce_oneshot_kernel<true>)
                                             : reinterpret_cast<const void *>(allreduce_oneshot_kernel<false>);
     return cuda_status(cudaLaunchCooperativeKernel(fn, grid, dim3(kArThreads), args, 0, static_cast<cudaStream_t>(stream)), "all-reduce launch (all ranks)");
+}
+
+static int ar_fused_check(const flh_b200_ar *h, const void *y, const void *residual, long M, long K, int dtype, float eps, float clip,
+                          const void *q, const void *scale, const void *zero) {
+    FLH_REQUIRE(dtype == FLH_B200_F16 || dtype == FLH_B200_BF16, FLH_B200_EINVAL, "dtype must be F16 or BF16");
+    FLH_REQUIRE(K == 4096 || K == 8192, FLH_B200_EUNSUPPORTED, "the fused form serves K = 4096 and 8192 (got %ld)", K);
+    FLH_REQUIRE(M >= 1 && M <= kArMaxCtas, FLH_B200_EINVAL, "M=%ld: one CTA per token row, at most %d rows", M, kArMaxCtas);
+    FLH_REQUIRE(eps >= 0.0f && clip > 0.0f && clip <= 1.0f, FLH_B200_EINVAL, "eps must be >= 0 and clip in (0, 1]");
+    FLH_REQUIRE(residual && q && scale && zero, FLH_B200_EINVAL, "null pointer");
+    FLH_REQUIRE(aligned16(q), FLH_B200_EALIGN, "q must be 16-byte aligned");
+    return ar_check(h, y, residual, M * K);
+}
+
+int flh_b200_allreduce_add_rmsnorm_quant_token_asym_i4(flh_b200_ar *h, const void *y, void *residual, long M, long K, int dtype,
+                                                       float eps, float clip, uint8_t *q, void *scale, void *zero, void *stream) {
+    if (const int rc = ar_fused_check(h, y, residual, M, K, dtype, eps, clip, q, scale, zero)) return rc;
+    ArParams p;
+    memset(&p, 0, sizeof(p));
+    for (int r = 0; r < h->world; ++r) p.r[0].peer[r] = h->peer[r];
+    p.r[0].x = y; p.r[0].out = residual; p.r[0].q = q; p.r[0].scale = static_cast<__half *>(scale); p.r[0].zero = static_cast<__half *>(zero);
+    p.r[0].rank = h->rank;
+    p.nvec = M * K / 8; p.max_bytes = h->max_bytes; p.world = h->world; p.K = (int)K; p.eps = eps; p.clip = clip;
+    const dim3 grid((unsigned)M, 1);
+    if (dtype == FLH_B200_BF16) allreduce_norm_quant_kernel<true><<<grid, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    else allreduce_norm_quant_kernel<false><<<grid, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return cuda_status(cudaGetLastError(), "fused all-reduce launch");
+}
+
+int flh_b200_allreduce_add_rmsnorm_quant_token_asym_i4_ranks(flh_b200_ar *const *hs, int world, const void *const *ys, void *const *residuals,
+                                                             long M, long K, int dtype, float eps, float clip, uint8_t *const *qs,
+                                                             void *const *scales, void *const *zeros, void *stream) {
+    FLH_REQUIRE(hs && ys && residuals && qs && scales && zeros && world >= 1 && world <= kArMaxWorld, FLH_B200_EINVAL, "bad arguments");
+    FLH_REQUIRE(M * world <= kNumSMs, FLH_B200_EINVAL, "M * world = %ld CTAs must all be resident (at most %d)", M * world, kNumSMs);
+    ArParams p;
+    memset(&p, 0, sizeof(p));
+    for (int r = 0; r < world; ++r) {
+        FLH_REQUIRE(hs[r] && hs[r]->world == world && hs[r]->rank == r && hs[r]->device == hs[0]->device, FLH_B200_EINVAL,
+                    "rank %d: all ranks of a single launch live on one device, in rank order", r);
+        if (const int rc = ar_fused_check(hs[r], ys[r], residuals[r], M, K, dtype, eps, clip, qs[r], scales[r], zeros[r])) return rc;
+        for (int q = 0; q < world; ++q) p.r[r].peer[q] = hs[r]->peer[q];
+        p.r[r].x = ys[r]; p.r[r].out = residuals[r]; p.r[r].q = qs[r];
+        p.r[r].scale = static_cast<__half *>(scales[r]); p.r[r].zero = static_cast<__half *>(zeros[r]); p.r[r].rank = r;
+    }
+    p.nvec = M * K / 8; p.max_bytes = hs[0]->max_bytes; p.world = world; p.K = (int)K; p.eps = eps; p.clip = clip;
+    const dim3 grid((unsigned)M, world);
+    void *args[] = {&p};
+    const void *fn = dtype == FLH_B200_BF16 ? reinterpret_cast<const void *>(allreduce_norm_quant_kernel<true>)
+                                            : reinterpret_cast<const void *>(allreduce_norm_quant_kernel<false>);
+    return cuda_status(cudaLaunchCooperativeKernel(fn, grid, dim3(kArThreads), args, 0, static_cast<cudaStream_t>(stream)), "fused all-reduce launch (all ranks)");
 }
 
 int flh_b200_ar_status(flh_b200_ar *h, int *out4) {

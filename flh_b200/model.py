@@ -132,10 +132,14 @@ class DecoderLayer(torch.nn.Module):
             return s.view(lead + (cfg.hidden // 128,)), None, q.view(lead + (cfg.hidden // 2,))
         return quant(norm(x))
 
-    def forward(self, x, pos, cache=None, tables=None, shape=None):
+    def forward(self, x, pos, cache=None, tables=None, shape=None, pre=None, next_layer=None):
         """x [B, S, hidden] f16 (or, sequence-parallel, this rank's B S / tp rows with shape = (B, S, blocks)); pos [S]
         absolute positions; cache = (k, v) [B, nkv, T, D] with a write cursor `cache[2]`, or None for a cache-less prefill;
-        tables = rope_tables(pos, ...) shared by the layers."""
+        tables = rope_tables(pos, ...) shared by the layers.
+        Tensor-parallel decode with tp.enable_one_shot(): the all-reduce behind o_proj / down_proj, the residual add, the
+        RMS-norm and the quantiser of the next linear's input run as ONE launch, and x is then updated in place.  For
+        down_proj the next linear belongs to `next_layer`: the layer returns (x, pre) and the caller hands `pre` (that
+        layer's quantised input) to it."""
         cfg = self.cfg
         sp = x.dim() == 2                                # sequence-parallel: x holds this rank's T / tp of the B * S rows (tp.local_rows)
         if sp:
@@ -143,8 +147,11 @@ class DecoderLayer(torch.nn.Module):
         else:
             B, S, _ = x.shape
         hd = cfg.head_dim
-        with timing.region("quant"):
-            s, z, q = self._norm_quant(self.norm1, self.q_in, x)
+        if pre is not None:
+            s, z, q = pre
+        else:
+            with timing.region("quant"):
+                s, z, q = self._norm_quant(self.norm1, self.q_in, x)
         if sp:
             q, s, z = gather_quantised(q, s, z, self.qkv.group, blocks)
             q, s = q.view(B, S, -1), s.view(B, S, -1)
@@ -184,11 +191,21 @@ class DecoderLayer(torch.nn.Module):
             att = att.transpose(1, 2).reshape(B, S, self.nh * hd)
         with timing.region("quant"):
             s, z, q = self.q_attn(att)
-        y = self.o.forward_scatter(q, s, z, blocks=blocks) if sp else self.o(q, s, z)
-        with timing.region("glue"):
-            x = x + y
-        with timing.region("quant"):
-            s, z, q = self._norm_quant(self.norm2, self.q_mlp, x)
+        fused = None
+        can_fuse = not sp and cfg.tp > 1 and cfg.fuse_norm and cfg.act_mode == "token_asym" and S == 1 and x.is_contiguous()
+        if can_fuse:
+            # decode: the all-reduce of o_proj, the residual add, the RMS-norm and the quantiser of gate_up's input as ONE launch
+            # (tp.enable_one_shot; returns None when that is off or does not take the shape).  x is updated in place.
+            fused = self.o.forward_add_norm_quant(q, s, z, x, self.norm2.eps, self.q_mlp.input_clip_ratio)
+        if fused is not None:
+            lead = x.shape[:-1]
+            q, s, z = fused[0].view(lead + (cfg.hidden // 2,)), fused[1].view(lead + (1,)), fused[2].view(lead + (1,))
+        else:
+            y = self.o.forward_scatter(q, s, z, blocks=blocks) if sp else self.o(q, s, z)
+            with timing.region("glue"):
+                x = x + y
+            with timing.region("quant"):
+                s, z, q = self._norm_quant(self.norm2, self.q_mlp, x)
         if sp:
             q, s, z = gather_quantised(q, s, z, self.gate_up.group, blocks)
         gu = self.gate_up(q, s, z)
@@ -209,6 +226,11 @@ class DecoderLayer(torch.nn.Module):
                     a = F.silu(g) * u
             with timing.region("quant"):
                 s, z, q = self.q_down(a)
+        if can_fuse and next_layer is not None:
+            fused = self.down.forward_add_norm_quant(q, s, z, x, next_layer.norm1.eps, next_layer.q_in.input_clip_ratio)
+            if fused is not None:
+                lead = x.shape[:-1]
+                return x, (fused[1].view(lead + (1,)), fused[2].view(lead + (1,)), fused[0].view(lead + (cfg.hidden // 2,)))
         y = self.down.forward_scatter(q, s, z, blocks=blocks) if sp else self.down(q, s, z)
         with timing.region("glue"):
             return x + y
@@ -257,10 +279,13 @@ class Decoder(torch.nn.Module):
         if sp:                                           # this rank's rows of the B * S token rows (tp.local_rows)
             blocks = self.cfg.sp_blocks if (B * S) % (world * self.cfg.sp_blocks) == 0 and B * S // self.cfg.sp_blocks >= 2048 else 1
             x = local_rows(x.view(B * S, -1), dist.get_rank(), world, blocks).contiguous()
+        pre = None
         for i, layer in enumerate(self.layers):
             if cache is not None:
                 cache[i][2] = start
-            x = layer(x, pos, None if cache is None else cache[i], tables, shape=(B, S, blocks) if sp else None)
+            out = layer(x, pos, None if cache is None else cache[i], tables, shape=(B, S, blocks) if sp else None, pre=pre,
+                        next_layer=self.layers[i + 1] if i + 1 < len(self.layers) else None)
+            x, pre = out if isinstance(out, tuple) else (out, None)
         if sp:
             x = gather_rows(x, None, blocks).view(B, S, -1)
         x = self.norm(x)

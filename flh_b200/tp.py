@@ -58,6 +58,26 @@ class OneShotAllReduce:
                                                   torch.cuda.current_stream(y.device).cuda_stream), "allreduce")
         return y
 
+    def takes_fused(self, y, residual) -> bool:
+        """The fused form: y, residual [M, K] f16 / bf16 contiguous, K = 4096 or 8192, at most 128 rows."""
+        K = y.shape[-1]
+        return (self.takes(y) and residual.shape == y.shape and residual.dtype == y.dtype and residual.is_contiguous()
+                and residual.data_ptr() % 16 == 0 and K in (4096, 8192) and y.numel() // K <= 128)
+
+    def reduce_add_norm_quant(self, y, residual, eps: float, clip: float = 1.0):
+        """residual += all-reduce(y) (in place), then RMS-norm (weight 1) + per-token asymmetric int4 of the new residual:
+        -> (q u8[M, K/2], scale f16[M], zero f16[M]).  One launch (include/flh_b200.h:
+        flh_b200_allreduce_add_rmsnorm_quant_token_asym_i4)."""
+        K = y.shape[-1]
+        M = y.numel() // K
+        q = torch.empty((M, K // 2), dtype=torch.uint8, device=y.device)
+        s = torch.empty((M,), dtype=torch.float16, device=y.device)
+        z = torch.empty((M,), dtype=torch.float16, device=y.device)
+        _lib.check(_lib.load().flh_b200_allreduce_add_rmsnorm_quant_token_asym_i4(
+            self._h, y.data_ptr(), residual.data_ptr(), M, K, 1 if y.dtype == torch.bfloat16 else 0, float(eps), float(clip),
+            q.data_ptr(), s.data_ptr(), z.data_ptr(), torch.cuda.current_stream(y.device).cuda_stream), "allreduce_add_rmsnorm_quant")
+        return q, s, z
+
     def status(self):
         out = (ctypes.c_int * 4)()
         _lib.check(_lib.load().flh_b200_ar_status(self._h, out), "ar_status")
@@ -201,6 +221,25 @@ class RowParallelLinearFLH(torch.nn.Module):
             with timing.region("allreduce"):
                 all_reduce_sum(y, self.group)
         return y
+
+    def forward_add_norm_quant(self, x, a_scale, a_zero, residual, eps: float, clip: float = 1.0, **kw):
+        """Decode: the GEMM, then ONE launch for the all-reduce, the residual add, the RMS-norm and the per-token quantiser
+        of the next linear's input.  `residual` is updated in place; returns (q, scale, zero), or None — before anything
+        ran — when the one-launch all-reduce is not enabled for this group or does not take the shape (the caller then
+        runs the separate steps)."""
+        ar = _ONE_SHOT.get(self.group)
+        if ar is None or not (dist.is_initialized() and dist.get_world_size(self.group) > 1):
+            return None
+        M, K = x.numel() // x.shape[-1], self.shard.out_features
+        dtype = kw.get("out_dtype") or self.shard.w_scale.dtype
+        if (M > 128 or K not in (4096, 8192) or M * K * 2 > ar.max_bytes or dtype not in (torch.float16, torch.bfloat16)
+                or residual.dtype != dtype or residual.numel() != M * K or not residual.is_contiguous() or residual.data_ptr() % 16):
+            return None
+        with timing.region("gemm"):
+            y = self.shard(x, a_scale, a_zero, **kw)
+        assert ar.takes_fused(y.view(M, K), residual.view(M, K))
+        with timing.region("allreduce"):
+            return ar.reduce_add_norm_quant(y.view(M, K), residual.view(M, K), eps, clip)
 
     def forward_scatter(self, x, a_scale=None, a_zero=None, blocks: int = 1, **kw):
         """Sequence-parallel form: this rank's K-slice of the GEMM over ALL token rows, then a reduce-scatter — every rank

@@ -315,6 +315,19 @@ int flh_b200_ar_attach(flh_b200_ar *h, int peer, flh_b200_ar *other);
 int flh_b200_allreduce(flh_b200_ar *h, const void *x, void *out, long n, int dtype, void *stream);
 int flh_b200_allreduce_ranks(flh_b200_ar *const *hs, int world, const void *const *xs, void *const *outs, long n,
                              int dtype, void *stream);
+/* The same all-reduce FUSED with what follows a row-parallel linear in the decoder (o_proj / down_proj -> residual add ->
+ * RMS-norm -> the per-token asymmetric int4 quantiser in front of the next linear; modeling_llama.py decoder layer), one launch,
+ * one CTA per token row (M <= 128, K = 4096 or 8192, M * K * 2 <= max_bytes):
+ *   residual <- round16(residual + round16(sum over ranks of y))          y, residual: [M, K] f16 / bf16, contiguous
+ *   q, scale, zero <- flh_b200_rmsnorm_quant_token_asym_i4(residual, eps, hadamard = 0, clip)      (norm weight 1)
+ * Bit for bit what flh_b200_allreduce, an f16 add and flh_b200_rmsnorm_quant_token_asym_i4 give as three launches.
+ * _ranks: all ranks in one cooperative launch on one device (M * world <= 148), for tests on a single GPU. */
+int flh_b200_allreduce_add_rmsnorm_quant_token_asym_i4(flh_b200_ar *h, const void *y, void *residual, long M, long K, int dtype,
+                                                       float eps, float clip, uint8_t *q, void *scale, void *zero, void *stream);
+int flh_b200_allreduce_add_rmsnorm_quant_token_asym_i4_ranks(flh_b200_ar *const *hs, int world, const void *const *ys,
+                                                             void *const *residuals, long M, long K, int dtype, float eps,
+                                                             float clip, uint8_t *const *qs, void *const *scales,
+                                                             void *const *zeros, void *stream);
 int flh_b200_ar_status(flh_b200_ar *h, int *out4);
 int flh_b200_ar_destroy(flh_b200_ar *h);
 

@@ -105,3 +105,40 @@ def test_wait_runs_out_when_a_peer_never_arrives(cuda):
         assert float((x + 1).sum().item()) >= 0.0                          # the context still runs kernels
     finally:
         ranks.close()
+
+
+@pytest.mark.parametrize("world,M,K", [(2, 64, 8192), (4, 32, 8192), (8, 16, 8192), (8, 1, 8192), (2, 5, 4096), (8, 18, 4096)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fused_add_norm_quant_equals_the_three_steps(cuda, world, M, K, dtype):
+    """All-reduce + residual add + RMS-norm + per-token quantiser as one launch against all-reduce (binary32 sum in rank
+    order, rounded once), a 16-bit add and flh_b200_rmsnorm_quant_token_asym_i4: residual stream, codes, scales and
+    zero-points bit for bit, on every rank; two calls in a row (the second sees the first's residual)."""
+    ranks = _Ranks(world, 1 << 20)
+    try:
+        g = torch.Generator(device="cuda").manual_seed(7 * world + M)
+        arr = ctypes.c_void_p * world
+        res = [(torch.randn(M, K, device="cuda", generator=g) * 0.5).to(dtype)] * world
+        res = [r.clone() for r in res]                       # the residual stream is replicated
+        for call in range(2):
+            ys = [(torch.randn(M, K, device="cuda", generator=g) * (0.3 + 0.1 * r)).to(dtype) for r in range(world)]
+            if call == 1:
+                ys[0][0].zero_()                             # a row whose partial outputs vanish on one rank
+            want_res = (res[0].float() + _reference(ys).float()).to(dtype)
+            want_q, want_s, want_z = cuda.rmsnorm_quant_token_asym_i4(want_res, 1e-5, hadamard=False)
+            qs = [torch.empty(M, K // 2, dtype=torch.uint8, device="cuda") for _ in range(world)]
+            ss = [torch.empty(M, dtype=torch.float16, device="cuda") for _ in range(world)]
+            zs = [torch.empty(M, dtype=torch.float16, device="cuda") for _ in range(world)]
+            ranks.check(ranks.lib.flh_b200_allreduce_add_rmsnorm_quant_token_asym_i4_ranks(
+                arr(*[h.value for h in ranks.hs]), world, arr(*[y.data_ptr() for y in ys]), arr(*[r.data_ptr() for r in res]),
+                M, K, 1 if dtype == torch.bfloat16 else 0, 1e-5, 1.0, arr(*[q.data_ptr() for q in qs]),
+                arr(*[s.data_ptr() for s in ss]), arr(*[z.data_ptr() for z in zs]), torch.cuda.current_stream().cuda_stream),
+                "fused all-reduce")
+            torch.cuda.synchronize()
+            for r in range(world):
+                assert torch.equal(res[r].view(torch.int16), want_res.view(torch.int16)), (call, r, "residual")
+                assert torch.equal(ss[r].view(torch.int16), want_s.view(torch.int16)), (call, r, "scale")
+                assert torch.equal(zs[r].view(torch.int16), want_z.view(torch.int16)), (call, r, "zero")
+                assert torch.equal(qs[r], want_q), (call, r, "codes")
+        assert all(s[0] == 0 for s in ranks.status())
+    finally:
+        ranks.close()

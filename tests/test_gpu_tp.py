@@ -108,6 +108,23 @@ def _worker(rank, world, port, tmp):
         y_ref = row(q2, s2, z2)
         rel = (y_nccl.float() - y_ref.float()).abs().max() / y_ref.float().abs().max()
         assert rel < 1e-3, rel
+        # decode through the decoder: with the one-launch form on, both all-reduces of a layer run fused with the residual add,
+        # the RMS-norm and the next quantiser — same logits bit for bit (two ranks: every sum is a + b)
+        cfg = DecoderConfig(hidden=4096, n_heads=32, n_kv_heads=8, ffn=14336, n_layers=3, vocab=1000, act_mode="token_asym", tp=world)
+        model = Decoder(cfg, dev, seed=4)
+        ids = torch.randint(10, 900, (5, 1), generator=torch.Generator().manual_seed(3)).to(dev)
+        logits = []
+        for fused in (False, True):
+            cache = model.new_cache(5, 40)
+            for c in cache:
+                c[0].copy_(torch.randn(c[0].shape, generator=torch.Generator().manual_seed(8)).half())
+                c[1].copy_(torch.randn(c[1].shape, generator=torch.Generator().manual_seed(9)).half())
+            if fused:
+                tp.enable_one_shot(max_bytes=1 << 20)
+            logits.append(model(ids, cache=cache, start=32))
+        assert tp._ONE_SHOT[None].status()[0] == 0
+        tp.disable_one_shot()
+        assert torch.equal(logits[0].view(torch.int16), logits[1].view(torch.int16)), "fused decode"
         if rank == 0:
             open(os.path.join(tmp, "ok"), "w").write("ok")
     finally:
