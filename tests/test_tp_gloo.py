@@ -143,6 +143,16 @@ def _worker(rank, world, port, tmp):
         err_whole = (y_whole.float() - ref).norm() / ref.norm()
         err_row = (y_row.float() - ref).norm() / ref.norm()
         assert err_whole < 0.3 and err_row < 1.5 * err_whole + 0.02, (err_row, err_whole)
+        # without tp.enable_one_shot() (no CUDA device here) the row-parallel layer stays on the process group's all-reduce:
+        # the fused decode form declines before running anything, all_reduce_sum is the group's sum
+        from flh_b200 import tp
+        assert tp._ONE_SHOT == {}
+        res = torch.zeros(M, N).half()
+        assert row.forward_add_norm_quant(torch.from_numpy(qm), torch.from_numpy(sm).view(M, 1), torch.from_numpy(zm).view(M, 1), res, 1e-5) is None
+        assert float(res.abs().max()) == 0.0
+        t = torch.full((16,), float(rank + 1))
+        tp.all_reduce_sum(t)
+        assert torch.all(t == float(sum(range(1, world + 1))))
         if rank == 0:
             open(os.path.join(tmp, "ok"), "w").write("ok")
     finally:
