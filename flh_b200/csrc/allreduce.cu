@@ -120,20 +120,12 @@ template <bool BF16> __device__ __forceinline__ uint4 round8(const float (&a)[8]
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-template <bool BF16>
-__global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArParams p) {
-    const ArRank &me = p.r[blockIdx.y];
-    const int rank = me.rank, world = p.world, cta = blockIdx.x, tid = threadIdx.x;
+// Steps 1-3 for the pieces [v0, v1) of CTA `cta`: push them into every peer's slot of this rank, raise the flags, wait for the
+// peers' flags (bounded).  Ends with a CTA barrier: after it the local slots of all ranks hold the pieces.
+__device__ __forceinline__ void ar_exchange(const ArParams &p, const ArRank &me, ArCtrl *ctrl, uint32_t epoch, long v0, long v1, int cta) {
+    const int rank = me.rank, world = p.world, tid = threadIdx.x, parity = (int)(epoch & 1u);
     uint8_t *base = me.peer[rank];
-    ArCtrl *ctrl = reinterpret_cast<ArCtrl *>(base);
-    // every CTA reads the counter before the last one advances it (that one first sees all the others done)
-    const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(&ctrl->epoch) + 1;
-    const int parity = (int)(epoch & 1u);
-    const long per = (p.nvec + gridDim.x - 1) / gridDim.x;
-    const long v0 = (long)cta * per, v1 = v0 + per < p.nvec ? v0 + per : p.nvec;
     const uint4 *x = reinterpret_cast<const uint4 *>(me.x);
-
-    // 1. push this rank's piece into every peer
     for (long v = v0 + tid; v < v1; v += kArThreads) {
         const uint4 val = x[v];
         for (int i = 1; i < world; ++i) {
@@ -142,8 +134,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArP
         }
     }
     __syncthreads();
-    // 2. signal, 3. wait: thread t handles peer t
-    if (tid < world && tid != rank) {
+    if (tid < world && tid != rank) {                    // thread t handles peer t
         // the release orders the whole CTA's stores (made visible to this thread by the barrier) before the flag
         st_release_sys(ar_flag(me.peer[tid], parity, rank, cta), epoch);
         const uint32_t *f = ar_flag(base, parity, tid, cta);
@@ -159,6 +150,35 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArP
         (void)ld_acquire_sys(f);
     }
     __syncthreads();
+}
+
+// The last CTA of a launch to get here advances the call counter (every CTA read it at its start).
+__device__ __forceinline__ void ar_finish(ArCtrl *ctrl, uint32_t epoch) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&ctrl->done, 1u) == gridDim.x - 1) {
+            ctrl->done = 0;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t *>(&ctrl->epoch) = epoch;
+        }
+    }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArParams p) {
+    const ArRank &me = p.r[blockIdx.y];
+    const int rank = me.rank, world = p.world, cta = blockIdx.x, tid = threadIdx.x;
+    uint8_t *base = me.peer[rank];
+    ArCtrl *ctrl = reinterpret_cast<ArCtrl *>(base);
+    // every CTA reads the counter before the last one advances it (that one first sees all the others done)
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(&ctrl->epoch) + 1;
+    const int parity = (int)(epoch & 1u);
+    const long per = (p.nvec + gridDim.x - 1) / gridDim.x;
+    const long v0 = (long)cta * per, v1 = v0 + per < p.nvec ? v0 + per : p.nvec;
+    const uint4 *x = reinterpret_cast<const uint4 *>(me.x);
+
+    ar_exchange(p, me, ctrl, epoch, v0, v1, cta);       // 1. push, 2. signal, 3. wait
     // 4. sum in rank order
     uint4 *out = reinterpret_cast<uint4 *>(me.out);
     for (long v = v0 + tid; v < v1; v += kArThreads) {
@@ -167,15 +187,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArP
             acc8<BF16>(a, src == rank ? x[v] : ld_cg_v4(ar_slot(base, p.max_bytes, world, parity, src) + v));
         out[v] = round8<BF16>(a);
     }
-    __syncthreads();
-    if (tid == 0) {
-        __threadfence();
-        if (atomicAdd(&ctrl->done, 1u) == gridDim.x - 1) {
-            ctrl->done = 0;
-            __threadfence();
-            *reinterpret_cast<volatile uint32_t *>(&ctrl->epoch) = epoch;
-        }
-    }
+    ar_finish(ctrl, epoch);
 }
 
 template <bool BF16> __device__ __forceinline__ float cvt16(uint16_t h) {
@@ -209,28 +221,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_norm_quant_kernel(const 
     const long v0 = (long)cta * rv;
     const uint4 *x = reinterpret_cast<const uint4 *>(me.x);
 
-    for (int i = tid; i < rv; i += kArThreads) {
-        const uint4 val = x[v0 + i];
-        for (int d = 1; d < world; ++d) {
-            const int dst = (rank + d) % world;
-            ar_slot(me.peer[dst], p.max_bytes, world, parity, rank)[v0 + i] = val;
-        }
-    }
-    __syncthreads();
-    if (tid < world && tid != rank) {
-        st_release_sys(ar_flag(me.peer[tid], parity, rank, cta), epoch);
-        const uint32_t *f = ar_flag(base, parity, tid, cta);
-        const unsigned long long t0 = ar_timer();
-        uint32_t spins = 0;
-        while ((int)(ld_relaxed_sys(f) - epoch) < 0) {
-            if ((++spins & 1023u) == 0 && ar_timer() - t0 > kArWaitNs) {
-                if (atomicCAS(&ctrl->status[0], 0, 1) == 0) { ctrl->status[1] = tid; ctrl->status[2] = cta; ctrl->status[3] = (int)epoch; }
-                break;
-            }
-        }
-        (void)ld_acquire_sys(f);
-    }
-    __syncthreads();
+    ar_exchange(p, me, ctrl, epoch, v0, v0 + rv, cta);
     // the row: sum, residual add, into the residual stream and into shared memory
     uint4 *res = reinterpret_cast<uint4 *>(me.out);
     for (int i = tid; i < rv; i += kArThreads) {
@@ -324,15 +315,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_norm_quant_kernel(const 
             qrow[i] = w;
         }
     }
-    __syncthreads();
-    if (tid == 0) {
-        __threadfence();
-        if (atomicAdd(&ctrl->done, 1u) == gridDim.x - 1) {
-            ctrl->done = 0;
-            __threadfence();
-            *reinterpret_cast<volatile uint32_t *>(&ctrl->epoch) = epoch;
-        }
-    }
+    ar_finish(ctrl, epoch);
 }
 
 int ar_grid(long nvec) {
