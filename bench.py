@@ -725,7 +725,7 @@ def _algo(m, n, k, group):
 def extras(C, device, peaks):
     """Short measurements of the other kernels of the path (not the headline)."""
     ex = {}
-    for (m, k) in ((16384, 4096), (4096, 11008), (4096, 14336)):
+    for (m, k) in ((16384, 4096), (4096, 11008), (4096, 14336), (4096, 28672)):
         xs = [synth_activations(m, k, 7 + i, device) for i in range(2)]
         it = [0]
 
